@@ -1,0 +1,350 @@
+// Depthwise causal conv1d + bias + SiLU for the Mamba2 mixer: full-sequence kernels in both tensor layouts and
+// the single-token conv_state update. HBM-bound: every element is read once and written once through 128-bit
+// accesses; the (width-1)-element halo comes from the neighbouring lane by warp shuffle (or a cached re-read at
+// warp boundaries). fp32 accumulation in the tap order of anyGPU's CPU operator
+// (srcs/fused/causal_conv1d.hpp:55-84): taps oldest-first, bias last, then x / (1 + exp(-x)).
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kMaxWidth = 4;  // same limit as anyGPU's CUDA operator (srcs/fused/causal_conv1d.hpp:100)
+
+template <typename T> struct Vec16;
+template <> struct Vec16<__half>
+{
+	static constexpr int E = 8;
+	static __device__ __forceinline__ void load(const __half* p, float* f)
+	{
+		Half8 v = *reinterpret_cast<const Half8*>(p);
+		unpack8(v, f);
+	}
+	static __device__ __forceinline__ void store(__half* p, const float* f) { *reinterpret_cast<Half8*>(p) = pack8(f); }
+};
+template <> struct Vec16<float>
+{
+	static constexpr int E = 4;
+	static __device__ __forceinline__ void load(const float* p, float* f)
+	{
+		float4 v = *reinterpret_cast<const float4*>(p);
+		f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+	}
+	static __device__ __forceinline__ void store(float* p, const float* f)
+	{
+		*reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+	}
+};
+
+// ---- (batch, dims, seq_len) layout: sequence contiguous -----------------------------------------------------
+// One thread owns NV consecutive 16-byte vectors of one row. A row is S elements; S % (E*NV) == 0.
+template <typename T, int NV, int W>
+__global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict__ x, const T* __restrict__ w,
+	const T* __restrict__ bias, T* __restrict__ y, int64_t nthreads, int vec_per_row /* S / (E*NV) */, int64_t dims)
+{
+	constexpr int E = Vec16<T>::E;
+	constexpr int EPT = E * NV;
+	const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	const bool active = tid < nthreads;
+	const int64_t row = active ? tid / vec_per_row : 0;
+	const int j = active ? static_cast<int>(tid - row * vec_per_row) : 0;
+	const int64_t base = row * (static_cast<int64_t>(vec_per_row) * EPT) + static_cast<int64_t>(j) * EPT;
+
+	float v[EPT + 3];  // v[0..2] = halo, v[3..] = own elements
+	if (active)
+	{
+#pragma unroll
+		for (int i = 0; i < NV; ++i) Vec16<T>::load(x + base + i * E, v + 3 + i * E);
+	}
+	else
+	{
+#pragma unroll
+		for (int i = 0; i < EPT; ++i) v[3 + i] = 0.f;
+	}
+	// halo: last three elements of the previous lane's run (same row when j > 0)
+	const int lane = threadIdx.x & 31;
+	float h0 = __shfl_up_sync(0xffffffffu, v[EPT], 1);
+	float h1 = __shfl_up_sync(0xffffffffu, v[EPT + 1], 1);
+	float h2 = __shfl_up_sync(0xffffffffu, v[EPT + 2], 1);
+	if (!active) return;
+	if (j == 0)
+	{
+		h0 = h1 = h2 = 0.f;  // zero left padding
+	}
+	else if (lane == 0)
+	{
+		h0 = ldf(x + base - 3);
+		h1 = ldf(x + base - 2);
+		h2 = ldf(x + base - 1);
+	}
+	v[0] = h0; v[1] = h1; v[2] = h2;
+
+	const int d = static_cast<int>(row % dims);
+	float wt[W];
+#pragma unroll
+	for (int k = 0; k < W; ++k) wt[k] = ldf(w + static_cast<int64_t>(d) * W + k);
+	const float bs = ldf(bias + d);
+
+	float out[EPT];
+#pragma unroll
+	for (int i = 0; i < EPT; ++i)
+	{
+		float acc = 0.f;
+#pragma unroll
+		for (int k = 0; k < W; ++k) acc += wt[k] * v[3 + i + k - (W - 1)];
+		acc += bs;
+		out[i] = silu_f32(acc);
+	}
+#pragma unroll
+	for (int i = 0; i < NV; ++i) Vec16<T>::store(y + base + i * E, out + i * E);
+}
+
+// Any shape: one thread per output element.
+template <typename T>
+__global__ void __launch_bounds__(256) conv1d_seq_scalar_kernel(const T* __restrict__ x, const T* __restrict__ w,
+	const T* __restrict__ bias, T* __restrict__ y, int64_t total, int64_t S, int64_t dims, int W)
+{
+	const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= total) return;
+	const int64_t row = i / S;
+	const int64_t s = i - row * S;
+	const int64_t d = row % dims;
+	float acc = 0.f;
+	for (int k = 0; k < W; ++k)
+	{
+		const int64_t delta = s + k - (W - 1);
+		if (delta >= 0) acc += ldf(w + d * W + k) * ldf(x + row * S + delta);
+	}
+	acc += ldf(bias + d);
+	stf(y + i, silu_f32(acc));
+}
+
+// ---- token-major layout: channels contiguous, rows strided ---------------------------------------------------
+// One thread owns V consecutive channels (V = 16 bytes worth, or 1) and TL consecutive tokens, sliding a
+// (W-1)-row window through registers.
+template <typename T, int V, int W, int TL>
+__global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
+	int64_t seqlen, int64_t dims, int cvec /* ceil(dims / V) */)
+{
+	const int cv = blockIdx.x * blockDim.x + threadIdx.x;
+	if (cv >= cvec) return;
+	const int64_t c0 = static_cast<int64_t>(cv) * V;
+	const int64_t b = blockIdx.z;
+	const int64_t t0 = static_cast<int64_t>(blockIdx.y) * TL;
+	const T* xb = x + b * seqlen * xs;
+	T* yb = y + b * seqlen * ys;
+
+	float wt[W][V], bs[V];
+#pragma unroll
+	for (int c = 0; c < V; ++c)
+	{
+		bs[c] = ldf(bias + c0 + c);
+#pragma unroll
+		for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + (c0 + c) * W + k);
+	}
+
+	float win[W][V];  // win[0..W-2] = previous rows (oldest first), win[W-1] = current
+#pragma unroll
+	for (int k = 0; k < W - 1; ++k)
+	{
+		const int64_t t = t0 - (W - 1) + k;
+		if (t >= 0)
+		{
+			if constexpr (V > 1) Vec16<T>::load(xb + t * xs + c0, win[k]);
+			else win[k][0] = ldf(xb + t * xs + c0);
+		}
+		else
+		{
+			// before the sequence: initial conv_state [b, dims, W-1] (oldest first) or zeros
+#pragma unroll
+			for (int c = 0; c < V; ++c)
+				win[k][c] = init ? ldf(init + (b * dims + c0 + c) * (W - 1) + (t + (W - 1))) : 0.f;
+		}
+	}
+
+#pragma unroll 4
+	for (int i = 0; i < TL; ++i)
+	{
+		const int64_t t = t0 + i;
+		if (t >= seqlen) break;
+		if constexpr (V > 1) Vec16<T>::load(xb + t * xs + c0, win[W - 1]);
+		else win[W - 1][0] = ldf(xb + t * xs + c0);
+		float out[V];
+#pragma unroll
+		for (int c = 0; c < V; ++c)
+		{
+			float acc = 0.f;
+#pragma unroll
+			for (int k = 0; k < W; ++k) acc += wt[k][c] * win[k][c];
+			acc += bs[c];
+			out[c] = silu_f32(acc);
+		}
+		if constexpr (V > 1) Vec16<T>::store(yb + t * ys + c0, out);
+		else stf(yb + t * ys + c0, out[0]);
+#pragma unroll
+		for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+			for (int c = 0; c < V; ++c) win[k][c] = win[k + 1][c];
+	}
+
+	// the thread that consumed the last token holds the next conv_state in its window
+	if (fin != nullptr && t0 < seqlen && t0 + TL >= seqlen)
+	{
+#pragma unroll
+		for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+			for (int c = 0; c < V; ++c) stf(fin + (b * dims + c0 + c) * (W - 1) + k, win[k][c]);
+	}
+}
+
+// ---- decode: one token, rolling state ----------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) conv1d_update_kernel(const T* __restrict__ xt, int64_t xs, T* __restrict__ state,
+	const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ yt, int64_t ys, int64_t batch, int64_t dims, int W)
+{
+	const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= batch * dims) return;
+	const int64_t b = i / dims;
+	const int64_t d = i - b * dims;
+	const int SW = W - 1;
+	T* st = state + i * SW;
+	float s[kMaxWidth];
+	for (int k = 0; k < SW; ++k) s[k] = ldf(st + k);
+	const float xv = ldf(xt + b * xs + d);
+	float acc = 0.f;
+	for (int k = 0; k < SW; ++k) acc += ldf(w + d * W + k) * s[k];
+	acc += ldf(w + d * W + SW) * xv;
+	acc += ldf(bias + d);
+	stf(yt + b * ys + d, silu_f32(acc));
+	for (int k = 0; k + 1 < SW; ++k) stf(st + k, s[k + 1]);
+	if (SW > 0) stf(st + SW - 1, xv);
+}
+
+// ---- host launchers ----------------------------------------------------------------------------------------
+
+template <typename T, int NV>
+static int launch_seq_vec(const T* x, const T* w, const T* bias, T* y, int64_t rows, int64_t S, int64_t dims, int W,
+	cudaStream_t st)
+{
+	constexpr int EPT = Vec16<T>::E * NV;
+	const int vec_per_row = static_cast<int>(S / EPT);
+	const int64_t nthreads = rows * vec_per_row;
+	const int64_t blocks = cdiv(nthreads, 256);
+	if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const dim3 g(static_cast<unsigned>(blocks));
+	switch (W)
+	{
+	case 1: conv1d_seq_vec_kernel<T, NV, 1><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
+	case 2: conv1d_seq_vec_kernel<T, NV, 2><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
+	case 3: conv1d_seq_vec_kernel<T, NV, 3><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
+	default: conv1d_seq_vec_kernel<T, NV, 4><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
+	}
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+template <typename T>
+static int conv1d_seq(const void* xv, const void* wv, const void* bv, void* yv, int64_t batch, int64_t dims, int64_t S, int W,
+	cudaStream_t st)
+{
+	const T* x = static_cast<const T*>(xv);
+	const T* w = static_cast<const T*>(wv);
+	const T* bias = static_cast<const T*>(bv);
+	T* y = static_cast<T*>(yv);
+	const int64_t rows = batch * dims;
+	constexpr int E = Vec16<T>::E;
+	const bool al = aligned16(x) && aligned16(y);
+	if (al && S % (2 * E) == 0) return launch_seq_vec<T, 2>(x, w, bias, y, rows, S, dims, W, st);
+	if (al && S % E == 0) return launch_seq_vec<T, 1>(x, w, bias, y, rows, S, dims, W, st);
+	const int64_t total = rows * S;
+	const int64_t blocks = cdiv(total, 256);
+	if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	conv1d_seq_scalar_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, st>>>(x, w, bias, y, total, S, dims, W);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+template <typename T, int V>
+static int launch_tok(const T* x, int64_t xs, const T* w, const T* bias, T* y, int64_t ys, const T* init, T* fin,
+	int64_t batch, int64_t seqlen, int64_t dims, int W, cudaStream_t st)
+{
+	constexpr int TL = 16;
+	const int cvec = static_cast<int>(cdiv(dims, V));
+	const dim3 g(static_cast<unsigned>(cdiv(cvec, 128)), static_cast<unsigned>(cdiv(seqlen, TL)), static_cast<unsigned>(batch));
+	if (g.y > 65535u || g.z > 65535u) return B200_ERR_UNSUPPORTED;
+	switch (W)
+	{
+	case 1: conv1d_tok_kernel<T, V, 1, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
+	case 2: conv1d_tok_kernel<T, V, 2, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
+	case 3: conv1d_tok_kernel<T, V, 3, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
+	default: conv1d_tok_kernel<T, V, 4, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
+	}
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+template <typename T>
+static int conv1d_tok(const void* xv, int64_t xs, const void* wv, const void* bv, void* yv, int64_t ys, const void* init,
+	void* fin, int64_t batch, int64_t seqlen, int64_t dims, int W, cudaStream_t st)
+{
+	constexpr int E = Vec16<T>::E;
+	const bool vec = aligned16(xv) && aligned16(yv) && xs % E == 0 && ys % E == 0 && dims % E == 0;
+	if (vec)
+		return launch_tok<T, E>(static_cast<const T*>(xv), xs, static_cast<const T*>(wv), static_cast<const T*>(bv),
+			static_cast<T*>(yv), ys, static_cast<const T*>(init), static_cast<T*>(fin), batch, seqlen, dims, W, st);
+	return launch_tok<T, 1>(static_cast<const T*>(xv), xs, static_cast<const T*>(wv), static_cast<const T*>(bv),
+		static_cast<T*>(yv), ys, static_cast<const T*>(init), static_cast<T*>(fin), batch, seqlen, dims, W, st);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_causal_conv1d(int dtype, const void* x, const void* w, const void* bias, void* y,
+	int64_t batch, int64_t dims, int64_t seqlen, int width, void* stream)
+{
+	if (!x || !w || !bias || !y) return B200_ERR_NULL;
+	if (batch < 0 || dims <= 0 || seqlen < 0 || width < 1 || width > kMaxWidth) return B200_ERR_BAD_SHAPE;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	if (dtype == B200_F16) return conv1d_seq<__half>(x, w, bias, y, batch, dims, seqlen, width, st);
+	if (dtype == B200_F32) return conv1d_seq<float>(x, w, bias, y, batch, dims, seqlen, width, st);
+	return B200_ERR_UNSUPPORTED;
+}
+
+extern "C" int b200_causal_conv1d_tokens(int dtype, const void* x, int64_t x_stride, const void* w, const void* bias,
+	void* y, int64_t y_stride, const void* initial_state, void* final_state,
+	int64_t batch, int64_t seqlen, int64_t dims, int width, void* stream)
+{
+	if (!x || !w || !bias || !y) return B200_ERR_NULL;
+	if (batch < 0 || dims <= 0 || seqlen < 0 || width < 1 || width > kMaxWidth || x_stride < dims || y_stride < dims)
+		return B200_ERR_BAD_SHAPE;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	if (dtype == B200_F16)
+		return conv1d_tok<__half>(x, x_stride, w, bias, y, y_stride, initial_state, final_state, batch, seqlen, dims, width, st);
+	if (dtype == B200_F32)
+		return conv1d_tok<float>(x, x_stride, w, bias, y, y_stride, initial_state, final_state, batch, seqlen, dims, width, st);
+	return B200_ERR_UNSUPPORTED;
+}
+
+extern "C" int b200_causal_conv1d_update(int dtype, const void* x_t, int64_t x_stride, void* conv_state, const void* w,
+	const void* bias, void* y_t, int64_t y_stride, int64_t batch, int64_t dims, int width, void* stream)
+{
+	if (!x_t || !conv_state || !w || !bias || !y_t) return B200_ERR_NULL;
+	if (batch < 0 || dims <= 0 || width < 1 || width > kMaxWidth || x_stride < dims || y_stride < dims) return B200_ERR_BAD_SHAPE;
+	if (batch == 0) return B200_OK;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	const unsigned blocks = static_cast<unsigned>(cdiv(batch * dims, 256));
+	if (dtype == B200_F16)
+		conv1d_update_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(x_t), x_stride,
+			static_cast<__half*>(conv_state), static_cast<const __half*>(w), static_cast<const __half*>(bias),
+			static_cast<__half*>(y_t), y_stride, batch, dims, width);
+	else if (dtype == B200_F32)
+		conv1d_update_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(x_t), x_stride,
+			static_cast<float*>(conv_state), static_cast<const float*>(w), static_cast<const float*>(bias),
+			static_cast<float*>(y_t), y_stride, batch, dims, width);
+	else
+		return B200_ERR_UNSUPPORTED;
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}

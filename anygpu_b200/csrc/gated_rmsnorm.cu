@@ -1,0 +1,200 @@
+// Fused gated RMSNorm: y = (x * silu(z)) * rsqrt(mean(g^2) + eps) * w in one pass over x and z.
+// Stands in for the silu -> mul -> rms_norm chain of tensor_zamba_gated_rmsnorm
+// (srcs/models/zamba2/zamba_gated_rmsnorm.hpp:9-23): 3 launches / 8 tensor passes there, 2 reads + 1 write here.
+// HBM-bound: one CTA per (row, group); the gated values stay in registers between the statistic and the scaling.
+#include "common.cuh"
+
+namespace b200 {
+
+constexpr int kNormThreads = 256;
+constexpr int kNormCache = 4;  // 16-byte vectors cached per thread (covers groups up to 8192 f16 / 4096 f32 elements)
+
+template <typename T> struct NV;
+template <> struct NV<__half>
+{
+	static constexpr int E = 8;
+	static __device__ __forceinline__ void load(const __half* p, float* f) { unpack8(*reinterpret_cast<const Half8*>(p), f); }
+	static __device__ __forceinline__ void store(__half* p, const float* f) { *reinterpret_cast<Half8*>(p) = pack8(f); }
+};
+template <> struct NV<float>
+{
+	static constexpr int E = 4;
+	static __device__ __forceinline__ void load(const float* p, float* f)
+	{
+		const float4 v = *reinterpret_cast<const float4*>(p);
+		f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+	}
+	static __device__ __forceinline__ void store(float* p, const float* f)
+	{
+		*reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+	}
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red)
+{
+	v = warp_sum(v);
+	const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+	if (lane == 0) red[wid] = v;
+	__syncthreads();
+	float t = (lane < kNormThreads / 32) ? red[lane] : 0.f;
+	t = warp_sum(t);
+	return t;  // identical in every thread of every warp
+}
+
+// VEC: 16-byte vectors (rows and group starts 16-byte aligned). CACHED: the group fits the register cache.
+template <typename T, bool CACHED>
+__global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T* __restrict__ x, int64_t xs,
+	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* __restrict__ y, int64_t ys, int gsize, int ngroups, float eps)
+{
+	constexpr int E = NV<T>::E;
+	__shared__ float red[kNormThreads / 32];
+	const int64_t row = blockIdx.x / ngroups;
+	const int grp = static_cast<int>(blockIdx.x - row * ngroups);
+	const T* xr = x + row * xs + static_cast<int64_t>(grp) * gsize;
+	const T* zr = z + row * zs + static_cast<int64_t>(grp) * gsize;
+	const T* wr = w + static_cast<int64_t>(grp) * gsize;
+	T* yr = y + row * ys + static_cast<int64_t>(grp) * gsize;
+	const int nvec = gsize / E;
+
+	float g[CACHED ? kNormCache : 1][E];
+	float ss = 0.f;
+	if constexpr (CACHED)
+	{
+#pragma unroll
+		for (int it = 0; it < kNormCache; ++it)
+		{
+			const int i = threadIdx.x + it * kNormThreads;
+			if (i < nvec)
+			{
+				float xv[E], zv[E];
+				NV<T>::load(xr + i * E, xv);
+				NV<T>::load(zr + i * E, zv);
+#pragma unroll
+				for (int e = 0; e < E; ++e)
+				{
+					const float gv = xv[e] * silu_f32(zv[e]);
+					g[it][e] = gv;
+					ss += gv * gv;
+				}
+			}
+		}
+	}
+	else
+	{
+		for (int i = threadIdx.x; i < nvec; i += kNormThreads)
+		{
+			float xv[E], zv[E];
+			NV<T>::load(xr + i * E, xv);
+			NV<T>::load(zr + i * E, zv);
+#pragma unroll
+			for (int e = 0; e < E; ++e)
+			{
+				const float gv = xv[e] * silu_f32(zv[e]);
+				ss += gv * gv;
+			}
+		}
+	}
+	const float total = block_sum(ss, red);
+	const float scale = rsqrtf(total / static_cast<float>(gsize) + eps);
+
+	if constexpr (CACHED)
+	{
+#pragma unroll
+		for (int it = 0; it < kNormCache; ++it)
+		{
+			const int i = threadIdx.x + it * kNormThreads;
+			if (i < nvec)
+			{
+				float wv[E], o[E];
+				NV<T>::load(wr + i * E, wv);
+#pragma unroll
+				for (int e = 0; e < E; ++e) o[e] = g[it][e] * scale * wv[e];
+				NV<T>::store(yr + i * E, o);
+			}
+		}
+	}
+	else
+	{
+		for (int i = threadIdx.x; i < nvec; i += kNormThreads)
+		{
+			float xv[E], zv[E], wv[E], o[E];
+			NV<T>::load(xr + i * E, xv);
+			NV<T>::load(zr + i * E, zv);
+			NV<T>::load(wr + i * E, wv);
+#pragma unroll
+			for (int e = 0; e < E; ++e) o[e] = xv[e] * silu_f32(zv[e]) * scale * wv[e];
+			NV<T>::store(yr + i * E, o);
+		}
+	}
+}
+
+// Any alignment / size.
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_scalar_kernel(const T* __restrict__ x, int64_t xs,
+	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* __restrict__ y, int64_t ys, int gsize, int ngroups, float eps)
+{
+	__shared__ float red[kNormThreads / 32];
+	const int64_t row = blockIdx.x / ngroups;
+	const int grp = static_cast<int>(blockIdx.x - row * ngroups);
+	const T* xr = x + row * xs + static_cast<int64_t>(grp) * gsize;
+	const T* zr = z + row * zs + static_cast<int64_t>(grp) * gsize;
+	const T* wr = w + static_cast<int64_t>(grp) * gsize;
+	T* yr = y + row * ys + static_cast<int64_t>(grp) * gsize;
+	float ss = 0.f;
+	for (int i = threadIdx.x; i < gsize; i += kNormThreads)
+	{
+		const float gv = ldf(xr + i) * silu_f32(ldf(zr + i));
+		ss += gv * gv;
+	}
+	const float total = block_sum(ss, red);
+	const float scale = rsqrtf(total / static_cast<float>(gsize) + eps);
+	for (int i = threadIdx.x; i < gsize; i += kNormThreads)
+	{
+		const float gv = ldf(xr + i) * silu_f32(ldf(zr + i));
+		stf(yr + i, gv * scale * ldf(wr + i));
+	}
+}
+
+template <typename T>
+static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs, const void* wv, void* yv, int64_t ys,
+	int64_t rows, int64_t d, int64_t gsize, float eps, cudaStream_t st)
+{
+	constexpr int E = NV<T>::E;
+	const T* x = static_cast<const T*>(xv);
+	const T* z = static_cast<const T*>(zv);
+	const T* w = static_cast<const T*>(wv);
+	T* y = static_cast<T*>(yv);
+	const int ngroups = static_cast<int>(d / gsize);
+	const int64_t blocks = rows * ngroups;
+	if (blocks > 0x7fffffffLL || gsize > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const unsigned g = static_cast<unsigned>(blocks);
+	const int gs = static_cast<int>(gsize);
+	const bool vec = aligned16(x) && aligned16(z) && aligned16(w) && aligned16(y) && xs % E == 0 && zs % E == 0 && ys % E == 0 &&
+		gsize % E == 0;
+	if (!vec)
+		gated_rmsnorm_scalar_kernel<T><<<g, kNormThreads, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+	else if (gsize / E <= kNormCache * kNormThreads)
+		gated_rmsnorm_vec_kernel<T, true><<<g, kNormThreads, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+	else
+		gated_rmsnorm_vec_kernel<T, false><<<g, kNormThreads, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gated_rmsnorm(int dtype, const void* x, int64_t x_stride, const void* z, int64_t z_stride, const void* w,
+	void* y, int64_t y_stride, int64_t rows, int64_t d, int64_t group_size, float eps, void* stream)
+{
+	if (!x || !z || !w || !y) return B200_ERR_NULL;
+	if (group_size == 0) group_size = d;
+	if (rows < 0 || d <= 0 || group_size <= 0 || d % group_size != 0 || x_stride < d || z_stride < d || y_stride < d)
+		return B200_ERR_BAD_SHAPE;
+	if (rows == 0) return B200_OK;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	if (dtype == B200_F16) return gated_rmsnorm<__half>(x, x_stride, z, z_stride, w, y, y_stride, rows, d, group_size, eps, st);
+	if (dtype == B200_F32) return gated_rmsnorm<float>(x, x_stride, z, z_stride, w, y, y_stride, rows, d, group_size, eps, st);
+	return B200_ERR_UNSUPPORTED;
+}

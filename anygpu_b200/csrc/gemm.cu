@@ -1,0 +1,436 @@
+// Y[M,N] = X[M,K] . W for the in_proj / out_proj of the Mamba2 mixer.
+//
+// f16: persistent, warp-specialised tcgen05 kernel. One CTA per SM walks 128x256 output tiles:
+//   warp 0    : TMA producer  - 128B-swizzled [128x64] X tiles and [256x64] W tiles into a 4-stage shared-memory ring
+//   warp 1    : MMA issuer    - tcgen05.mma (M128 N256 K16, f16 in, fp32 accumulate) into one of two TMEM accumulators
+//   warps 2-5 : epilogue      - tcgen05.ld the finished accumulator, round to f16, 16-byte stores; overlaps the next tile's MMAs
+// W is consumed as stored: (in,out) row-major tiles are fed MN-major, (out,in) row-major tiles K-major. Tails in M, N
+// and K come from TMA zero fill and predicated stores. Every mbarrier wait is bounded.
+//
+// f32: exact fp32 SIMT kernel (64x64 tiles through shared memory), for Tensor<float32> callers.
+#include <mutex>
+#include <unordered_map>
+#include <cstring>
+
+#include "tcgen05.cuh"
+
+namespace b200 {
+
+// ---- tensor-map encoding ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+	const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+	CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn()
+{
+	static EncodeTiledFn fn = []() -> EncodeTiledFn {
+		void* p = nullptr;
+		cudaDriverEntryPointQueryResult q;
+		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+		if (q != cudaDriverEntryPointSuccess) return nullptr;
+		return reinterpret_cast<EncodeTiledFn>(p);
+	}();
+	return fn;
+}
+
+int encode_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
+	uint32_t box_rows)
+{
+	EncodeTiledFn fn = get_encode_fn();
+	if (!fn) return B200_ERR_CUDA;
+	const cuuint64_t dims[2] = { cols, rows };
+	const cuuint64_t strides[1] = { ld_elems * sizeof(__half) };
+	const cuuint32_t box[2] = { box_cols, box_rows };
+	const cuuint32_t estr[2] = { 1, 1 };
+	const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+		CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS)
+	{
+		g_last_cuda_error = static_cast<int>(r);
+		return B200_ERR_CUDA;
+	}
+	return B200_OK;
+}
+
+// Encoding a map costs a few microseconds of host time; the mixer re-issues the same few (pointer, shape) pairs
+// every step, so keep the most recent ones.
+struct TmapKey
+{
+	const void* base;
+	uint64_t rows, cols, ld;
+	uint32_t bc, br;
+	bool operator==(const TmapKey& o) const
+	{
+		return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && bc == o.bc && br == o.br;
+	}
+};
+struct TmapKeyHash
+{
+	size_t operator()(const TmapKey& k) const
+	{
+		size_t h = reinterpret_cast<size_t>(k.base);
+		h ^= k.rows * 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+		h ^= k.cols * 0xc2b2ae3d27d4eb4full + (h << 6) + (h >> 2);
+		h ^= (k.ld + k.bc * 131 + k.br * 7) * 0x165667b19e3779f9ull + (h << 6) + (h >> 2);
+		return h;
+	}
+};
+
+static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t bc, uint32_t br)
+{
+	static std::mutex mu;
+	static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+	const TmapKey key{ base, rows, cols, ld, bc, br };
+	{
+		std::lock_guard<std::mutex> lk(mu);
+		auto it = cache.find(key);
+		if (it != cache.end())
+		{
+			std::memcpy(out, &it->second, sizeof(CUtensorMap));
+			return B200_OK;
+		}
+	}
+	const int rc = encode_tmap_2d_f16(out, base, rows, cols, ld, bc, br);
+	if (rc) return rc;
+	std::lock_guard<std::mutex> lk(mu);
+	if (cache.size() > 256) cache.clear();
+	cache.emplace(key, *out);
+	return B200_OK;
+}
+
+// ---- f16 tcgen05 kernel -----------------------------------------------------------------------------------
+
+namespace gemm {
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the ring to 1024 B
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;  // two 256-column fp32 accumulators
+}  // namespace gemm
+
+template <int B_MN>
+__global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+	const __grid_constant__ CUtensorMap tmB, __half* __restrict__ Y, int64_t ldy, int M, int N, int K, int m_tiles, int n_tiles,
+	uint32_t* err_word)
+{
+	using namespace gemm;
+	using namespace tc;
+	extern __shared__ uint8_t smem_raw[];
+	__shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2];
+	__shared__ uint32_t tmem_slot;
+	__shared__ int abort_flag;
+
+	const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int k_blocks = (K + BK - 1) / BK;
+	const int num_tiles = m_tiles * n_tiles;
+	volatile int* abortp = &abort_flag;
+
+	if (threadIdx.x == 0)
+	{
+		abort_flag = 0;
+		for (int s = 0; s < STAGES; ++s)
+		{
+			mbar_init(smem_u32(&bar_full[s]), 1);
+			mbar_init(smem_u32(&bar_empty[s]), 1);
+		}
+		for (int a = 0; a < 2; ++a)
+		{
+			mbar_init(smem_u32(&bar_tfull[a]), 1);
+			mbar_init(smem_u32(&bar_tempty[a]), 4);
+		}
+		fence_mbar_init();
+	}
+	if (warp == 1)
+	{
+		tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+		tmem_relinquish();
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_slot;
+
+	if (warp == 0)
+	{
+		if (lane == 0)
+		{
+			prefetch_tmap(&tmA);
+			prefetch_tmap(&tmB);
+			int stage = 0;
+			uint32_t phase = 0;
+			for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+			{
+				const int m0 = (tile % m_tiles) * BM;
+				const int n0 = (tile / m_tiles) * BN;
+				for (int kb = 0; kb < k_blocks; ++kb)
+				{
+					if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp))
+					{
+						report_timeout(err_word, kErrProducerWait);
+						goto role_done;
+					}
+					const uint32_t full = smem_u32(&bar_full[stage]);
+					const uint32_t a_s = ring + stage * STAGE_BYTES;
+					const uint32_t b_s = a_s + A_BYTES;
+					mbar_arrive_expect_tx(full, STAGE_BYTES);
+					tma_load_2d(a_s, &tmA, full, kb * BK, m0);
+					if (B_MN == 0)
+					{
+						tma_load_2d(b_s, &tmB, full, kb * BK, n0);  // W^T [N,K]: one [256 n x 64 k] box
+					}
+					else
+					{
+#pragma unroll
+						for (int j = 0; j < BN / 64; ++j)  // W [K,N]: four [64 k x 64 n] boxes
+							tma_load_2d(b_s + j * (BK * 128), &tmB, full, n0 + j * 64, kb * BK);
+					}
+					if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+				}
+			}
+		}
+	}
+	else if (warp == 1)
+	{
+		if (lane == 0)
+		{
+			constexpr uint32_t idesc = make_idesc_f16(BM, BN, B_MN);
+			int stage = 0;
+			uint32_t phase = 0;
+			int acc = 0;
+			uint32_t acc_phase = 0;
+			for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+			{
+				if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1u, abortp))
+				{
+					report_timeout(err_word, kErrMmaWaitTmem);
+					goto role_done;
+				}
+				tc_fence_after();
+				const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+				for (int kb = 0; kb < k_blocks; ++kb)
+				{
+					if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp))
+					{
+						report_timeout(err_word, kErrMmaWaitFull);
+						goto role_done;
+					}
+					tc_fence_after();
+					const uint32_t a_s = ring + stage * STAGE_BYTES;
+					const uint32_t b_s = a_s + A_BYTES;
+					const uint64_t a_desc = make_smem_desc_sw128(a_s, 16, 1024);
+					const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_s, BK * 128, 1024) : make_smem_desc_sw128(b_s, 16, 1024);
+#pragma unroll
+					for (int k = 0; k < BK / 16; ++k)
+					{
+						// K-major: 16 f16 = 32 B along the swizzled row; MN-major: 16 k-rows = two 1024-byte groups
+						const uint64_t a_k = a_desc + static_cast<uint64_t>(k * 2);
+						const uint64_t b_k = b_desc + static_cast<uint64_t>(B_MN ? k * 128 : k * 2);
+						mma_f16_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+					}
+					mma_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
+					if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+				}
+				mma_commit(smem_u32(&bar_tfull[acc]));  // accumulator complete
+				if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+			}
+		}
+	}
+	else
+	{
+		const int q = warp & 3;  // TMEM lane quadrant this warp may read
+		int acc = 0;
+		uint32_t acc_phase = 0;
+		for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+		{
+			const int m0 = (tile % m_tiles) * BM;
+			const int n0 = (tile / m_tiles) * BN;
+			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp))
+			{
+				if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
+				goto role_done;
+			}
+			tc_fence_after();
+			const int row = m0 + q * 32 + lane;
+			__half* yrow = Y + static_cast<int64_t>(row) * ldy + n0;
+			const uint32_t t_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+			for (int c = 0; c < BN / 32; ++c)
+			{
+				if (n0 + c * 32 >= N) break;  // warp-uniform
+				uint32_t r[32];
+				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 32), r);
+				tmem_ld_wait();
+				if (row < M)
+				{
+#pragma unroll
+					for (int v = 0; v < 4; ++v)
+					{
+						const int col = n0 + c * 32 + v * 8;
+						if (col < N)  // N % 8 == 0, so a vector is either fully inside or fully outside
+						{
+							Half8 h;
+#pragma unroll
+							for (int e = 0; e < 4; ++e)
+								h.h[e] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
+							*reinterpret_cast<Half8*>(yrow + c * 32 + v * 8) = h;
+						}
+					}
+				}
+			}
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
+			if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+		}
+	}
+
+role_done:
+	__syncwarp();
+	if (*abortp)
+	{
+		// give copies and MMAs already in flight time to land before shared and tensor memory are released
+		for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+	}
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 1)
+	{
+		tc_fence_after();
+		tmem_dealloc(tmem_base, TMEM_COLS);
+	}
+}
+
+static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout, __half* y, int64_t ldy, int64_t M, int64_t K,
+	int64_t N, cudaStream_t st)
+{
+	using namespace gemm;
+	if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y))
+		return B200_ERR_MISALIGNED;
+	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	CUtensorMap tmA, tmB;
+	int rc = cached_tmap(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
+	if (rc) return rc;
+	if (w_layout == B200_W_NK)
+		rc = cached_tmap(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, BN);
+	else
+		rc = cached_tmap(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
+	if (rc) return rc;
+	const int m_tiles = static_cast<int>(cdiv(M, BM)), n_tiles = static_cast<int>(cdiv(N, BN));
+	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+	const unsigned grid = static_cast<unsigned>(tiles < kNumSMs ? tiles : kNumSMs);
+	static bool attr_set[2] = { false, false };
+	if (w_layout == B200_W_NK)
+	{
+		if (!attr_set[0])
+		{
+			B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+			attr_set[0] = true;
+		}
+		gemm_f16_tcgen05_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, y, ldy, static_cast<int>(M), static_cast<int>(N),
+			static_cast<int>(K), m_tiles, n_tiles, device_error_word());
+	}
+	else
+	{
+		if (!attr_set[1])
+		{
+			B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+			attr_set[1] = true;
+		}
+		gemm_f16_tcgen05_kernel<1><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, y, ldy, static_cast<int>(M), static_cast<int>(N),
+			static_cast<int>(K), m_tiles, n_tiles, device_error_word());
+	}
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+// ---- f32 SIMT kernel --------------------------------------------------------------------------------------
+// 64x64 output tile, 16x16 threads, 4x4 per thread, k in slices of 16. ws_k / ws_n: element strides of W along k and n.
+__global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restrict__ X, int64_t ldx, const float* __restrict__ W,
+	int64_t ws_k, int64_t ws_n, float* __restrict__ Y, int64_t ldy, int M, int N, int K)
+{
+	__shared__ __align__(16) float sa[16][64 + 4];  // [k][m]
+	__shared__ __align__(16) float sb[16][64 + 4];  // [k][n]
+	const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+	const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+	float acc[4][4] = {};
+	for (int k0 = 0; k0 < K; k0 += 16)
+	{
+		for (int idx = threadIdx.x; idx < 16 * 64; idx += 256)
+		{
+			{
+				const int kk = idx & 15, mm = idx >> 4;  // X: k contiguous
+				const int m = m0 + mm, k = k0 + kk;
+				sa[kk][mm] = (m < M && k < K) ? X[static_cast<int64_t>(m) * ldx + k] : 0.f;
+			}
+			{
+				int kk, nn;
+				if (ws_n == 1) { nn = idx & 63; kk = idx >> 6; }  // W (K,N): n contiguous
+				else { kk = idx & 15; nn = idx >> 4; }             // W (N,K): k contiguous
+				const int n = n0 + nn, k = k0 + kk;
+				sb[kk][nn] = (n < N && k < K) ? W[static_cast<int64_t>(k) * ws_k + static_cast<int64_t>(n) * ws_n] : 0.f;
+			}
+		}
+		__syncthreads();
+#pragma unroll
+		for (int kk = 0; kk < 16; ++kk)
+		{
+			const float4 a = *reinterpret_cast<const float4*>(&sa[kk][ty * 4]);
+			const float4 b = *reinterpret_cast<const float4*>(&sb[kk][tx * 4]);
+			const float ar[4] = { a.x, a.y, a.z, a.w };
+			const float br[4] = { b.x, b.y, b.z, b.w };
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+#pragma unroll
+				for (int j = 0; j < 4; ++j) acc[i][j] += ar[i] * br[j];
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int i = 0; i < 4; ++i)
+#pragma unroll
+		for (int j = 0; j < 4; ++j)
+		{
+			const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
+			if (m < M && n < N) Y[static_cast<int64_t>(m) * ldy + n] = acc[i][j];
+		}
+}
+
+static int gemm_f32(const float* x, int64_t ldx, const float* w, int w_layout, float* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+	cudaStream_t st)
+{
+	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const dim3 g(static_cast<unsigned>(cdiv(N, 64)), static_cast<unsigned>(cdiv(M, 64)));
+	if (g.y > 65535u) return B200_ERR_UNSUPPORTED;
+	const int64_t ws_k = w_layout == B200_W_KN ? N : 1;
+	const int64_t ws_n = w_layout == B200_W_KN ? 1 : K;
+	gemm_f32_simt_kernel<<<g, 256, 0, st>>>(x, ldx, w, ws_k, ws_n, y, ldy, static_cast<int>(M), static_cast<int>(N),
+		static_cast<int>(K));
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_linear(int dtype, const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy,
+	int64_t M, int64_t K, int64_t N, void* stream)
+{
+	if (!x || !w || !y) return B200_ERR_NULL;
+	if (M < 0 || K <= 0 || N <= 0 || ldx < K || ldy < N) return B200_ERR_BAD_SHAPE;
+	if (w_layout != B200_W_KN && w_layout != B200_W_NK) return B200_ERR_UNSUPPORTED;
+	if (M == 0) return B200_OK;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	if (dtype == B200_F16)
+		return gemm_f16(static_cast<const __half*>(x), ldx, static_cast<const __half*>(w), w_layout, static_cast<__half*>(y), ldy, M,
+			K, N, st);
+	if (dtype == B200_F32)
+		return gemm_f32(static_cast<const float*>(x), ldx, static_cast<const float*>(w), w_layout, static_cast<float*>(y), ldy, M, K,
+			N, st);
+	return B200_ERR_UNSUPPORTED;
+}

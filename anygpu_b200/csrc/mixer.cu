@@ -1,0 +1,242 @@
+// The Mamba2 mixer of a Zamba2 block, composed from the operators of this library with every slice of the
+// in_proj output (z | xBC | dt) and of the conv output (x | B | C) consumed in place through row strides:
+//   prefill: in_proj GEMM -> causal conv1d+SiLU (token-major) -> SSD chunked scan -> gated RMSNorm -> out_proj GEMM
+//   decode : in_proj GEMM -> conv_state update -> ssm_state recurrence -> gated RMSNorm -> out_proj GEMM
+// Six to eight launches on one stream, no allocation, no host synchronisation.
+#include "common.cuh"
+
+namespace b200 {
+
+struct MixerDims
+{
+	int64_t conv_dim, d_in_proj;
+	size_t esz;
+};
+
+static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
+{
+	if (!c) return false;
+	if (c->d_model <= 0 || c->d_inner <= 0 || c->nheads <= 0 || c->headdim <= 0 || c->d_state <= 0 || c->ngroups <= 0 ||
+		c->d_conv < 1 || c->d_conv > 4 || c->chunk <= 0)
+		return false;
+	if (c->nheads * c->headdim != c->d_inner || c->nheads % c->ngroups != 0) return false;
+	if (c->norm_group_size != 0 && c->d_inner % c->norm_group_size != 0) return false;
+	if (dtype != B200_F16 && dtype != B200_F32) return false;
+	m->conv_dim = c->d_inner + 2 * c->ngroups * c->d_state;
+	m->d_in_proj = 2 * c->d_inner + 2 * c->ngroups * c->d_state + c->nheads;
+	m->esz = dtype == B200_F16 ? 2 : 4;
+	return true;
+}
+
+// ---- optional per-stage timing of the prefill mixer (CUDA events on the caller's stream) -------------------------
+constexpr int kStages = 5;       // in_proj, conv1d, ssd, gated_rmsnorm, out_proj
+constexpr int kTimingSlots = 256;  // mixer calls recorded between two collects
+
+struct StageTiming
+{
+	bool enabled = false;
+	int calls = 0;
+	cudaEvent_t ev[kTimingSlots][kStages + 1] = {};
+	bool created = false;
+};
+static StageTiming g_timing;
+
+static void stage_mark(int stage, cudaStream_t st)
+{
+	if (g_timing.enabled && g_timing.calls < kTimingSlots) cudaEventRecord(g_timing.ev[g_timing.calls][stage], st);
+}
+
+struct PrefillWs
+{
+	char* zxbcdt;
+	char* xbc;
+	char* y;
+	char* ssd;
+	size_t ssd_bytes;
+	size_t bytes;
+};
+
+static PrefillWs carve_prefill(void* base, const b200_mamba2_config* c, const MixerDims& m, int64_t batch, int64_t seqlen)
+{
+	PrefillWs w;
+	const size_t T = static_cast<size_t>(batch) * seqlen;
+	char* p = static_cast<char*>(base);
+	size_t off = 0;
+	w.zxbcdt = p + off; off += align_up(T * m.d_in_proj * m.esz, 256);
+	w.xbc = p + off; off += align_up(T * m.conv_dim * m.esz, 256);
+	w.y = p + off; off += align_up(T * c->d_inner * m.esz, 256);
+	w.ssd = p + off;
+	w.ssd_bytes = b200_mamba_chunk_scan_combined_workspace_bytes(batch, seqlen, c->nheads, c->headdim, c->ngroups, c->d_state, c->chunk);
+	off += w.ssd_bytes;
+	w.bytes = off;
+	return w;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_mamba2_mixer_prefill_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen)
+{
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0 || seqlen <= 0) return 0;
+	return carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
+}
+
+extern "C" int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, int64_t batch, int64_t seqlen,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !u || !out) return B200_ERR_NULL;
+	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
+		!w->out_proj_weight)
+		return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch < 0 || seqlen < 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const PrefillWs ws = carve_prefill(workspace, cfg, m, batch, seqlen);
+	if (workspace_bytes < ws.bytes) return B200_ERR_WORKSPACE;
+
+	const int64_t T = batch * seqlen;
+	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
+	const size_t e = m.esz;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	stage_mark(0, st);
+	int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model,
+		m.d_in_proj, stream);
+	if (rc) return rc;
+	stage_mark(1, st);
+	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
+		nullptr, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+	if (rc) return rc;
+	stage_mark(2, st);
+	rc = b200_mamba_chunk_scan_combined(dtype, ws.xbc, m.conv_dim, ws.zxbcdt + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
+		ws.xbc + d_inner * e, m.conv_dim, ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, ws.y, d_inner,
+		ssm_state_out, batch, seqlen, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, 1, ws.ssd, ws.ssd_bytes,
+		stream);
+	if (rc) return rc;
+	stage_mark(3, st);
+	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,
+		cfg->norm_group_size, cfg->eps, stream);
+	if (rc) return rc;
+	stage_mark(4, st);
+	rc = b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out, cfg->d_model, T, d_inner, cfg->d_model,
+		stream);
+	if (rc) return rc;
+	stage_mark(5, st);
+	if (g_timing.enabled && g_timing.calls < kTimingSlots) ++g_timing.calls;
+	return B200_OK;
+}
+
+extern "C" int b200_stage_timing_enable(int enable)
+{
+	if (enable && !g_timing.created)
+	{
+		for (int i = 0; i < kTimingSlots; ++i)
+			for (int j = 0; j <= kStages; ++j) B200_CUDA_TRY(cudaEventCreate(&g_timing.ev[i][j]));
+		g_timing.created = true;
+	}
+	g_timing.enabled = enable != 0;
+	g_timing.calls = 0;
+	return B200_OK;
+}
+
+extern "C" int b200_stage_timing_collect(float* stage_ms, int* calls)
+{
+	if (!stage_ms || !calls) return B200_ERR_NULL;
+	for (int j = 0; j < kStages; ++j) stage_ms[j] = 0.f;
+	*calls = g_timing.calls;
+	for (int i = 0; i < g_timing.calls; ++i)
+	{
+		B200_CUDA_TRY(cudaEventSynchronize(g_timing.ev[i][kStages]));
+		for (int j = 0; j < kStages; ++j)
+		{
+			float ms = 0.f;
+			B200_CUDA_TRY(cudaEventElapsedTime(&ms, g_timing.ev[i][j], g_timing.ev[i][j + 1]));
+			stage_ms[j] += ms;
+		}
+	}
+	g_timing.calls = 0;
+	return B200_OK;
+}
+
+extern "C" size_t b200_mamba2_mixer_prefill_host_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch,
+	int64_t seqlen)
+{
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0 || seqlen <= 0) return 0;
+	const size_t io = align_up(static_cast<size_t>(batch) * seqlen * cfg->d_model * m.esz, 256);
+	return 2 * io + carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
+}
+
+extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !u_host || !out_host) return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch < 0 || seqlen < 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const size_t io_bytes = static_cast<size_t>(batch) * seqlen * cfg->d_model * m.esz;
+	const size_t io = align_up(io_bytes, 256);
+	const size_t inner = carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
+	if (workspace_bytes < 2 * io + inner) return B200_ERR_WORKSPACE;
+	char* p = static_cast<char*>(workspace);
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	B200_CUDA_TRY(cudaMemcpyAsync(p, u_host, io_bytes, cudaMemcpyHostToDevice, st));
+	const int rc = b200_mamba2_mixer_prefill(dtype, cfg, w, p, p + io, batch, seqlen, nullptr, nullptr, nullptr, p + 2 * io, inner,
+		stream);
+	if (rc) return rc;
+	B200_CUDA_TRY(cudaMemcpyAsync(out_host, p + io, io_bytes, cudaMemcpyDeviceToHost, st));
+	return B200_OK;
+}
+
+extern "C" size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch)
+{
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0) return 0;
+	return align_up(batch * m.d_in_proj * m.esz, 256) + align_up(batch * m.conv_dim * m.esz, 256) +
+		align_up(batch * cfg->d_inner * m.esz, 256);
+}
+
+extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !u_t || !out_t || !conv_state || !ssm_state) return B200_ERR_NULL;
+	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
+		!w->out_proj_weight)
+		return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch < 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	if (workspace_bytes < b200_mamba2_mixer_decode_workspace_bytes(cfg, dtype, batch)) return B200_ERR_WORKSPACE;
+	const size_t e = m.esz;
+	char* zx = static_cast<char*>(workspace);
+	char* xbc = zx + align_up(batch * m.d_in_proj * e, 256);
+	char* y = xbc + align_up(batch * m.conv_dim * e, 256);
+	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
+
+	int rc = b200_linear(dtype, u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model,
+		m.d_in_proj, stream);
+	if (rc) return rc;
+	rc = b200_causal_conv1d_update(dtype, zx + d_inner * e, m.d_in_proj, conv_state, w->conv1d_weight, w->conv1d_bias, xbc,
+		m.conv_dim, batch, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+	if (rc) return rc;
+	rc = b200_selective_state_update(dtype, ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
+		xbc + d_inner * e, m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, batch, cfg->nheads,
+		cfg->headdim, cfg->ngroups, cfg->d_state, 1, stream);
+	if (rc) return rc;
+	rc = b200_gated_rmsnorm(dtype, y, d_inner, zx, m.d_in_proj, w->norm_weight, y, d_inner, batch, d_inner, cfg->norm_group_size,
+		cfg->eps, stream);
+	if (rc) return rc;
+	return b200_linear(dtype, y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
+		stream);
+}

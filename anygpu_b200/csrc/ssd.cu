@@ -1,0 +1,61 @@
+// C entry point of the SSD chunked selective scan: validates, carves the workspace and runs the four stages.
+#include "ssd_common.cuh"
+
+namespace b200 {
+
+template <typename T>
+static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
+	const void* Cm, int64_t cs, const float* D, const float* dt_bias, const float* init, void* y, int64_t ys, float* fin,
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	int rc = ssd_dt_cumsum<T>(static_cast<const T*>(dt), dts, A, a_is_log, dt_bias, 1, d, w, st);
+	if (rc) return rc;
+	rc = ssd_chunk_state_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, d, w, st);
+	if (rc) return rc;
+	rc = ssd_state_passing(init, fin, d, w, st);
+	if (rc) return rc;
+	return ssd_chunk_scan_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, static_cast<const T*>(Cm), cs, D,
+		static_cast<T*>(y), ys, d, w, st);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_mamba_chunk_scan_combined_workspace_bytes(int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G,
+	int64_t N, int64_t chunk)
+{
+	if (batch <= 0 || seqlen <= 0 || H <= 0 || P <= 0 || G <= 0 || N <= 0 || chunk <= 0) return 0;
+	SsdDims d{ batch, seqlen, static_cast<int>(H), static_cast<int>(P), static_cast<int>(G), static_cast<int>(N),
+		static_cast<int>(chunk), static_cast<int>(cdiv(seqlen, chunk)) };
+	return ssd_carve(nullptr, d).bytes;
+}
+
+extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
+	const float* D, const float* dt_bias, const float* initial_states,
+	void* y, int64_t y_stride, float* final_states,
+	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!x || !dt || !A || !B || !C || !y) return B200_ERR_NULL;
+	if (batch < 0 || seqlen < 0 || H <= 0 || P <= 0 || G <= 0 || N <= 0 || chunk <= 0 || H % G != 0) return B200_ERR_BAD_SHAPE;
+	if (chunk > 256) return B200_ERR_UNSUPPORTED;
+	if (x_stride < H * P || y_stride < H * P || dt_stride < H || B_stride < G * N || C_stride < G * N) return B200_ERR_BAD_SHAPE;
+	if (dtype != B200_F16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+	if (!dt_softplus) return B200_ERR_UNSUPPORTED;  // the mixer always applies softplus (scripts/zamba2/mamba_chunk_scan_comb.py:44-45)
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	if (batch * cdiv(seqlen, chunk) * H > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	SsdDims d{ batch, seqlen, static_cast<int>(H), static_cast<int>(P), static_cast<int>(G), static_cast<int>(N),
+		static_cast<int>(chunk), static_cast<int>(cdiv(seqlen, chunk)) };
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const SsdWorkspace w = ssd_carve(workspace, d);
+	if (workspace_bytes < w.bytes) return B200_ERR_WORKSPACE;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	if (dtype == B200_F16)
+		return run_simt<__half>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
+			y_stride, final_states, d, w, st);
+	return run_simt<float>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
+		y_stride, final_states, d, w, st);
+}

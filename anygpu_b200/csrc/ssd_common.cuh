@@ -1,0 +1,57 @@
+// Shared declarations of the SSD chunked-scan stages (prefill).
+//
+// Stage structure follows mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:167-215):
+//   1. dt / cumsum     : dt = softplus(dt_raw + dt_bias), dA = dt*A, in-chunk inclusive cumsum      (:32-48)
+//   2. chunk state     : states[b,c,h,p,n] = sum_l B[l,n] exp(dAcs[last]-dAcs[l]) dt[l] x[l,p]      (:51-80)
+//   3. state passing   : running state across chunks; states[c] is replaced by the state BEFORE c   (:83-106)
+//   4. chunk scan      : y = (C.B^T o decay o causal).(dt x) + exp(dAcs) C.prev^T + D x            (:109-160)
+// Workspace layout (fp32): dt[b,H,nc,Q] | dAcs[b,H,nc,Q] | states[b,nc,H,P,N].
+#pragma once
+#include "common.cuh"
+
+namespace b200 {
+
+struct SsdDims
+{
+	int64_t batch, seqlen;
+	int H, P, G, N, Q, nchunks;
+};
+
+struct SsdWorkspace
+{
+	float* dt;
+	float* dacs;
+	float* states;
+	size_t bytes;
+};
+
+inline SsdWorkspace ssd_carve(void* base, const SsdDims& d)
+{
+	SsdWorkspace w;
+	const size_t n_dt = static_cast<size_t>(d.batch) * d.H * d.nchunks * d.Q;
+	const size_t n_st = static_cast<size_t>(d.batch) * d.nchunks * d.H * d.P * d.N;
+	const size_t o1 = align_up(n_dt * sizeof(float), 256);
+	const size_t o2 = o1 + align_up(n_dt * sizeof(float), 256);
+	char* p = static_cast<char*>(base);
+	w.dt = reinterpret_cast<float*>(p);
+	w.dacs = reinterpret_cast<float*>(p + o1);
+	w.states = reinterpret_cast<float*>(p + o2);
+	w.bytes = o2 + align_up(n_st * sizeof(float), 256);
+	return w;
+}
+
+// Stage launchers. T is the activation storage type.
+template <typename T>
+int ssd_dt_cumsum(const T* dt, int64_t dts, const float* A, int a_is_log, const float* dt_bias, int dt_softplus,
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+
+template <typename T>
+int ssd_chunk_state_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+
+int ssd_state_passing(const float* initial_states, float* final_states, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+
+template <typename T>
+int ssd_chunk_scan_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const T* Cm, int64_t cs, const float* D, T* y, int64_t ys,
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+
+}  // namespace b200

@@ -1,0 +1,365 @@
+// SSD chunked selective scan: dt/cumsum and state-passing stages (all dtypes) and exact-fp32 SIMT versions of
+// the two contraction stages. The SIMT contractions serve Tensor<float32> callers (fp32 end to end, like the
+// reference's CPU path); f16 callers take the tensor-core stages in ssd_tc.cu.
+#include "ssd_common.cuh"
+
+namespace b200 {
+
+// ---- stage 1: dt = softplus(dt_raw + bias); dAcs = cumsum_l(dt * A) within each chunk -------------------------
+// grid (b*nchunks, ceil(H/32)), 256 threads. Positions past seqlen hold dt_raw = 0 BEFORE bias and softplus,
+// exactly as the reference pads (scripts/zamba2/mamba_chunk_scan_comb.py:38-45).
+constexpr int kCsHeads = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
+	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
+	float* __restrict__ dt_out, float* __restrict__ dacs_out)
+{
+	extern __shared__ float sdt[];  // [Q][33]
+	const int64_t b = blockIdx.x / nchunks;
+	const int c = static_cast<int>(blockIdx.x % nchunks);
+	const int h0 = blockIdx.y * kCsHeads;
+	for (int idx = threadIdx.x; idx < Q * kCsHeads; idx += blockDim.x)
+	{
+		const int l = idx / kCsHeads, hh = idx % kCsHeads;
+		const int h = h0 + hh;
+		const int64_t t = static_cast<int64_t>(c) * Q + l;
+		float v = 0.f;
+		if (h < H)
+		{
+			if (t < seqlen) v = ldf(dt + (b * seqlen + t) * dts + h);
+			if (dt_bias) v += dt_bias[h];
+			if (dt_softplus) v = softplus_f32(v);
+		}
+		sdt[l * (kCsHeads + 1) + hh] = v;
+	}
+	__syncthreads();
+	const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+	const int ep = (Q + 31) / 32;  // consecutive positions per lane (<= 8)
+	for (int hh = wid; hh < kCsHeads; hh += blockDim.x / 32)
+	{
+		const int h = h0 + hh;
+		if (h >= H) break;
+		const float a = a_is_log ? -expf(A[h]) : A[h];
+		float loc[8];
+		float run = 0.f;
+#pragma unroll
+		for (int i = 0; i < 8; ++i)
+		{
+			const int l = lane * ep + i;
+			float v = 0.f;
+			if (i < ep && l < Q) v = sdt[l * (kCsHeads + 1) + hh] * a;
+			run += v;
+			loc[i] = run;
+		}
+		// exclusive prefix of lane totals
+		float incl = run;
+#pragma unroll
+		for (int o = 1; o < 32; o <<= 1)
+		{
+			const float n = __shfl_up_sync(0xffffffffu, incl, o);
+			if (lane >= o) incl += n;
+		}
+		const float excl = incl - run;
+		const int64_t base = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+#pragma unroll
+		for (int i = 0; i < 8; ++i)
+		{
+			const int l = lane * ep + i;
+			if (i < ep && l < Q)
+			{
+				dacs_out[base + l] = excl + loc[i];
+				dt_out[base + l] = sdt[l * (kCsHeads + 1) + hh];
+			}
+		}
+	}
+}
+
+template <typename T>
+int ssd_dt_cumsum(const T* dt, int64_t dts, const float* A, int a_is_log, const float* dt_bias, int dt_softplus,
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	const dim3 g(static_cast<unsigned>(d.batch * d.nchunks), static_cast<unsigned>(cdiv(d.H, kCsHeads)));
+	const size_t smem = static_cast<size_t>(d.Q) * (kCsHeads + 1) * sizeof(float);
+	ssd_dt_cumsum_kernel<T><<<g, 256, smem, st>>>(dt, dts, A, a_is_log, dt_bias, dt_softplus, d.seqlen, d.H, d.Q, d.nchunks,
+		w.dt, w.dacs);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+template int ssd_dt_cumsum<__half>(const __half*, int64_t, const float*, int, const float*, int, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+template int ssd_dt_cumsum<float>(const float*, int64_t, const float*, int, const float*, int, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+
+// ---- stage 2 (SIMT): chunk states --------------------------------------------------------------------------
+// grid (b*nchunks*H, ceil(P/64), ceil(N/64)), 16x16 threads, each a 4x4 patch of the [P x N] state.
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_chunk_state_simt_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ Bm,
+	int64_t bs, const float* __restrict__ dt, const float* __restrict__ dacs, float* __restrict__ states, int64_t seqlen, int H,
+	int P, int G, int N, int Q, int nchunks)
+{
+	__shared__ __align__(16) float sx[32][64 + 4];  // [l][p] scaled x
+	__shared__ __align__(16) float sb[32][64 + 4];  // [l][n]
+	const int h = blockIdx.x % H;
+	const int64_t bc = blockIdx.x / H;
+	const int c = static_cast<int>(bc % nchunks);
+	const int64_t b = bc / nchunks;
+	const int g = h / (H / G);
+	const int p0 = blockIdx.y * 64, n0 = blockIdx.z * 64;
+	const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+	const int64_t cbase = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+	const float last = dacs[cbase + Q - 1];
+	float acc[4][4] = {};
+	for (int l0 = 0; l0 < Q; l0 += 32)
+	{
+		for (int idx = threadIdx.x; idx < 32 * 64; idx += 256)
+		{
+			const int ll = idx >> 6, e = idx & 63;
+			const int l = l0 + ll;
+			const int64_t t = static_cast<int64_t>(c) * Q + l;
+			float xv = 0.f, bv = 0.f;
+			if (l < Q && t < seqlen)
+			{
+				const float sc = expf(last - dacs[cbase + l]) * dt[cbase + l];
+				if (p0 + e < P) xv = ldf(x + (b * seqlen + t) * xs + static_cast<int64_t>(h) * P + p0 + e) * sc;
+				if (n0 + e < N) bv = ldf(Bm + (b * seqlen + t) * bs + static_cast<int64_t>(g) * N + n0 + e);
+			}
+			sx[ll][e] = xv;
+			sb[ll][e] = bv;
+		}
+		__syncthreads();
+#pragma unroll 8
+		for (int ll = 0; ll < 32; ++ll)
+		{
+			const float4 xa = *reinterpret_cast<const float4*>(&sx[ll][ty * 4]);
+			const float4 ba = *reinterpret_cast<const float4*>(&sb[ll][tx * 4]);
+			const float xr[4] = { xa.x, xa.y, xa.z, xa.w };
+			const float br[4] = { ba.x, ba.y, ba.z, ba.w };
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+#pragma unroll
+				for (int j = 0; j < 4; ++j) acc[i][j] += xr[i] * br[j];
+		}
+		__syncthreads();
+	}
+	float* out = states + (((b * nchunks + c) * H + h) * static_cast<int64_t>(P)) * N;
+#pragma unroll
+	for (int i = 0; i < 4; ++i)
+#pragma unroll
+		for (int j = 0; j < 4; ++j)
+		{
+			const int p = p0 + ty * 4 + i, n = n0 + tx * 4 + j;
+			if (p < P && n < N) out[static_cast<int64_t>(p) * N + n] = acc[i][j];
+		}
+}
+
+template <typename T>
+int ssd_chunk_state_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	const dim3 g(static_cast<unsigned>(d.batch * d.nchunks * d.H), static_cast<unsigned>(cdiv(d.P, 64)),
+		static_cast<unsigned>(cdiv(d.N, 64)));
+	ssd_chunk_state_simt_kernel<T><<<g, 256, 0, st>>>(x, xs, Bm, bs, w.dt, w.dacs, w.states, d.seqlen, d.H, d.P, d.G, d.N, d.Q,
+		d.nchunks);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+template int ssd_chunk_state_simt<__half>(const __half*, int64_t, const __half*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+template int ssd_chunk_state_simt<float>(const float*, int64_t, const float*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+
+// ---- stage 3: state passing across chunks --------------------------------------------------------------------
+// One thread per state element walks the chunks: states[c] <- state before chunk c; carries the running state in a
+// register. Bandwidth-bound (one read + one write of the chunk states), fully coalesced.
+__global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restrict__ states, const float* __restrict__ dacs,
+	const float* __restrict__ init, float* __restrict__ fin, int H, int PN, int Q, int nchunks)
+{
+	const int i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i >= PN) return;
+	const int h = blockIdx.y;
+	const int64_t b = blockIdx.z;
+	float s = init ? init[(b * H + h) * static_cast<int64_t>(PN) + i] : 0.f;
+	for (int c = 0; c < nchunks; ++c)
+	{
+		float* p = states + ((b * nchunks + c) * H + h) * static_cast<int64_t>(PN) + i;
+		const float cur = *p;
+		*p = s;
+		const float dec = expf(dacs[((b * H + h) * nchunks + c) * static_cast<int64_t>(Q) + Q - 1]);
+		s = s * dec + cur;
+	}
+	if (fin) fin[(b * H + h) * static_cast<int64_t>(PN) + i] = s;
+}
+
+int ssd_state_passing(const float* initial_states, float* final_states, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	const int PN = d.P * d.N;
+	const dim3 g(static_cast<unsigned>(cdiv(PN, 256)), static_cast<unsigned>(d.H), static_cast<unsigned>(d.batch));
+	if (g.z > 65535u || g.y > 65535u) return B200_ERR_UNSUPPORTED;
+	ssd_state_passing_kernel<<<g, 256, 0, st>>>(w.states, w.dacs, initial_states, final_states, d.H, PN, d.Q, d.nchunks);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+// ---- stage 4 (SIMT): chunk scan -----------------------------------------------------------------------------
+// grid (b*nchunks*H, ceil(Q/64), ceil(P/64)), 16x16 threads, each a 4x4 patch of the [64 l x 64 p] output tile.
+template <typename T>
+__global__ void __launch_bounds__(256) ssd_chunk_scan_simt_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ Bm,
+	int64_t bs, const T* __restrict__ Cm, int64_t cs, const float* __restrict__ D, const float* __restrict__ dt,
+	const float* __restrict__ dacs, const float* __restrict__ prev, T* __restrict__ y, int64_t ys, int64_t seqlen, int H, int P,
+	int G, int N, int Q, int nchunks)
+{
+	// s_x (x tile [s][p]) shares storage with s_a / s_b (C tile [l][n-slice]; B tile [s][n-slice] or prev tile
+	// [p][n-slice]): their uses are separated by block barriers.
+	__shared__ __align__(16) float s_buf[64 * (64 + 4)];
+	__shared__ __align__(16) float s_s[64][64 + 4];  // decayed scores [l][s]
+	float (*s_a)[33] = reinterpret_cast<float (*)[33]>(s_buf);
+	float (*s_b)[33] = reinterpret_cast<float (*)[33]>(s_buf + 64 * 33);
+	float (*s_x)[64 + 4] = reinterpret_cast<float (*)[64 + 4]>(s_buf);
+	__shared__ float s_dl[64], s_ds[64], s_dts[64];
+	const int h = blockIdx.x % H;
+	const int64_t bc = blockIdx.x / H;
+	const int c = static_cast<int>(bc % nchunks);
+	const int64_t b = bc / nchunks;
+	const int g = h / (H / G);
+	const int l0 = blockIdx.y * 64, p0 = blockIdx.z * 64;
+	const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+	const int64_t cbase = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+	const int64_t tok0 = b * seqlen + static_cast<int64_t>(c) * Q;  // first token of the chunk
+	const int64_t valid = min(static_cast<int64_t>(Q), seqlen - static_cast<int64_t>(c) * Q);  // tokens of this chunk inside the sequence
+
+	if (threadIdx.x < 64)
+	{
+		const int l = l0 + threadIdx.x;
+		s_dl[threadIdx.x] = l < Q ? dacs[cbase + l] : 0.f;
+	}
+
+	// part 1: acc_prev[l,p] = sum_n C[l,n] prev[p,n]
+	float accp[4][4] = {};
+	const float* pst = prev + (((b * nchunks + c) * H + h) * static_cast<int64_t>(P)) * N;
+	for (int n0 = 0; n0 < N; n0 += 32)
+	{
+		for (int idx = threadIdx.x; idx < 64 * 32; idx += 256)
+		{
+			const int r = idx >> 5, e = idx & 31;
+			const int n = n0 + e;
+			const int l = l0 + r, p = p0 + r;
+			s_a[r][e] = (l < valid && n < N) ? ldf(Cm + (tok0 + l) * cs + static_cast<int64_t>(g) * N + n) : 0.f;
+			s_b[r][e] = (p < P && n < N) ? pst[static_cast<int64_t>(p) * N + n] : 0.f;
+		}
+		__syncthreads();
+#pragma unroll 8
+		for (int e = 0; e < 32; ++e)
+		{
+			float ar[4], br[4];
+#pragma unroll
+			for (int i = 0; i < 4; ++i) { ar[i] = s_a[ty * 4 + i][e]; br[i] = s_b[tx * 4 + i][e]; }
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+#pragma unroll
+				for (int j = 0; j < 4; ++j) accp[i][j] += ar[i] * br[j];
+		}
+		__syncthreads();
+	}
+
+	// part 2: acc[l,p] = sum_{s<=l} (C[l].B[s]) exp(dAcs[l]-dAcs[s]) dt[s] x[s,p]
+	float acc[4][4] = {};
+	const int s_end = min(l0 + 64, static_cast<int>(valid));  // causal: s <= l < l0+64
+	for (int s0 = 0; s0 < s_end; s0 += 64)
+	{
+		if (threadIdx.x < 64)
+		{
+			const int s = s0 + threadIdx.x;
+			s_ds[threadIdx.x] = s < Q ? dacs[cbase + s] : 0.f;
+			s_dts[threadIdx.x] = s < Q ? dt[cbase + s] : 0.f;
+		}
+		float sc[4][4] = {};
+		for (int n0 = 0; n0 < N; n0 += 32)
+		{
+			for (int idx = threadIdx.x; idx < 64 * 32; idx += 256)
+			{
+				const int r = idx >> 5, e = idx & 31;
+				const int n = n0 + e;
+				const int l = l0 + r, s = s0 + r;
+				s_a[r][e] = (l < valid && n < N) ? ldf(Cm + (tok0 + l) * cs + static_cast<int64_t>(g) * N + n) : 0.f;
+				s_b[r][e] = (s < valid && n < N) ? ldf(Bm + (tok0 + s) * bs + static_cast<int64_t>(g) * N + n) : 0.f;
+			}
+			__syncthreads();
+#pragma unroll 8
+			for (int e = 0; e < 32; ++e)
+			{
+				float ar[4], br[4];
+#pragma unroll
+				for (int i = 0; i < 4; ++i) { ar[i] = s_a[ty * 4 + i][e]; br[i] = s_b[tx * 4 + i][e]; }
+#pragma unroll
+				for (int i = 0; i < 4; ++i)
+#pragma unroll
+					for (int j = 0; j < 4; ++j) sc[i][j] += ar[i] * br[j];
+			}
+			__syncthreads();
+		}
+		// decay, dt and causal mask; stage scores and the x tile
+#pragma unroll
+		for (int i = 0; i < 4; ++i)
+#pragma unroll
+			for (int j = 0; j < 4; ++j)
+			{
+				const int lr = ty * 4 + i, sr = tx * 4 + j;
+				const int l = l0 + lr, s = s0 + sr;
+				float v = 0.f;
+				if (s <= l && l < valid) v = sc[i][j] * expf(s_dl[lr] - s_ds[sr]) * s_dts[sr];
+				s_s[lr][sr] = v;
+			}
+		for (int idx = threadIdx.x; idx < 64 * 64; idx += 256)
+		{
+			const int r = idx >> 6, e = idx & 63;
+			const int s = s0 + r, p = p0 + e;
+			s_x[r][e] = (s < valid && p < P) ? ldf(x + (tok0 + s) * xs + static_cast<int64_t>(h) * P + p) : 0.f;
+		}
+		__syncthreads();
+#pragma unroll 8
+		for (int sr = 0; sr < 64; ++sr)
+		{
+			const float4 xa = *reinterpret_cast<const float4*>(&s_x[sr][tx * 4]);
+			const float xr[4] = { xa.x, xa.y, xa.z, xa.w };
+#pragma unroll
+			for (int i = 0; i < 4; ++i)
+			{
+				const float sv = s_s[ty * 4 + i][sr];
+#pragma unroll
+				for (int j = 0; j < 4; ++j) acc[i][j] += sv * xr[j];
+			}
+		}
+		__syncthreads();
+	}
+
+	const float dh = D ? D[h] : 0.f;
+#pragma unroll
+	for (int i = 0; i < 4; ++i)
+	{
+		const int lr = ty * 4 + i;
+		const int l = l0 + lr;
+		if (l >= valid) continue;
+		const float dec = expf(s_dl[lr]);
+#pragma unroll
+		for (int j = 0; j < 4; ++j)
+		{
+			const int p = p0 + tx * 4 + j;
+			if (p >= P) continue;
+			float out = acc[i][j] + accp[i][j] * dec;
+			if (D) out += dh * ldf(x + (tok0 + l) * xs + static_cast<int64_t>(h) * P + p);
+			stf(y + (tok0 + l) * ys + static_cast<int64_t>(h) * P + p, out);
+		}
+	}
+}
+
+template <typename T>
+int ssd_chunk_scan_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const T* Cm, int64_t cs, const float* D, T* y, int64_t ys,
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	const dim3 g(static_cast<unsigned>(d.batch * d.nchunks * d.H), static_cast<unsigned>(cdiv(d.Q, 64)),
+		static_cast<unsigned>(cdiv(d.P, 64)));
+	ssd_chunk_scan_simt_kernel<T><<<g, 256, 0, st>>>(x, xs, Bm, bs, Cm, cs, D, w.dt, w.dacs, w.states, y, ys, d.seqlen, d.H, d.P,
+		d.G, d.N, d.Q, d.nchunks);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+template int ssd_chunk_scan_simt<__half>(const __half*, int64_t, const __half*, int64_t, const __half*, int64_t, const float*, __half*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+template int ssd_chunk_scan_simt<float>(const float*, int64_t, const float*, int64_t, const float*, int64_t, const float*, float*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+
+}  // namespace b200

@@ -1,0 +1,167 @@
+// Thin inline-PTX layer for the Blackwell (sm_100a) data path used by the tensor-core kernels:
+// mbarrier (with BOUNDED waits), TMA tiled loads, tensor-memory allocation, tcgen05.mma / commit / ld,
+// and the shared-memory / instruction descriptor encodings.
+#pragma once
+#include <cuda.h>  // CUtensorMap (types only; the encode function is fetched from the driver at run time)
+#include "common.cuh"
+
+namespace b200 {
+namespace tc {
+
+// A wait gives up after this many polls, sets the abort flag and lets the kernel unwind (free TMEM, return).
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// Codes written to the device error word (upper 16 bits: site, lower 16 bits: blockIdx.x).
+enum : uint32_t
+{
+	kErrProducerWait = 1,
+	kErrMmaWaitFull = 2,
+	kErrMmaWaitTmem = 3,
+	kErrEpilogueWait = 4,
+	kErrScanWait = 5
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+	asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+	asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+	asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+	uint32_t ok;
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+		"selp.b32 %0, 1, 0, p;\n\t}"
+		: "=r"(ok)
+		: "r"(bar), "r"(parity)
+		: "memory");
+	return ok != 0;
+}
+
+// Bounded wait. Returns false when it gave up (or another role already aborted); never spins forever.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+{
+	for (uint32_t i = 0; i < kSpinLimit; ++i)
+	{
+		if (mbar_try_wait(bar, parity)) return true;
+		if ((i & 255u) == 255u && *abort_flag) return false;
+	}
+	*abort_flag = 1;
+	return false;
+}
+
+__device__ __forceinline__ void report_timeout(uint32_t* err_word, uint32_t site)
+{
+	if (err_word) atomicCAS(err_word, 0u, (site << 16) | (blockIdx.x & 0xffffu));
+}
+
+// ---- TMA ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m)
+{
+	asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+// 2-D tiled load global -> shared, completion counted in bytes on `bar`. x = innermost coordinate (elements).
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+		::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y)
+		: "memory");
+}
+
+// ---- tensor memory -----------------------------------------------------------------------------------------
+// Whole-warp calls. ncols: power of two in [32, 512].
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
+{
+	asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+	asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// D[tmem] (+)= A[smem] . B[smem], f16 inputs, fp32 accumulate. One thread issues.
+__device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+	asm volatile(
+		"{\n\t.reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+		::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+// Arrives on `bar` when every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar)
+{
+	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread i of the warp = lane base + i).
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r)
+{
+	asm volatile(
+		"tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+		"{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+		"%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+		: "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+		  "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+		  "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+		  "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+		: "r"(taddr)
+		: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- descriptors -------------------------------------------------------------------------------------------
+// Instruction descriptor, kind::f16: D fp32, A/B f16, A K-major; B K-major (b_mn = 0) or MN-major (b_mn = 1).
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, int b_mn, int a_mn = 0)
+{
+	return (1u << 4)                                   // D format fp32
+		| (0u << 7) | (0u << 10)                       // A, B format f16
+		| (static_cast<uint32_t>(a_mn) << 15)          // A major
+		| (static_cast<uint32_t>(b_mn) << 16)          // B major
+		| (static_cast<uint32_t>(N >> 3) << 17)        // N / 8
+		| (static_cast<uint32_t>(M >> 4) << 24);       // M / 16
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled operand tile (tile base 1024-byte aligned).
+//   K-major : rows of 64 f16 (128 B); 8-row groups 1024 B apart  -> sbo = 1024, lbo unused (1).
+//   MN-major: k-rows of 64 f16 along MN (128 B); 8-k-row groups sbo bytes apart, 64-wide MN blocks lbo bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+	uint64_t d = 0;
+	d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+	d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+	d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+	d |= 1ull << 46;  // descriptor version for sm_100
+	d |= 2ull << 61;  // SWIZZLE_128B
+	return d;
+}
+
+}  // namespace tc
+
+// ---- host: tensor-map encoding through the driver entry point (no link-time libcuda dependency) ----------------
+// 2-D f16 tensor [rows, cols] with row stride ld (elements); box = box_cols x box_rows; 128-byte swizzle.
+int encode_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
+	uint32_t box_rows);
+
+}  // namespace b200

@@ -1,0 +1,326 @@
+"""Benchmark of the Mamba2-mixer prefill path (tokens/s) on N B200 GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+    python bench.py --impl reference ...      # the reference's CPU operators on the host cores
+
+A step is one forward pass of one mixer layer over one synthetic batch. Workload `cfg2` (default) is the
+Zamba2-1.2B-shaped layer (batch 4 x 2048 tokens, f16, fp32 scan state) per GPU; with N GPUs each rank runs its own
+batch shard (weak scaling, no data-path collective). `cfg4` is the Zamba2-7B-shaped layer with 4 sequences per GPU.
+One JSON line is printed by rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from anygpu_b200 import synth  # noqa: E402
+
+METRIC = "mamba2_mixer_prefill_tokens_per_s"
+UNIT = "tokens/s"
+STAGES = ["in_proj", "conv1d", "ssd", "gated_rmsnorm", "out_proj"]
+
+
+def workload(name):
+    cfg = dict(synth.CONFIGS[name])
+    if name == "cfg4":
+        cfg["batch"] = 4  # per GPU: 32 sequences over 8 GPUs
+        cfg["norm_group_size"] = cfg["d_inner"]  # the reference normalises the whole row
+    return cfg
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], tflops_burst=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"], source="measured")
+    return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.rows, self.proc, self.thread = gpu_index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.1 and len(r) >= 9] or [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = [float(r[1]) for r in rows]
+        reasons = set()
+        for r in rows:
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons), "samples": len(rows),
+                "power_w_max": max(float(r[3]) for r in rows)}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# reference arm: the reference's CPU operators on the host cores
+# ---------------------------------------------------------------------------------------------------------------
+
+def _ref_mixer_tokens(u, w, cfg):
+    """One mixer forward over u [1, l, d_model] with the reference's own CPU operators where it has them (linear,
+    causal conv1d, gated RMSNorm: compiled from its sources) and the oracle's restatement of its Python SSD script."""
+    from oracle import oracle as orc
+    use_ref = orc.ref_lib() is not None
+    lin = orc.ref_linear if use_ref else (lambda a, b: orc.linear(a, b, fast=False))
+    conv = orc.ref_causal_conv1d if use_ref else orc.causal_conv1d
+    norm = (lambda x, z, nw, eps: orc.ref_gated_rmsnorm(x, z, nw, eps)) if use_ref else orc.gated_rmsnorm
+    b, l, _ = u.shape
+    d_inner, H, P, G, N = cfg["d_inner"], cfg["nheads"], cfg["headdim"], cfg["ngroups"], cfg["d_state"]
+    conv_dim, d_in_proj = synth.dims(cfg)
+    zx = lin(u.reshape(b * l, -1), w["in_proj_weight"]).reshape(b, l, d_in_proj)
+    xbc = conv(np.ascontiguousarray(zx[..., d_inner:d_inner + conv_dim].transpose(0, 2, 1)), w["conv1d_weight"], w["conv1d_bias"])
+    xbc = np.ascontiguousarray(xbc.transpose(0, 2, 1))
+    y, _ = orc.ssd_chunk_scan(xbc[..., :d_inner].reshape(b, l, H, P), np.ascontiguousarray(zx[..., d_inner + conv_dim:]),
+                              -np.exp(w["A_log"]), xbc[..., d_inner:d_inner + G * N].reshape(b, l, G, N),
+                              xbc[..., d_inner + G * N:].reshape(b, l, G, N), cfg["chunk"], D=w["D"], dt_bias=w["dt_bias"])
+    g = norm(y.reshape(b * l, d_inner), np.ascontiguousarray(zx[..., :d_inner]).reshape(b * l, d_inner), w["norm_weight"], cfg["eps"])
+    return lin(g, w["out_proj_weight"]).reshape(b, l, -1), ("reference" if use_ref else "port")
+
+
+_W = {}
+
+
+def _worker_step(args):
+    name, tokens, seed = args
+    cfg = workload(name)
+    if name not in _W:
+        _W[name] = synth.make_weights(cfg, 0)
+    u = synth.make_input(cfg, seed, batch=1, seqlen=tokens)
+    t0 = time.perf_counter()
+    _, kind = _ref_mixer_tokens(u, _W[name], cfg)
+    return time.perf_counter() - t0, kind
+
+
+def cpu_reference_throughput(name, tokens_per_worker, workers, steps, warmup):
+    """tokens/s of the reference CPU path: `workers` processes (the reference is single-threaded) each push
+    `tokens_per_worker` tokens of one sequence through the mixer per step."""
+    import multiprocessing as mp
+    ctx = mp.get_context("fork")
+    kind = "port"
+    with ctx.Pool(workers) as pool:
+        for i in range(warmup):
+            pool.map(_worker_step, [(name, tokens_per_worker, 100 + i * workers + k) for k in range(workers)])
+        t0 = time.perf_counter()
+        for i in range(steps):
+            res = pool.map(_worker_step, [(name, tokens_per_worker, 1000 + i * workers + k) for k in range(workers)])
+            kind = res[0][1]
+        dt = time.perf_counter() - t0
+    return workers * tokens_per_worker * steps / dt, dt / steps, kind
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cfg = workload(args.workload)
+    workers = os.cpu_count() or 1
+    tokens = 16
+    value, sec_per_step, kind = cpu_reference_throughput(args.workload, tokens, workers, args.steps, args.warmup)
+    sample = (f"{workers} single-threaded processes x {tokens} tokens of one sequence per step (reference CPU linear / conv1d / "
+              f"gated RMSNorm compiled from its sources + CPU restatement of its Python SSD script)")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": _config_dict(args.workload, cfg, args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": workers, "kind": kind, "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def _config_dict(name, cfg, n):
+    return {"workload": f"{name}: Mamba2 mixer prefill, batch {cfg['batch']} x seqlen {cfg['seqlen']} per GPU, d_model {cfg['d_model']}, "
+                        f"d_inner {cfg['d_inner']}, {cfg['nheads']} heads x {cfg['headdim']}, d_state {cfg['d_state']}, ngroups {cfg['ngroups']}, "
+                        f"chunk {cfg['chunk']}, f16 weights/activations, fp32 scan state",
+            "global_batch": cfg["batch"] * n, "seq_len": cfg["seqlen"], "parallelism": f"batch-sharded x{n} (replicated weights, no collective)",
+            "l2": "inputs rotate over 4 buffers; per-step working set (~0.45 GB at cfg2) exceeds the 126 MB L2"}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------------
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from anygpu_b200 import capi, ops
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = capi.load()
+
+    cfg = workload(args.workload)
+    b, l = cfg["batch"], cfg["seqlen"]
+    tokens = b * l
+    w_np = synth.make_weights(cfg, 0)
+    weights = ops.ZambaMamba2weights.from_numpy(w_np, torch.float16)
+    mixer = ops.Mamba2Mixer(cfg, weights)
+    nbuf = 4
+    us = [torch.from_numpy(synth.make_input(cfg, 10 * rank + i)).to("cuda", torch.float16) for i in range(nbuf)]
+    out = torch.empty_like(us[0])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident timing (the headline `value`) -------------------------------------------------------
+    for i in range(args.warmup):
+        mixer.prefill(us[i % nbuf], out=out)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    lib.b200_stage_timing_enable(1)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t_wall0 = time.time()
+    ev0.record()
+    for i in range(args.steps):
+        mixer.prefill(us[i % nbuf], out=out)
+    ev1.record()
+    barrier()
+    t_wall1 = time.time()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    stage_ms = (ctypes.c_float * 5)()
+    calls = ctypes.c_int(0)
+    capi.check("b200_stage_timing_collect", lib.b200_stage_timing_collect(stage_ms, ctypes.byref(calls)))
+    lib.b200_stage_timing_enable(0)
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    dev_err = lib.b200_last_device_error(None, None)
+    if dev_err != 0:
+        raise SystemExit(f"device-side wait timed out during the benchmark (status {dev_err})")
+    ms_per_step = ms_total / args.steps
+    value = world * tokens * args.steps / (ms_total * 1e-3)
+
+    # ---- end to end through the host-buffer entry point --------------------------------------------------------
+    u_pin = [torch.from_numpy(synth.make_input(cfg, 10 * rank + i)).half().pin_memory() for i in range(2)]
+    out_pin = torch.empty_like(u_pin[0]).pin_memory()
+    for i in range(max(1, min(args.warmup, 3))):
+        mixer.prefill_host(u_pin[i % 2], out_pin)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        mixer.prefill_host(u_pin[i % 2], out_pin)
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1))
+    io_bytes = u_pin[0].numel() * 2
+    e2e_value = world * tokens * args.steps / (e2e_ms * 1e-3)
+    checksum = float(out_pin.float().abs().mean())
+    if not np.isfinite(checksum) or checksum == 0.0:
+        raise SystemExit("mixer output is not finite / all zero")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel (in_proj GEMM), live stage times from the timed region --------------------
+    peaks = measured_peaks()
+    conv_dim, d_in_proj = synth.dims(cfg)
+    per_stage = [stage_ms[j] / max(calls.value, 1) for j in range(5)]
+    flops_in = 2.0 * tokens * cfg["d_model"] * d_in_proj
+    dom = int(np.argmax(per_stage))
+    roofline = {"kernel": "gemm_f16_tcgen05_kernel (in_proj)", "bound": "tensor",
+                "achieved": flops_in / (per_stage[0] * 1e-3) / 1e12 if per_stage[0] > 0 else None,
+                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "traffic": None,
+                "peak_source": f"{peaks['source']} cuBLAS bf16, sustained (kernel timed inside a long step)",
+                "algorithmic_flops_per_launch": flops_in, "avg_launch_ms": per_stage[0],
+                "stage_ms": dict(zip(STAGES, per_stage)), "dominant_stage": STAGES[dom]}
+    roofline["frac"] = roofline["achieved"] / roofline["peak"] if roofline["achieved"] else None
+    G, N, H, P, Q = cfg["ngroups"], cfg["d_state"], cfg["nheads"], cfg["headdim"], cfg["chunk"]
+    nchunks = -(-l // Q)
+    flops_total = flops_in + 2.0 * tokens * cfg["d_inner"] * cfg["d_model"] + b * nchunks * (H * (2 * Q * Q * P + 4 * Q * N * P) + G * 2 * Q * Q * N)
+    whole = {"algorithmic_flops_per_step": flops_total, "achieved_tflops": flops_total / (ms_per_step * 1e-3) / 1e12,
+             "frac_of_sustained_peak": flops_total / (ms_per_step * 1e-3) / 1e12 / peaks["tflops_sustained"]}
+
+    # ---- CPU baseline: bounded sample on the host cores ----------------------------------------------------------
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        t0 = time.perf_counter()
+        cpu_tokens = 32
+        _, kind = _ref_mixer_tokens(synth.make_input(cfg, 99, batch=1, seqlen=cpu_tokens), w_np, cfg)
+        dt = time.perf_counter() - t0
+        cpu = {"value": cpu_tokens / dt, "unit": UNIT, "cores": 1, "kind": kind,
+               "sample": f"{cpu_tokens} tokens of one sequence through the whole mixer, single thread (the reference is single-threaded), {dt:.1f} s"}
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": _config_dict(args.workload, cfg, world), "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
+                    "ms_per_step": e2e_ms / args.steps},
+            "gpu_launches": 8 * args.steps, "roofline": roofline, "whole_step": whole, "cpu_baseline": cpu}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,201 @@
+/*
+ * b200_mamba2.h - C ABI of the B200 (sm_100a) Mamba2-mixer forward path.
+ *
+ * This is the boundary a host program binds against when it replaces anyGPU's operators for the
+ * Mamba2 mixer of its Zamba2 blocks. anyGPU has no FFI: its boundary is the set of C++ host launchers
+ * `cu_<op>_<dtype>(const Tensor<..,CUDA>&, ..., Tensor<..,CUDA>& out)` declared in srcs/kernels/cuda/*.cuh
+ * and called by the `tensor_<op>` templates in srcs/ops, srcs/fused and srcs/models/zamba2. Each entry
+ * point below names the launcher / template it stands in for. The C++ header layer under
+ * include/anygpu/ re-creates the `tensor_<op>` templates on top of this ABI.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer unless its name ends in `_host`;
+ *  - tensors are row-major; `*_stride` arguments are element strides between consecutive rows (tokens)
+ *    so that slices of a wider buffer (z | xBC | dt inside the in_proj output) are consumed in place;
+ *  - `dtype` selects the storage type of activations and weights (B200_F16 or B200_F32); the scan
+ *    parameters A / A_log, D, dt_bias, the SSM state and all statistics are always fp32;
+ *  - `stream` is a cudaStream_t passed as void*; all work is stream-ordered and nothing synchronises;
+ *  - no entry point allocates device memory: scratch comes from the caller's `workspace`
+ *    (size from the matching *_workspace_bytes query), 256-byte aligned;
+ *  - the return value is 0 on success or a negative b200_status; nothing calls exit().
+ *  - f16 rows must start on 16-byte boundaries (row strides multiples of 8 elements) for the vectorised
+ *    kernels; shapes that break this take a scalar kernel where one exists or return B200_ERR_MISALIGNED.
+ */
+#ifndef B200_MAMBA2_H
+#define B200_MAMBA2_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum b200_status
+{
+	B200_OK = 0,
+	B200_ERR_BAD_SHAPE = -1,      /* a dimension is zero/negative or inconsistent with another */
+	B200_ERR_MISALIGNED = -2,     /* pointer or stride alignment required by the kernel is not met */
+	B200_ERR_WORKSPACE = -3,      /* workspace null or smaller than *_workspace_bytes reports */
+	B200_ERR_DEVICE_TIMEOUT = -4, /* a bounded device-side wait gave up (reported by b200_last_device_error) */
+	B200_ERR_CUDA = -5,           /* a CUDA runtime / driver call failed; see b200_last_cuda_error() */
+	B200_ERR_UNSUPPORTED = -6,    /* dtype / size combination that no kernel covers */
+	B200_ERR_NULL = -7            /* a required pointer is null */
+} b200_status;
+
+typedef enum b200_dtype
+{
+	B200_F16 = 0,
+	B200_F32 = 1
+} b200_dtype;
+
+/* Layout of a projection weight handed to b200_linear. */
+typedef enum b200_weight_layout
+{
+	B200_W_KN = 0, /* (in_features, out_features) row-major: what anyGPU's tensor_linear takes (srcs/ops/mm_ops.hpp:206-232) */
+	B200_W_NK = 1  /* (out_features, in_features) row-major: the torch / checkpoint layout before anyGPU's load-time transpose
+	                  (srcs/models/zamba2/zamba_mlp.hpp:26-29) */
+} b200_weight_layout;
+
+const char* b200_status_string(int status);
+/* Last cudaError_t (as int) recorded by a failing call on this host thread, 0 if none. */
+int b200_last_cuda_error(void);
+/* ABI version; bumped when a signature changes. */
+int b200_abi_version(void);
+/* Reads (and clears) the device-side error word that bounded waits set. Synchronises `stream`.
+ * Returns B200_OK or B200_ERR_DEVICE_TIMEOUT; *detail (optional) receives the raw word. */
+int b200_last_device_error(void* stream, uint32_t* detail);
+
+/* ---- Y[M,N] = X[M,K] . W ------------------------------------------------------------------------------
+ * Replaces opt2::cu_tensor_mm_f16 (srcs/kernels/cuda/mm_ops.cu:231-350) and cu_tensor_mm_f32_opt0
+ * (mm_ops.cu:7-51) behind tensor_mm / tensor_linear (srcs/ops/mm_ops.hpp:48-71,206-232).
+ * f16: tcgen05 tensor-core kernel, fp32 accumulation, K % 8 == 0, N % 8 == 0, ldx % 8 == 0, ldy % 8 == 0.
+ * f32: exact fp32 SIMT kernel (any shape).  ldx / ldy: row strides of X and Y in elements. */
+int b200_linear(int dtype, const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy,
+	int64_t M, int64_t K, int64_t N, void* stream);
+
+/* ---- causal conv1d + SiLU, (batch, dims, seq_len) layout ---------------------------------------------------
+ * Replaces cu_tensor_causal_conv1d_f32 (srcs/kernels/cuda/causal_conv1d.cu:78-101) behind
+ * tensor_causal_conv1d (srcs/fused/causal_conv1d.hpp:90-117). y[b,d,s] = silu(bias[d] + sum_k w[d,k] x[b,d,s+k-(W-1)]),
+ * zero left padding, fp32 accumulation. width in [1,4]. w is (dims, width), bias (dims). */
+int b200_causal_conv1d(int dtype, const void* x, const void* w, const void* bias, void* y,
+	int64_t batch, int64_t dims, int64_t seqlen, int width, void* stream);
+
+/* Same operator on token-major data: x is [batch, seqlen, dims] with row stride x_stride (so the xBC slice of
+ * the in_proj output is read in place, without anyGPU's tensor_slice + tensor_transp round trip,
+ * srcs/ops/shape_ops.hpp:190-254, srcs/ops/transp_ops.hpp:81-134). y likewise with y_stride.
+ * initial_state (optional) is [batch, dims, width-1] holding the inputs that precede the sequence (oldest first);
+ * final_state (optional) receives the last width-1 inputs in the same layout (the decode conv_state). */
+int b200_causal_conv1d_tokens(int dtype, const void* x, int64_t x_stride, const void* w, const void* bias,
+	void* y, int64_t y_stride, const void* initial_state, void* final_state,
+	int64_t batch, int64_t seqlen, int64_t dims, int width, void* stream);
+
+/* One decode step: conv_state [batch, dims, width-1] (oldest first) is read, the output for token x_t
+ * [batch, dims] (row stride x_stride) is written to y_t (row stride y_stride), and the state is advanced in place.
+ * No counterpart in anyGPU (its backlog lists the mamba layer as open, docs/TODO_backlog.md:3-25);
+ * defined so that step t reproduces column t of tensor_causal_conv1d on the concatenated history. */
+int b200_causal_conv1d_update(int dtype, const void* x_t, int64_t x_stride, void* conv_state, const void* w,
+	const void* bias, void* y_t, int64_t y_stride, int64_t batch, int64_t dims, int width, void* stream);
+
+/* ---- gated RMSNorm ------------------------------------------------------------------------------------------
+ * Replaces the three launches of tensor_zamba_gated_rmsnorm (srcs/models/zamba2/zamba_gated_rmsnorm.hpp:9-23):
+ * cu_tensor_silu_f32 (srcs/kernels/cuda/math_ops.cu:3-34), cu_tensor_mul_f32 (binary_ops.cu:112-124),
+ * cu_tensor_rms_norm_f32_v1 (norm_rms_f32_v1.cu:94-119) by one pass:
+ * g = x * silu(z); y = g * rsqrt(mean_group(g^2) + eps) * w.  group_size must divide d; group_size == d is
+ * anyGPU's behaviour (it ignores its gsize argument). */
+int b200_gated_rmsnorm(int dtype, const void* x, int64_t x_stride, const void* z, int64_t z_stride, const void* w,
+	void* y, int64_t y_stride, int64_t rows, int64_t d, int64_t group_size, float eps, void* stream);
+
+/* ---- SSD chunked selective scan (prefill) -------------------------------------------------------------------
+ * CUDA counterpart of mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:167-215), which anyGPU
+ * has only as a PyTorch script. Argument meaning follows that function:
+ *   x [b,l,H,P] (token stride x_stride), dt [b,l,H] (dt_stride), A [H] fp32 (or A_log when a_is_log != 0: A = -exp(A_log)),
+ *   B, C [b,l,G,N] (B_stride, C_stride), D [H] fp32 or null, dt_bias [H] fp32 or null,
+ *   initial_states [b,H,P,N] fp32 or null  ->  y [b,l,H,P] (y_stride), final_states [b,H,P,N] fp32 (or null).
+ * chunk <= 256. seqlen need not be a multiple of chunk (y is exact; final_states then follows the script's
+ * pad-before-softplus behaviour). */
+size_t b200_mamba_chunk_scan_combined_workspace_bytes(int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G,
+	int64_t N, int64_t chunk);
+int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
+	const float* D, const float* dt_bias, const float* initial_states,
+	void* y, int64_t y_stride, float* final_states,
+	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
+	void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- single-token state recurrence (decode) -----------------------------------------------------------------
+ * dt = softplus(dt_raw + dt_bias); h <- exp(dt A) h + dt x (x) B; y = h.C + D x, per (batch, head).
+ * ssm_state [b,H,P,N] fp32 is updated in place. No counterpart in anyGPU; equals one step of the per-token form of
+ * mamba_chunk_scan_combined_ref with initial_states (scripts/zamba2/mamba_chunk_scan_comb.py:93-95,196-210).
+ * x [b,H,P] (row stride x_stride), dt [b,H], B, C [b,G,N], y [b,H,P]. */
+int b200_selective_state_update(int dtype, float* ssm_state, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
+	const float* D, const float* dt_bias, void* y, int64_t y_stride,
+	int64_t batch, int64_t H, int64_t P, int64_t G, int64_t N, int dt_softplus, void* stream);
+
+/* ---- the mixer ----------------------------------------------------------------------------------------------
+ * The block anyGPU was building towards (docs/TODO_backlog.md:3-25), composed as
+ *   zxbcdt = in_proj(u) ; z | xBC | dt ; xBC = silu(conv1d(xBC)) ; x | B | C ; y = SSD(...) ;
+ *   g = gated_rmsnorm(y, z) ; out = out_proj(g)
+ * in the style of its other Zamba2 blocks (weights struct + cache + config, srcs/models/zamba2/zamba_attn_decoder.hpp:68-118). */
+typedef struct b200_mamba2_config
+{
+	int64_t d_model, d_inner, nheads, headdim, d_state, ngroups, d_conv, chunk;
+	int64_t norm_group_size; /* 0 = whole row (anyGPU's gated RMSNorm behaviour) */
+	float eps;
+} b200_mamba2_config;
+
+typedef struct b200_mamba2_weights
+{
+	const void* in_proj_weight;  /* dtype, layout in_proj_layout: [d_model, d_in_proj] (KN) or [d_in_proj, d_model] (NK) */
+	const void* conv1d_weight;   /* dtype [conv_dim, d_conv] */
+	const void* conv1d_bias;     /* dtype [conv_dim] */
+	const float* dt_bias;        /* fp32 [nheads] */
+	const float* A_log;          /* fp32 [nheads] */
+	const float* D;              /* fp32 [nheads] */
+	const void* norm_weight;     /* dtype [d_inner] */
+	const void* out_proj_weight; /* dtype, layout out_proj_layout */
+	int in_proj_layout, out_proj_layout; /* b200_weight_layout */
+} b200_mamba2_weights;
+
+size_t b200_mamba2_mixer_prefill_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen);
+/* u [batch, seqlen, d_model] -> out [batch, seqlen, d_model]. initial_states / ssm_state_out [b,H,P,N] fp32 and
+ * conv_state_out [b, conv_dim, d_conv-1] (dtype) are optional (null to skip). */
+int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, int64_t batch, int64_t seqlen,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream);
+/* Same call for callers holding HOST tensors (anyGPU's Tensor<dtype,CPU>::copy_to_cuda / copy_to_host pattern,
+ * srcs/core/tensor.hpp:318-370): copies u_host in, runs the mixer, copies out_host back, all on `stream`.
+ * The workspace must be b200_mamba2_mixer_prefill_host_workspace_bytes large (it also holds the staging tensors). */
+size_t b200_mamba2_mixer_prefill_host_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen);
+int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
+	void* workspace, size_t workspace_bytes, void* stream);
+
+size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch);
+/* One token per sequence: u_t [batch, d_model] -> out_t [batch, d_model]; conv_state [b, conv_dim, d_conv-1] (dtype) and
+ * ssm_state [b,H,P,N] fp32 are advanced in place. */
+int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
+	void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- per-stage timing of b200_mamba2_mixer_prefill -----------------------------------------------------------
+ * No counterpart in anyGPU (its workflow is an external Nsight Compute CSV, scripts/perf_reports/plot_gemma_decoder.py:23-26).
+ * When enabled, the prefill mixer records CUDA events on the caller's stream between its five stages
+ * (in_proj, conv1d, ssd, gated_rmsnorm, out_proj) for up to 256 calls. b200_stage_timing_collect waits for the recorded
+ * calls, writes the SUM of each stage's milliseconds over those calls to stage_ms[5] and their number to *calls, and
+ * starts a new window. Not thread safe; meant for a benchmark harness. */
+int b200_stage_timing_enable(int enable);
+int b200_stage_timing_collect(float* stage_ms, int* calls);
+
+#ifdef __cplusplus
+}
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#endif /* B200_MAMBA2_H */

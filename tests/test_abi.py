@@ -1,0 +1,72 @@
+"""CPU-side checks of the C-ABI boundary: the library loads, exports every symbol the header declares, and rejects
+bad arguments with status codes before touching the GPU (no compute is launched here)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from anygpu_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "b200_mamba2.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_list_the_same_functions():
+    assert declared_functions() == sorted(capi.SIGNATURES)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = capi.load()
+    for name in declared_functions():
+        assert hasattr(lib, name), name
+    assert lib.b200_abi_version() == 1
+    assert lib.b200_status_string(0) == b"ok"
+    assert lib.b200_status_string(-4) == b"device-side wait timed out"
+
+
+def test_null_and_shape_validation_needs_no_gpu():
+    lib = capi.load()
+    one = ctypes.c_void_p(256)  # never dereferenced: validation fails first
+    assert lib.b200_linear(capi.F16, None, 8, one, 0, one, 8, 1, 8, 8, None) == -7
+    assert lib.b200_linear(capi.F16, one, 8, one, 0, one, 8, 1, 0, 8, None) == -1
+    assert lib.b200_linear(capi.F16, one, 4, one, 0, one, 8, 1, 8, 8, None) == -1  # ldx < K
+    assert lib.b200_linear(capi.F16, one, 8, one, 7, one, 8, 1, 8, 8, None) == -6  # unknown weight layout
+    assert lib.b200_linear(capi.F16, one, 12, one, 0, one, 8, 4, 12, 8, None) == -2  # K % 8 != 0 for the f16 kernel
+    assert lib.b200_causal_conv1d(capi.F16, one, one, one, one, 1, 8, 8, 5, None) == -1  # width > 4
+    assert lib.b200_causal_conv1d(capi.F16, one, None, one, one, 1, 8, 8, 4, None) == -7
+    assert lib.b200_causal_conv1d(7, one, one, one, one, 1, 8, 8, 4, None) == -6
+    assert lib.b200_causal_conv1d(capi.F16, one, one, one, one, 0, 8, 8, 4, None) == 0  # empty batch is a no-op
+    assert lib.b200_causal_conv1d_tokens(capi.F16, one, 4, one, one, one, 8, None, None, 1, 8, 8, 4, None) == -1  # stride < dims
+    assert lib.b200_causal_conv1d_update(capi.F16, one, 8, None, one, one, one, 8, 1, 8, 4, None) == -7
+    assert lib.b200_gated_rmsnorm(capi.F16, one, 8, one, 8, one, one, 8, 1, 8, 3, 1e-5, None) == -1  # group does not divide d
+    assert lib.b200_gated_rmsnorm(capi.F16, one, 8, one, 8, one, one, 8, 0, 8, 8, 1e-5, None) == 0
+    args = [capi.F16, one, 64, one, 8, one, 0, one, 16, one, 16, None, None, None, one, 64, None]
+    assert lib.b200_mamba_chunk_scan_combined(*args, 1, 32, 8, 8, 1, 16, 512, 1, one, 1 << 20, None) == -6  # chunk > 256
+    assert lib.b200_mamba_chunk_scan_combined(*args, 1, 32, 8, 8, 3, 16, 32, 1, one, 1 << 20, None) == -1  # H % G != 0
+    assert lib.b200_mamba_chunk_scan_combined(*args, 1, 32, 8, 8, 1, 16, 32, 1, None, 0, None) == -3  # no workspace
+    assert lib.b200_mamba_chunk_scan_combined(*args, 1, 32, 8, 8, 1, 16, 32, 1, one, 16, None) == -3  # workspace too small
+    assert lib.b200_selective_state_update(capi.F16, None, one, 64, one, 8, one, 0, one, 16, one, 16, None, None, one, 64,
+                                           1, 8, 8, 1, 16, 1, None) == -7
+
+
+def test_workspace_queries():
+    lib = capi.load()
+    n = lib.b200_mamba_chunk_scan_combined_workspace_bytes(4, 2048, 64, 64, 1, 64, 256)
+    assert n == 2 * 4 * 64 * 2048 * 4 + 4 * 8 * 64 * 64 * 64 * 4
+    cfg = capi.Mamba2Config(2048, 4096, 64, 64, 64, 1, 4, 256, 0, 1e-5)
+    T = 4 * 2048
+    want = T * 8384 * 2 + T * 4224 * 2 + T * 4096 * 2 + n
+    assert lib.b200_mamba2_mixer_prefill_workspace_bytes(ctypes.byref(cfg), capi.F16, 4, 2048) == want
+    assert lib.b200_mamba2_mixer_prefill_host_workspace_bytes(ctypes.byref(cfg), capi.F16, 4, 2048) == want + 2 * T * 2048 * 2
+    bad = capi.Mamba2Config(2048, 4096, 63, 64, 64, 1, 4, 256, 0, 1e-5)  # nheads * headdim != d_inner
+    assert lib.b200_mamba2_mixer_prefill_workspace_bytes(ctypes.byref(bad), capi.F16, 4, 2048) == 0
+    w = capi.Mamba2Weights()
+    assert lib.b200_mamba2_mixer_prefill(capi.F16, ctypes.byref(cfg), ctypes.byref(w), ctypes.c_void_p(256), ctypes.c_void_p(256),
+                                         1, 8, None, None, None, None, 0, None) == -7  # null weights
+    assert lib.b200_mamba2_mixer_decode_workspace_bytes(ctypes.byref(cfg), capi.F16, 64) > 0
