@@ -8,97 +8,9 @@
 // and K come from TMA zero fill and predicated stores. Every mbarrier wait is bounded.
 //
 // f32: exact fp32 SIMT kernel (64x64 tiles through shared memory), for Tensor<float32> callers.
-#include <mutex>
-#include <unordered_map>
-#include <cstring>
-
 #include "tcgen05.cuh"
 
 namespace b200 {
-
-// ---- tensor-map encoding ---------------------------------------------------------------------------------
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-	const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-	CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn()
-{
-	static EncodeTiledFn fn = []() -> EncodeTiledFn {
-		void* p = nullptr;
-		cudaDriverEntryPointQueryResult q;
-		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
-		if (q != cudaDriverEntryPointSuccess) return nullptr;
-		return reinterpret_cast<EncodeTiledFn>(p);
-	}();
-	return fn;
-}
-
-int encode_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
-	uint32_t box_rows)
-{
-	EncodeTiledFn fn = get_encode_fn();
-	if (!fn) return B200_ERR_CUDA;
-	const cuuint64_t dims[2] = { cols, rows };
-	const cuuint64_t strides[1] = { ld_elems * sizeof(__half) };
-	const cuuint32_t box[2] = { box_cols, box_rows };
-	const cuuint32_t estr[2] = { 1, 1 };
-	const CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-		CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-		CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-	if (r != CUDA_SUCCESS)
-	{
-		g_last_cuda_error = static_cast<int>(r);
-		return B200_ERR_CUDA;
-	}
-	return B200_OK;
-}
-
-// Encoding a map costs a few microseconds of host time; the mixer re-issues the same few (pointer, shape) pairs
-// every step, so keep the most recent ones.
-struct TmapKey
-{
-	const void* base;
-	uint64_t rows, cols, ld;
-	uint32_t bc, br;
-	bool operator==(const TmapKey& o) const
-	{
-		return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && bc == o.bc && br == o.br;
-	}
-};
-struct TmapKeyHash
-{
-	size_t operator()(const TmapKey& k) const
-	{
-		size_t h = reinterpret_cast<size_t>(k.base);
-		h ^= k.rows * 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
-		h ^= k.cols * 0xc2b2ae3d27d4eb4full + (h << 6) + (h >> 2);
-		h ^= (k.ld + k.bc * 131 + k.br * 7) * 0x165667b19e3779f9ull + (h << 6) + (h >> 2);
-		return h;
-	}
-};
-
-static int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t bc, uint32_t br)
-{
-	static std::mutex mu;
-	static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
-	const TmapKey key{ base, rows, cols, ld, bc, br };
-	{
-		std::lock_guard<std::mutex> lk(mu);
-		auto it = cache.find(key);
-		if (it != cache.end())
-		{
-			std::memcpy(out, &it->second, sizeof(CUtensorMap));
-			return B200_OK;
-		}
-	}
-	const int rc = encode_tmap_2d_f16(out, base, rows, cols, ld, bc, br);
-	if (rc) return rc;
-	std::lock_guard<std::mutex> lk(mu);
-	if (cache.size() > 256) cache.clear();
-	cache.emplace(key, *out);
-	return B200_OK;
-}
 
 // ---- f16 tcgen05 kernel -----------------------------------------------------------------------------------
 
@@ -313,12 +225,12 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 		return B200_ERR_MISALIGNED;
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 	CUtensorMap tmA, tmB;
-	int rc = cached_tmap(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
+	int rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
 	if (rc) return rc;
 	if (w_layout == B200_W_NK)
-		rc = cached_tmap(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, BN);
+		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, BN);
 	else
-		rc = cached_tmap(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
+		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
 	if (rc) return rc;
 	const int m_tiles = static_cast<int>(cdiv(M, BM)), n_tiles = static_cast<int>(cdiv(N, BN));
 	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;

@@ -12,10 +12,27 @@ static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, cons
 	if (rc) return rc;
 	rc = ssd_chunk_state_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, d, w, st);
 	if (rc) return rc;
-	rc = ssd_state_passing(init, fin, d, w, st);
+	rc = ssd_state_passing(init, fin, false, d, w, st);
 	if (rc) return rc;
 	return ssd_chunk_scan_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, static_cast<const T*>(Cm), cs, D,
 		static_cast<T*>(y), ys, d, w, st);
+}
+
+// f16 activations on the tensor cores: the two contractions run as tcgen05 kernels.
+static int run_tc(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
+	const void* Cm, int64_t cs, const float* D, const float* dt_bias, const float* init, void* y, int64_t ys, float* fin,
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	const __half* xh = static_cast<const __half*>(x);
+	const __half* bh = static_cast<const __half*>(Bm);
+	const __half* ch = static_cast<const __half*>(Cm);
+	int rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, 1, d, w, st);
+	if (rc) return rc;
+	rc = ssd_chunk_state_tc(xh, xs, bh, bs, d, w, st);
+	if (rc) return rc;
+	rc = ssd_state_passing(init, fin, true, d, w, st);
+	if (rc) return rc;
+	return ssd_chunk_scan_tc(xh, xs, bh, bs, ch, cs, D, static_cast<__half*>(y), ys, d, w, st);
 }
 
 }  // namespace b200
@@ -53,6 +70,9 @@ extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t 
 	const SsdWorkspace w = ssd_carve(workspace, d);
 	if (workspace_bytes < w.bytes) return B200_ERR_WORKSPACE;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	if (dtype == B200_F16 && ssd_tc_supported(d, x, x_stride, B, B_stride, C, C_stride, y, y_stride))
+		return run_tc(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y, y_stride,
+			final_states, d, w, st);
 	if (dtype == B200_F16)
 		return run_simt<__half>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
 			y_stride, final_states, d, w, st);

@@ -5,7 +5,9 @@
 //   2. chunk state     : states[b,c,h,p,n] = sum_l B[l,n] exp(dAcs[last]-dAcs[l]) dt[l] x[l,p]      (:51-80)
 //   3. state passing   : running state across chunks; states[c] is replaced by the state BEFORE c   (:83-106)
 //   4. chunk scan      : y = (C.B^T o decay o causal).(dt x) + exp(dAcs) C.prev^T + D x            (:109-160)
-// Workspace layout (fp32): dt[b,H,nc,Q] | dAcs[b,H,nc,Q] | states[b,nc,H,P,N].
+// Workspace layout: dt[b,H,nc,Q] f32 | dAcs[b,H,nc,Q] f32 | states[b,nc,H,P,N] f32 | prev16[b,nc,H,P,N] f16
+// (prev16: the state before each chunk rounded to f16, the tensor-core operand of stage 4; the reference rounds the
+// passed states to the activation dtype as well, scripts/zamba2/mamba_chunk_scan_comb.py:211).
 #pragma once
 #include "common.cuh"
 
@@ -22,6 +24,7 @@ struct SsdWorkspace
 	float* dt;
 	float* dacs;
 	float* states;
+	__half* prev16;
 	size_t bytes;
 };
 
@@ -36,7 +39,9 @@ inline SsdWorkspace ssd_carve(void* base, const SsdDims& d)
 	w.dt = reinterpret_cast<float*>(p);
 	w.dacs = reinterpret_cast<float*>(p + o1);
 	w.states = reinterpret_cast<float*>(p + o2);
-	w.bytes = o2 + align_up(n_st * sizeof(float), 256);
+	const size_t o3 = o2 + align_up(n_st * sizeof(float), 256);
+	w.prev16 = reinterpret_cast<__half*>(p + o3);
+	w.bytes = o3 + align_up(n_st * sizeof(__half), 256);
 	return w;
 }
 
@@ -48,7 +53,16 @@ int ssd_dt_cumsum(const T* dt, int64_t dts, const float* A, int a_is_log, const 
 template <typename T>
 int ssd_chunk_state_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
 
-int ssd_state_passing(const float* initial_states, float* final_states, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+// write_prev16: also store the f16 copy of the state before each chunk (needed by the tensor-core chunk scan).
+int ssd_state_passing(const float* initial_states, float* final_states, bool write_prev16, const SsdDims& d, const SsdWorkspace& w,
+	cudaStream_t st);
+
+// Tensor-core stages (f16 activations; shapes accepted by ssd_tc_supported).
+bool ssd_tc_supported(const SsdDims& d, const void* x, int64_t xs, const void* Bm, int64_t bs, const void* Cm, int64_t cs, const void* y,
+	int64_t ys);
+int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D, __half* y,
+	int64_t ys, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
 
 template <typename T>
 int ssd_chunk_scan_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const T* Cm, int64_t cs, const float* D, T* y, int64_t ys,

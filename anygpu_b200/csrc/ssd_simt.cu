@@ -167,8 +167,8 @@ template int ssd_chunk_state_simt<float>(const float*, int64_t, const float*, in
 // ---- stage 3: state passing across chunks --------------------------------------------------------------------
 // One thread per state element walks the chunks: states[c] <- state before chunk c; carries the running state in a
 // register. Bandwidth-bound (one read + one write of the chunk states), fully coalesced.
-__global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restrict__ states, const float* __restrict__ dacs,
-	const float* __restrict__ init, float* __restrict__ fin, int H, int PN, int Q, int nchunks)
+__global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restrict__ states, __half* __restrict__ prev16,
+	const float* __restrict__ dacs, const float* __restrict__ init, float* __restrict__ fin, int H, int PN, int Q, int nchunks)
 {
 	const int i = blockIdx.x * blockDim.x + threadIdx.x;
 	if (i >= PN) return;
@@ -180,18 +180,21 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restric
 		float* p = states + ((b * nchunks + c) * H + h) * static_cast<int64_t>(PN) + i;
 		const float cur = *p;
 		*p = s;
+		if (prev16) prev16[((b * nchunks + c) * H + h) * static_cast<int64_t>(PN) + i] = __float2half_rn(s);
 		const float dec = expf(dacs[((b * H + h) * nchunks + c) * static_cast<int64_t>(Q) + Q - 1]);
 		s = s * dec + cur;
 	}
 	if (fin) fin[(b * H + h) * static_cast<int64_t>(PN) + i] = s;
 }
 
-int ssd_state_passing(const float* initial_states, float* final_states, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+int ssd_state_passing(const float* initial_states, float* final_states, bool write_prev16, const SsdDims& d, const SsdWorkspace& w,
+	cudaStream_t st)
 {
 	const int PN = d.P * d.N;
 	const dim3 g(static_cast<unsigned>(cdiv(PN, 256)), static_cast<unsigned>(d.H), static_cast<unsigned>(d.batch));
 	if (g.z > 65535u || g.y > 65535u) return B200_ERR_UNSUPPORTED;
-	ssd_state_passing_kernel<<<g, 256, 0, st>>>(w.states, w.dacs, initial_states, final_states, d.H, PN, d.Q, d.nchunks);
+	ssd_state_passing_kernel<<<g, 256, 0, st>>>(w.states, write_prev16 ? w.prev16 : nullptr, w.dacs, initial_states, final_states, d.H,
+		PN, d.Q, d.nchunks);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }

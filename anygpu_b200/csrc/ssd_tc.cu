@@ -1,0 +1,624 @@
+// Tensor-core (tcgen05 / TMEM / TMA) stages of the SSD chunked scan for f16 activations.
+//
+// chunk state  : states[(h,p), n] = sum_l (x[l,h,p] * exp(dAcs[last]-dAcs[l]) * dt[l]) * B[l,n]
+//                one CTA per (batch, chunk, head pair): M = 2 heads x 64 p = 128, N = d_state, K = chunk.
+//                CUDA cores scale x into a 128B-swizzled MN-major A tile; B comes straight from TMA (MN-major).
+// chunk scan   : per (batch, chunk, group, 128-row block) one CTA computes CB = C.B^T ONCE into TMEM (it is shared by all
+//                heads of the group) and then streams the heads of the group through a warp-specialised pipeline:
+//                  compute warps : tcgen05.ld CB -> * exp(dAcs[l]-dAcs[s]) * dt[s], causal mask -> f16 -> swizzled smem (A operand)
+//                  MMA warp      : Y  += S_kblock . X_kblock   (X tiles by TMA, MN-major B operand)
+//                                  Z   = C . prev_state^T      (C tile reused from CB; prev state f16 by TMA)
+//                  compute warps : y = Y + exp(dAcs[l]) * Z + D * x  -> f16
+// The decay is always formed from the DIFFERENCE dAcs[l]-dAcs[s] <= 0 (never a ratio of exponentials).
+// Every mbarrier wait is bounded; on a timeout the CTA records a code, drains and frees its tensor memory.
+#include "ssd_common.cuh"
+#include "tcgen05.cuh"
+
+namespace b200 {
+
+using namespace tc;
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2_approx(float v)
+{
+	float r;
+	asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+	return r;
+}
+
+// =====================================================================================================================
+// chunk state
+// =====================================================================================================================
+namespace cstate {
+constexpr int THREADS = 128;
+constexpr int KB = 64;                      // l per K-block
+constexpr int A_KB_BYTES = KB * 128 * 2;    // [2 atoms][64 l][64 m] f16 = 16 KiB
+}  // namespace cstate
+
+template <int NSTATE>
+__global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(const __grid_constant__ CUtensorMap tmB,
+	const __half* __restrict__ x, int64_t xs, const float* __restrict__ dt, const float* __restrict__ dacs,
+	float* __restrict__ states, int64_t seqlen, int H, int G, int Q, int nchunks, uint32_t* err_word)
+{
+	using namespace cstate;
+	constexpr int KA = NSTATE / 64;              // 64-wide n atoms
+	constexpr int B_KB_BYTES = KA * KB * 128;    // per K-block: [KA atoms][64 l][64 n]
+	extern __shared__ uint8_t smem_raw[];
+	__shared__ uint64_t bar_in, bar_done;
+	__shared__ uint32_t tmem_slot;
+	__shared__ int abort_flag;
+
+	const int nkb = Q / KB;
+	const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+	const uint32_t a_s = base;
+	const uint32_t b_s = base + static_cast<uint32_t>(nkb) * A_KB_BYTES;
+	uint8_t* a_gen = smem_raw + (base - smem_u32(smem_raw));
+
+	const int warp = threadIdx.x >> 5;
+	const int hp = blockIdx.x % (H / 2);
+	const int64_t bc = blockIdx.x / (H / 2);
+	const int c = static_cast<int>(bc % nchunks);
+	const int64_t b = bc / nchunks;
+	const int h0 = hp * 2;
+	const int g = h0 / (H / G);
+	const int64_t tok0 = b * seqlen + static_cast<int64_t>(c) * Q;
+	const int valid = static_cast<int>(min(static_cast<int64_t>(Q), seqlen - static_cast<int64_t>(c) * Q));
+	volatile int* abortp = &abort_flag;
+
+	if (threadIdx.x == 0)
+	{
+		abort_flag = 0;
+		mbar_init(smem_u32(&bar_in), 1);
+		mbar_init(smem_u32(&bar_done), 1);
+		fence_mbar_init();
+	}
+	if (warp == 0)
+	{
+		tmem_alloc(smem_u32(&tmem_slot), NSTATE);
+		tmem_relinquish();
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_slot;
+
+	if (threadIdx.x == 0)
+	{
+		prefetch_tmap(&tmB);
+		mbar_arrive_expect_tx(smem_u32(&bar_in), static_cast<uint32_t>(nkb) * B_KB_BYTES);
+		for (int kb = 0; kb < nkb; ++kb)
+#pragma unroll
+			for (int a = 0; a < KA; ++a)
+				tma_load_3d(b_s + kb * B_KB_BYTES + a * (KB * 128), &tmB, smem_u32(&bar_in), g * NSTATE + a * 64, c * Q + kb * KB,
+					static_cast<int>(b));
+	}
+
+	// scaled x -> MN-major A tiles. 16 chunks of 8 m-values per l row (2 heads x 64 p).
+	{
+		const int64_t cb0 = ((b * H + h0) * nchunks + c) * static_cast<int64_t>(Q);
+		const int64_t cb1 = cb0 + static_cast<int64_t>(nchunks) * Q;
+		const float last0 = dacs[cb0 + Q - 1], last1 = dacs[cb1 + Q - 1];
+		const int chunk = threadIdx.x & 15;
+		const int j = chunk >> 3, cj = chunk & 7;  // atom (= head of the pair), 16-byte chunk inside the atom row
+		const int64_t cbh = j ? cb1 : cb0;
+		const float last = j ? last1 : last0;
+		for (int l = threadIdx.x >> 4; l < Q; l += THREADS / 16)
+		{
+			Half8 v;
+			if (l < valid)
+			{
+				const float sc = __expf(last - dacs[cbh + l]) * dt[cbh + l];
+				const Half8 in = *reinterpret_cast<const Half8*>(x + (tok0 + l) * xs + static_cast<int64_t>(h0) * 64 + chunk * 8);
+				float f[8];
+				unpack8(in, f);
+#pragma unroll
+				for (int e = 0; e < 8; ++e) f[e] *= sc;
+				v = pack8(f);
+			}
+			else
+			{
+#pragma unroll
+				for (int e = 0; e < 4; ++e) v.h[e] = __floats2half2_rn(0.f, 0.f);
+			}
+			const int kb = l >> 6, lk = l & 63;
+			const uint32_t off = static_cast<uint32_t>(kb) * A_KB_BYTES + static_cast<uint32_t>(j) * (KB * 128) +
+				static_cast<uint32_t>(lk) * 128 + (static_cast<uint32_t>(cj ^ (lk & 7)) << 4);
+			*reinterpret_cast<Half8*>(a_gen + off) = v;
+		}
+	}
+	fence_proxy_async_smem();
+	__syncthreads();
+
+	if (threadIdx.x == 0)
+	{
+		if (mbar_wait(smem_u32(&bar_in), 0, abortp))
+		{
+			tc_fence_after();
+			constexpr uint32_t idesc = make_idesc_f16(128, NSTATE, 1, 1);
+			for (int kb = 0; kb < nkb; ++kb)
+			{
+				const uint64_t a_desc = make_smem_desc_sw128(a_s + kb * A_KB_BYTES, KB * 128, 1024);
+				const uint64_t b_desc = make_smem_desc_sw128(b_s + kb * B_KB_BYTES, KB * 128, 1024);
+#pragma unroll
+				for (int k = 0; k < KB / 16; ++k)
+					mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 128), b_desc + static_cast<uint64_t>(k * 128), idesc,
+						(kb | k) != 0 ? 1u : 0u);
+			}
+			mma_commit(smem_u32(&bar_done));
+		}
+		else
+		{
+			report_timeout(err_word, kErrScanWait);
+		}
+	}
+	__syncwarp();
+	if (mbar_wait(smem_u32(&bar_done), 0, abortp))
+	{
+		tc_fence_after();
+		const int m = threadIdx.x;  // row of D: head h0 + m/64, p = m%64
+		float* out = states + ((((b * nchunks + c) * H + h0 + (m >> 6)) * 64) + (m & 63)) * static_cast<int64_t>(NSTATE);
+		const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll 1
+		for (int cc = 0; cc < NSTATE / 32; ++cc)
+		{
+			uint32_t r[32];
+			tmem_ld_32x32(t_row + static_cast<uint32_t>(cc * 32), r);
+			tmem_ld_wait();
+#pragma unroll
+			for (int v = 0; v < 8; ++v)
+				*reinterpret_cast<float4*>(out + cc * 32 + v * 4) = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+					__uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+		}
+	}
+	else if ((threadIdx.x & 31) == 0)
+	{
+		report_timeout(err_word, kErrScanWait);
+	}
+	if (*abortp)
+		for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 0)
+	{
+		tc_fence_after();
+		tmem_dealloc(tmem_base, NSTATE);
+	}
+}
+
+// =====================================================================================================================
+// chunk scan
+// =====================================================================================================================
+namespace cscan {
+constexpr int LB = 128;   // output rows (l) per CTA
+constexpr int KB = 64;    // s per K-block
+constexpr int NX = 4;     // X ring stages
+constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 compute
+constexpr int S_STAGE = LB * KB * 2;  // 16 KiB
+constexpr int X_STAGE = KB * 64 * 2;  // 8 KiB
+constexpr uint32_t TMEM_COLS = 512;   // CB [0,256) | Y0 Z0 [256,384) | Y1 Z1 [384,512)
+
+template <int NSTATE, int NS>
+struct Layout
+{
+	static constexpr int KA = NSTATE / 64;
+	static constexpr int C_BYTES = KA * LB * 128;      // [KA atoms][128 l][64 n]
+	static constexpr int B_BYTES = KA * 256 * 128;     // [KA atoms][256 s][64 n]
+	static constexpr int P_BYTES = KA * 64 * 128;      // [KA atoms][64 p][64 n]
+	static constexpr int OFF_C = 0;
+	static constexpr int OFF_B = OFF_C + C_BYTES;
+	static constexpr int OFF_S = OFF_B + B_BYTES;
+	static constexpr int OFF_X = OFF_S + NS * S_STAGE;
+	static constexpr int OFF_P = OFF_X + NX * X_STAGE;
+	static constexpr int TOTAL = OFF_P + 2 * P_BYTES + 1024;
+};
+}  // namespace cscan
+
+template <int NSTATE, int NS>
+__global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap tmX,
+	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
+	const __half* __restrict__ x, int64_t xs, __half* __restrict__ y, int64_t ys, const float* __restrict__ D,
+	const float* __restrict__ dt, const float* __restrict__ dacs, int64_t seqlen, int H, int G, int Q, int nchunks,
+	int heads_per_cta, uint32_t* err_word)
+{
+	using namespace cscan;
+	using L = Layout<NSTATE, NS>;
+	constexpr int KA = L::KA;
+	extern __shared__ uint8_t smem_raw[];
+	__shared__ uint64_t bar_in, bar_cb, s_full[NS], s_empty[NS], x_full[NX], x_empty[NX], p_full[2], p_empty[2], acc_full[2],
+		acc_empty[2];
+	__shared__ uint32_t tmem_slot;
+	__shared__ int abort_flag;
+
+	const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+	uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	volatile int* abortp = &abort_flag;
+
+	// work decode: blockIdx.x -> (batch, chunk, group, l-block); blockIdx.y -> slice of the group's heads
+	const int lblocks = Q / LB;
+	const int lb = lblocks - 1 - static_cast<int>(blockIdx.x % lblocks);  // heavier blocks first
+	int64_t rest = blockIdx.x / lblocks;
+	const int g = static_cast<int>(rest % G);
+	rest /= G;
+	const int c = static_cast<int>(rest % nchunks);
+	const int64_t b = rest / nchunks;
+	const int hpg = H / G;
+	const int h_begin = g * hpg + static_cast<int>(blockIdx.y) * heads_per_cta;
+	const int h_end = min(h_begin + heads_per_cta, (g + 1) * hpg);
+	const int nheads = h_end - h_begin;
+	const int l0 = lb * LB;
+	const int s_count = l0 + LB;        // causal extent of this row block
+	const int nkb = s_count / KB;       // 2 or 4
+	const int64_t tok0 = b * seqlen + static_cast<int64_t>(c) * Q;
+	const int valid = static_cast<int>(min(static_cast<int64_t>(Q), seqlen - static_cast<int64_t>(c) * Q));
+
+	if (threadIdx.x == 0)
+	{
+		abort_flag = 0;
+		mbar_init(smem_u32(&bar_in), 1);
+		mbar_init(smem_u32(&bar_cb), 1);
+		for (int i = 0; i < NS; ++i) { mbar_init(smem_u32(&s_full[i]), 4); mbar_init(smem_u32(&s_empty[i]), 1); }
+		for (int i = 0; i < NX; ++i) { mbar_init(smem_u32(&x_full[i]), 1); mbar_init(smem_u32(&x_empty[i]), 1); }
+		for (int i = 0; i < 2; ++i)
+		{
+			mbar_init(smem_u32(&p_full[i]), 1);
+			mbar_init(smem_u32(&p_empty[i]), 1);
+			mbar_init(smem_u32(&acc_full[i]), 1);
+			mbar_init(smem_u32(&acc_empty[i]), 8);
+		}
+		fence_mbar_init();
+	}
+	if (warp == 1)
+	{
+		tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+		tmem_relinquish();
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_slot;
+
+	if (nheads <= 0 || l0 >= valid) goto role_done;  // nothing to produce (uniform across the CTA)
+
+	if (warp == 0)
+	{
+		if (lane == 0)
+		{
+			prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmP);
+			const uint32_t in = smem_u32(&bar_in);
+			mbar_arrive_expect_tx(in, static_cast<uint32_t>(KA * (LB + s_count) * 128));
+#pragma unroll
+			for (int a = 0; a < KA; ++a)
+			{
+				for (int j = 0; j < LB / 64; ++j)
+					tma_load_3d(base + L::OFF_C + a * (LB * 128) + j * 8192, &tmC, in, g * NSTATE + a * 64, c * Q + l0 + j * 64,
+						static_cast<int>(b));
+				for (int j = 0; j < s_count / 64; ++j)
+					tma_load_3d(base + L::OFF_B + a * (256 * 128) + j * 8192, &tmB, in, g * NSTATE + a * 64, c * Q + j * 64,
+						static_cast<int>(b));
+			}
+			int kbc = 0;
+			for (int i = 0; i < nheads; ++i)
+			{
+				const int h = h_begin + i;
+				for (int kb = 0; kb < nkb; ++kb, ++kbc)
+				{
+					const int st = kbc % NX;
+					if (!mbar_wait(smem_u32(&x_empty[st]), ((kbc / NX) & 1) ^ 1u, abortp))
+					{
+						report_timeout(err_word, kErrProducerWait);
+						goto role_done;
+					}
+					mbar_arrive_expect_tx(smem_u32(&x_full[st]), X_STAGE);
+					tma_load_3d(base + L::OFF_X + st * X_STAGE, &tmX, smem_u32(&x_full[st]), h * 64, c * Q + kb * KB, static_cast<int>(b));
+				}
+				const int buf = i & 1;
+				if (!mbar_wait(smem_u32(&p_empty[buf]), ((i >> 1) & 1) ^ 1u, abortp))
+				{
+					report_timeout(err_word, kErrProducerWait);
+					goto role_done;
+				}
+				mbar_arrive_expect_tx(smem_u32(&p_full[buf]), L::P_BYTES);
+				const int prow = static_cast<int>(((b * nchunks + c) * H + h) * 64);
+#pragma unroll
+				for (int a = 0; a < KA; ++a)
+					tma_load_2d(base + L::OFF_P + buf * L::P_BYTES + a * 8192, &tmP, smem_u32(&p_full[buf]), a * 64, prow);
+			}
+		}
+	}
+	else if (warp == 1)
+	{
+		if (lane == 0)
+		{
+			if (!mbar_wait(smem_u32(&bar_in), 0, abortp))
+			{
+				report_timeout(err_word, kErrMmaWaitFull);
+				goto role_done;
+			}
+			tc_fence_after();
+			{
+				// CB[l, s] = sum_n C[l,n] B[s,n]  (N = s_count columns)
+				const uint32_t idesc_cb = make_idesc_f16(LB, s_count, 0);
+#pragma unroll
+				for (int a = 0; a < KA; ++a)
+				{
+					const uint64_t a_desc = make_smem_desc_sw128(base + L::OFF_C + a * (LB * 128), 16, 1024);
+					const uint64_t b_desc = make_smem_desc_sw128(base + L::OFF_B + a * (256 * 128), 16, 1024);
+#pragma unroll
+					for (int k = 0; k < 4; ++k)
+						mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_cb,
+							(a | k) != 0 ? 1u : 0u);
+				}
+				mma_commit(smem_u32(&bar_cb));
+			}
+			constexpr uint32_t idesc_y = make_idesc_f16(LB, 64, 1);  // B operand (x) is MN-major
+			constexpr uint32_t idesc_z = make_idesc_f16(LB, 64, 0);
+			int kbc = 0;
+			for (int i = 0; i < nheads; ++i)
+			{
+				const int buf = i & 1;
+				if (!mbar_wait(smem_u32(&acc_empty[buf]), ((i >> 1) & 1) ^ 1u, abortp))
+				{
+					report_timeout(err_word, kErrMmaWaitTmem);
+					goto role_done;
+				}
+				tc_fence_after();
+				const uint32_t y_tmem = tmem_base + 256u + static_cast<uint32_t>(buf * 128);
+				const uint32_t z_tmem = y_tmem + 64u;
+				for (int kb = 0; kb < nkb; ++kb, ++kbc)
+				{
+					const int ss = kbc % NS, xsn = kbc % NX;
+					if (!mbar_wait(smem_u32(&s_full[ss]), (kbc / NS) & 1, abortp) ||
+						!mbar_wait(smem_u32(&x_full[xsn]), (kbc / NX) & 1, abortp))
+					{
+						report_timeout(err_word, kErrMmaWaitFull);
+						goto role_done;
+					}
+					tc_fence_after();
+					const uint64_t a_desc = make_smem_desc_sw128(base + L::OFF_S + ss * S_STAGE, 16, 1024);
+					const uint64_t b_desc = make_smem_desc_sw128(base + L::OFF_X + xsn * X_STAGE, KB * 128, 1024);
+#pragma unroll
+					for (int k = 0; k < KB / 16; ++k)
+						mma_f16_ss(y_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
+							(kb | k) != 0 ? 1u : 0u);
+					mma_commit(smem_u32(&s_empty[ss]));
+					mma_commit(smem_u32(&x_empty[xsn]));
+				}
+				if (!mbar_wait(smem_u32(&p_full[buf]), (i >> 1) & 1, abortp))
+				{
+					report_timeout(err_word, kErrMmaWaitFull);
+					goto role_done;
+				}
+				tc_fence_after();
+#pragma unroll
+				for (int a = 0; a < KA; ++a)
+				{
+					const uint64_t a_desc = make_smem_desc_sw128(base + L::OFF_C + a * (LB * 128), 16, 1024);
+					const uint64_t b_desc = make_smem_desc_sw128(base + L::OFF_P + buf * L::P_BYTES + a * 8192, 16, 1024);
+#pragma unroll
+					for (int k = 0; k < 4; ++k)
+						mma_f16_ss(z_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_z,
+							(a | k) != 0 ? 1u : 0u);
+				}
+				mma_commit(smem_u32(&p_empty[buf]));
+				mma_commit(smem_u32(&acc_full[buf]));
+			}
+		}
+	}
+	else
+	{
+		const int q = warp & 3;           // TMEM lane quadrant
+		const int half = (warp - 2) >> 2;  // 0: warps 2-5, 1: warps 6-9
+		const int r = q * 32 + lane;      // row inside the block
+		const int l = l0 + r;
+		const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+		float dl2_prev = 0.f;
+		bool cb_ready = false;
+
+		auto epilogue = [&](int i, float dl2) -> bool {
+			const int buf = i & 1;
+			const int h = h_begin + i;
+			if (!mbar_wait(smem_u32(&acc_full[buf]), (i >> 1) & 1, abortp)) return false;
+			tc_fence_after();
+			uint32_t yr[32], zr[32];
+			const uint32_t col = 256u + static_cast<uint32_t>(buf * 128 + half * 32);
+			tmem_ld_32x32(t_lane + col, yr);
+			tmem_ld_32x32(t_lane + col + 64u, zr);
+			tmem_ld_wait();
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
+			if (l < valid)
+			{
+				const float dec = ex2_approx(dl2);
+				const float dh = D ? D[h] : 0.f;
+				const __half* xp = x + (tok0 + l) * xs + static_cast<int64_t>(h) * 64 + half * 32;
+				__half* yp = y + (tok0 + l) * ys + static_cast<int64_t>(h) * 64 + half * 32;
+#pragma unroll
+				for (int v = 0; v < 4; ++v)
+				{
+					float xv[8], o[8];
+					unpack8(*reinterpret_cast<const Half8*>(xp + v * 8), xv);
+#pragma unroll
+					for (int e = 0; e < 8; ++e)
+						o[e] = __uint_as_float(yr[v * 8 + e]) + dec * __uint_as_float(zr[v * 8 + e]) + dh * xv[e];
+					*reinterpret_cast<Half8*>(yp + v * 8) = pack8(o);
+				}
+			}
+			return true;
+		};
+
+		for (int i = 0; i < nheads; ++i)
+		{
+			const int h = h_begin + i;
+			const int64_t cbase = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+			const float dl2 = dacs[cbase + l] * kLog2e;
+			for (int kb = half; kb < nkb; kb += 2)
+			{
+				const int kbc = i * nkb + kb;
+				const int ss = kbc % NS;
+				if (!mbar_wait(smem_u32(&s_empty[ss]), ((kbc / NS) & 1) ^ 1u, abortp))
+				{
+					if (lane == 0) report_timeout(err_word, kErrScanWait);
+					goto role_done;
+				}
+				if (!cb_ready)
+				{
+					if (!mbar_wait(smem_u32(&bar_cb), 0, abortp))
+					{
+						if (lane == 0) report_timeout(err_word, kErrScanWait);
+						goto role_done;
+					}
+					cb_ready = true;
+				}
+				tc_fence_after();
+				uint8_t* srow = gen + L::OFF_S + ss * S_STAGE + r * 128;
+#pragma unroll
+				for (int c2 = 0; c2 < 2; ++c2)
+				{
+					uint32_t cbv[32];
+					tmem_ld_32x32(t_lane + static_cast<uint32_t>(kb * KB + c2 * 32), cbv);
+					tmem_ld_wait();
+					const int s0 = kb * KB + c2 * 32;
+					const float4* dsp = reinterpret_cast<const float4*>(dacs + cbase + s0);
+					const float4* dtp = reinterpret_cast<const float4*>(dt + cbase + s0);
+#pragma unroll
+					for (int v = 0; v < 4; ++v)  // 8 s-values -> one 16-byte chunk
+					{
+						float o[8];
+#pragma unroll
+						for (int hq = 0; hq < 2; ++hq)
+						{
+							const float4 ds = __ldg(dsp + v * 2 + hq);
+							const float4 dv = __ldg(dtp + v * 2 + hq);
+							const float dsa[4] = { ds.x, ds.y, ds.z, ds.w };
+							const float dta[4] = { dv.x, dv.y, dv.z, dv.w };
+#pragma unroll
+							for (int e = 0; e < 4; ++e)
+							{
+								const int j = v * 8 + hq * 4 + e;
+								const float w = ex2_approx(fmaf(dsa[e], -kLog2e, dl2)) * dta[e];
+								o[hq * 4 + e] = (s0 + j <= l) ? __uint_as_float(cbv[j]) * w : 0.f;
+							}
+						}
+						const int chunk = c2 * 4 + v;
+						*reinterpret_cast<Half8*>(srow + ((chunk ^ (r & 7)) << 4)) = pack8(o);
+					}
+				}
+				fence_proxy_async_smem();
+				__syncwarp();
+				if (lane == 0) mbar_arrive(smem_u32(&s_full[ss]));
+			}
+			if (i > 0 && !epilogue(i - 1, dl2_prev))
+			{
+				if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
+				goto role_done;
+			}
+			dl2_prev = dl2;
+		}
+		if (!epilogue(nheads - 1, dl2_prev))
+		{
+			if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
+		}
+	}
+
+role_done:
+	__syncwarp();
+	if (*abortp)
+		for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 1)
+	{
+		tc_fence_after();
+		tmem_dealloc(tmem_base, TMEM_COLS);
+	}
+}
+
+// =====================================================================================================================
+// host side
+// =====================================================================================================================
+
+bool ssd_tc_supported(const SsdDims& d, const void* x, int64_t xs, const void* Bm, int64_t bs, const void* Cm, int64_t cs, const void* y,
+	int64_t ys)
+{
+	if (d.P != 64 || (d.N != 64 && d.N != 128) || (d.Q != 128 && d.Q != 256)) return false;
+	if ((d.H / d.G) % 2 != 0) return false;  // head pairs must share a group
+	if (xs % 8 || bs % 8 || cs % 8 || ys % 8) return false;
+	if (!aligned16(x) || !aligned16(Bm) || !aligned16(Cm) || !aligned16(y)) return false;
+	if (d.batch > 0x7fffffffLL || d.seqlen > 0x7fffffffLL) return false;
+	if (d.batch * d.nchunks * d.H * 64 > 0x7fffffffLL) return false;  // prev-state row index is a 32-bit TMA coordinate
+	return true;
+}
+
+int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	CUtensorMap tmB;
+	int rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, static_cast<uint64_t>(d.seqlen), static_cast<uint64_t>(d.batch),
+		static_cast<uint64_t>(bs), static_cast<uint64_t>(d.seqlen) * bs, 64, 64);
+	if (rc) return rc;
+	const int nkb = d.Q / 64;
+	const unsigned grid = static_cast<unsigned>(d.batch * d.nchunks * (d.H / 2));
+	if (d.N == 64)
+	{
+		const int smem = nkb * (cstate::A_KB_BYTES + 64 * 128) + 1024;
+		static bool set = false;
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_state_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (cstate::A_KB_BYTES + 64 * 128) + 1024)); set = true; }
+		ssd_chunk_state_tc_kernel<64><<<grid, cstate::THREADS, smem, st>>>(tmB, x, xs, w.dt, w.dacs, w.states, d.seqlen, d.H, d.G, d.Q,
+			d.nchunks, device_error_word());
+	}
+	else
+	{
+		const int smem = nkb * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024;
+		static bool set = false;
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_state_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024)); set = true; }
+		ssd_chunk_state_tc_kernel<128><<<grid, cstate::THREADS, smem, st>>>(tmB, x, xs, w.dt, w.dacs, w.states, d.seqlen, d.H, d.G, d.Q,
+			d.nchunks, device_error_word());
+	}
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D, __half* y,
+	int64_t ys, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	CUtensorMap tmX, tmB, tmC, tmP;
+	const uint64_t L = static_cast<uint64_t>(d.seqlen), Bt = static_cast<uint64_t>(d.batch);
+	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(xs), L * xs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(bs), L * bs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmC, Cm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(cs), L * cs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_2d_f16(&tmP, w.prev16, static_cast<uint64_t>(d.batch) * d.nchunks * d.H * 64, static_cast<uint64_t>(d.N),
+		static_cast<uint64_t>(d.N), 64, 64);
+	if (rc) return rc;
+	const int lblocks = d.Q / cscan::LB;
+	const int hpg = d.H / d.G;
+	// enough CTAs to fill the machine, but as many heads per CTA as possible so that CB is computed rarely
+	const int64_t base_ctas = d.batch * d.nchunks * d.G * lblocks;
+	int hpc = hpg;
+	while (hpc > 4 && base_ctas * cdiv(hpg, hpc) < 2 * kNumSMs) hpc = (hpc + 1) / 2;
+	const dim3 grid(static_cast<unsigned>(base_ctas), static_cast<unsigned>(cdiv(hpg, hpc)));
+	if (d.N == 64)
+	{
+		using Lt = cscan::Layout<64, 4>;
+		static bool set = false;
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		ssd_chunk_scan_tc_kernel<64, 4><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, x, xs, y, ys, D, w.dt, w.dacs, d.seqlen,
+			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
+	}
+	else
+	{
+		using Lt = cscan::Layout<128, 2>;
+		static bool set = false;
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		ssd_chunk_scan_tc_kernel<128, 2><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, x, xs, y, ys, D, w.dt, w.dacs, d.seqlen,
+			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
+	}
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+}  // namespace b200

@@ -82,6 +82,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
 		: "memory");
 }
 
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+		::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+		: "memory");
+}
+
 // ---- tensor memory -----------------------------------------------------------------------------------------
 // Whole-warp calls. ncols: power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
@@ -159,9 +167,13 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t saddr, uint32_
 
 }  // namespace tc
 
-// ---- host: tensor-map encoding through the driver entry point (no link-time libcuda dependency) ----------------
-// 2-D f16 tensor [rows, cols] with row stride ld (elements); box = box_cols x box_rows; 128-byte swizzle.
-int encode_tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
+// ---- host: 128-byte-swizzled f16 tensor maps (encoded through the driver entry point, cached by key) -------------
+// 2-D tensor [rows, cols], row stride ld (elements); box = box_cols x box_rows.
+int tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
 	uint32_t box_rows);
+// 3-D tensor [d2, d1, d0] (d0 innermost), element strides s1 (between d1 rows) and s2 (between d2 slabs); box d0 x d1 x 1.
+// Out-of-range coordinates in any dimension read zeros, so a per-sequence row tail never picks up the next sequence.
+int tmap_3d_f16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems, uint64_t s2_elems,
+	uint32_t box0, uint32_t box1);
 
 }  // namespace b200

@@ -306,6 +306,108 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# single-operator mode (micro-benchmarks of the other configurations; small cases for profiler captures)
+# ---------------------------------------------------------------------------------------------------------------
+
+def run_kernel(args):
+    """Times one operator alone with CUDA events: `--kernel NAME [--small] --steps K --warmup W`.
+    conv1d_prefill / conv1d_decode: the standalone conv configuration (batch 8, 4224 channels, 4096 tokens; 256 decode steps).
+    decode: the Zamba2-2.7B-shaped decode step (batch 64). in_proj / out_proj / conv1d_tokens / ssd / gated_rmsnorm: the stages
+    of the cfg2 mixer on their in-mixer shapes. --small shrinks the token count (profiler-sized case, still larger than L2
+    where the operator is bandwidth-bound)."""
+    import torch
+    from anygpu_b200 import capi, ops
+    torch.cuda.set_device(0)
+    peaks = measured_peaks()
+    k = args.kernel
+    h = torch.float16
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rn = lambda *shape, std=1.0: (torch.randn(*shape, device="cuda", generator=g) * std).to(h)
+    cfg = workload("cfg2")
+    conv_dim, d_in_proj = synth.dims(cfg)
+    T = cfg["batch"] * cfg["seqlen"] // (4 if args.small else 1)
+    b, l = (1 if args.small else cfg["batch"]), cfg["seqlen"]
+    H, P, N, G, Q = cfg["nheads"], cfg["headdim"], cfg["d_state"], cfg["ngroups"], cfg["chunk"]
+    bytes_alg = flops_alg = None
+    nbuf = 3
+    if k == "conv1d_prefill":
+        B_, C_, L_ = (2 if args.small else 8), 4224, 4096
+        xs = [rn(B_, C_, L_) for _ in range(nbuf)]
+        w, bs = rn(C_, 4, std=0.5), rn(C_, std=0.1)
+        fn = lambda i: ops.tensor_causal_conv1d(xs[i % nbuf], w, bs)
+        bytes_alg = 2 * B_ * C_ * L_ * 2
+    elif k == "conv1d_decode":
+        B_, C_ = 8, 4224
+        w, bs = rn(C_, 4, std=0.5), rn(C_, std=0.1)
+        state, xt = rn(B_, C_, 3), rn(B_, C_)
+        fn = lambda i: ops.tensor_causal_conv1d_update(xt, state, w, bs)
+        bytes_alg = B_ * C_ * 2 * (3 + 3 + 1 + 1) + C_ * 5 * 2
+    elif k == "conv1d_tokens":
+        zx = [rn(b, l, d_in_proj) for _ in range(nbuf)]
+        w, bs = rn(conv_dim, 4, std=0.5), rn(conv_dim, std=0.1)
+        fn = lambda i: ops.tensor_causal_conv1d_tokens(zx[i % nbuf][:, :, cfg["d_inner"]:cfg["d_inner"] + conv_dim], w, bs)
+        bytes_alg = 2 * b * l * conv_dim * 2
+    elif k == "gated_rmsnorm":
+        xs = [rn(T, cfg["d_inner"]) for _ in range(nbuf)]
+        zs = [rn(T, cfg["d_inner"]) for _ in range(nbuf)]
+        w = rn(cfg["d_inner"])
+        fn = lambda i: ops.tensor_zamba_gated_rmsnorm(xs[i % nbuf], zs[i % nbuf], w, cfg["d_inner"], 1e-5)
+        bytes_alg = 3 * T * cfg["d_inner"] * 2
+    elif k in ("in_proj", "out_proj"):
+        K_, N_ = (cfg["d_model"], d_in_proj) if k == "in_proj" else (cfg["d_inner"], cfg["d_model"])
+        xs = [rn(T, K_) for _ in range(nbuf)]
+        w = rn(K_, N_, std=0.02)
+        outs = torch.empty(T, N_, device="cuda", dtype=h)
+        fn = lambda i: ops.tensor_linear(xs[i % nbuf], w, out=outs)
+        flops_alg = 2.0 * T * K_ * N_
+    elif k == "ssd":
+        xbc = [rn(b, l, conv_dim, std=0.5) for _ in range(nbuf)]
+        dts = rn(b, l, H)
+        A = -(torch.rand(H, device="cuda", generator=g) * 15 + 1)
+        D, dtb = torch.ones(H, device="cuda"), torch.full((H,), -3.0, device="cuda")
+        def fn(i):
+            t = xbc[i % nbuf]
+            return ops.tensor_mamba_chunk_scan_combined(t[:, :, :H * P].unflatten(2, (H, P)), dts, A,
+                                                        t[:, :, H * P:H * P + G * N].unflatten(2, (G, N)),
+                                                        t[:, :, H * P + G * N:].unflatten(2, (G, N)), Q, D=D, dt_bias=dtb)
+        nchunks = -(-l // Q)
+        flops_alg = float(b * nchunks * (H * (2 * Q * Q * P + 4 * Q * N * P) + G * 2 * Q * Q * N))
+    elif k == "decode":
+        c3 = workload("cfg3")
+        wts = ops.ZambaMamba2weights.from_numpy(synth.make_weights(c3, 0), h)
+        mixer = ops.Mamba2Mixer(c3, wts)
+        cs, ss = synth.make_decode_state(c3, 0)
+        cache = ops.ZambaMambaCache(torch.from_numpy(cs).cuda().half(), torch.from_numpy(ss).cuda())
+        u = rn(c3["batch"], c3["d_model"])
+        o = torch.empty_like(u)
+        fn = lambda i: mixer.decode(u, cache, out=o)
+        cd3, dip3 = synth.dims(c3)
+        bytes_alg = (c3["d_model"] * dip3 + c3["d_inner"] * c3["d_model"]) * 2 + 2 * ss.size * 4 + 2 * cs.size * 2
+    else:
+        raise SystemExit(f"unknown kernel {k}")
+    for i in range(args.warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    for i, (e0, e1) in enumerate(evs):
+        e0.record()
+        fn(i)
+        e1.record()
+    torch.cuda.synchronize()
+    ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+    med, mn = ms[len(ms) // 2], ms[0]
+    capi.check("b200_last_device_error", capi.load().b200_last_device_error(None, None))
+    out = {"kernel": k, "small": bool(args.small), "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
+    if bytes_alg:
+        out.update(algorithmic_bytes=bytes_alg, gbs_median=bytes_alg / (med * 1e-3) / 1e9, hbm_peak_gbs=peaks["hbm_gbs"],
+                   frac_of_hbm_peak=bytes_alg / (med * 1e-3) / 1e9 / peaks["hbm_gbs"], peak_source=peaks["source"])
+    if flops_alg:
+        out.update(algorithmic_flops=flops_alg, tflops_median=flops_alg / (med * 1e-3) / 1e12, tensor_peak_tflops=peaks["tflops_burst"],
+                   frac_of_tensor_peak=flops_alg / (med * 1e-3) / 1e12 / peaks["tflops_burst"], peak_source=peaks["source"])
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -314,7 +416,11 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
+    ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
     args = ap.parse_args()
+    if args.kernel:
+        return run_kernel(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -234,7 +234,9 @@ def _ssd_inputs(seed, b, l, H, P, G, N):
 
 
 @pytest.mark.parametrize("dims", [(1, 512, 4, 64, 1, 64, 256), (2, 256, 8, 64, 2, 64, 128), (1, 300, 4, 64, 1, 64, 256),
-                                  (1, 128, 2, 64, 1, 128, 64), (2, 64, 8, 64, 1, 16, 32), (1, 96, 2, 32, 1, 16, 32)])
+                                  (1, 128, 2, 64, 1, 128, 64), (2, 64, 8, 64, 1, 16, 32), (1, 96, 2, 32, 1, 16, 32),
+                                  (1, 256, 2, 64, 1, 128, 128), (1, 512, 4, 64, 2, 128, 256), (3, 1024, 16, 64, 1, 64, 256),
+                                  (1, 200, 12, 64, 3, 64, 128)])
 def test_ssd_f16_vs_oracle(ops, dims):
     b, l, H, P, G, N, Q = dims
     x, dt, A, B, C, D, dt_bias = _ssd_inputs(sum(dims), b, l, H, P, G, N)
@@ -250,7 +252,7 @@ def test_ssd_f16_vs_oracle(ops, dims):
 
 def test_ssd_f16_in_place_slices(ops):
     # x | B | C read in place from one [b,l,conv_dim] tensor and dt from another wide tensor, as the mixer does
-    b, l, H, P, G, N, Q = 1, 128, 4, 64, 1, 64, 64
+    b, l, H, P, G, N, Q = 2, 384, 4, 64, 1, 64, 128
     x, dt, A, B, C, D, dt_bias = _ssd_inputs(77, b, l, H, P, G, N)
     x, dt, B, C = map(f16v, (x, dt, B, C))
     xbc = np.concatenate([x.reshape(b, l, H * P), B.reshape(b, l, G * N), C.reshape(b, l, G * N)], axis=2)
