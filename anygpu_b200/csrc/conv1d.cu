@@ -48,6 +48,15 @@ __global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict
 	const int j = active ? static_cast<int>(tid - row * vec_per_row) : 0;
 	const int64_t base = row * (static_cast<int64_t>(vec_per_row) * EPT) + static_cast<int64_t>(j) * EPT;
 
+	// lane 0 cannot get its halo from a neighbour: fetch it first so that it does not queue behind the main loads
+	const int lane = threadIdx.x & 31;
+	float g0 = 0.f, g1 = 0.f, g2 = 0.f;
+	if (active && lane == 0 && j > 0)
+	{
+		g0 = ldf(x + base - 3);
+		g1 = ldf(x + base - 2);
+		g2 = ldf(x + base - 1);
+	}
 	float v[EPT + 3];  // v[0..2] = halo, v[3..] = own elements
 	if (active)
 	{
@@ -60,7 +69,6 @@ __global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict
 		for (int i = 0; i < EPT; ++i) v[3 + i] = 0.f;
 	}
 	// halo: last three elements of the previous lane's run (same row when j > 0)
-	const int lane = threadIdx.x & 31;
 	float h0 = __shfl_up_sync(0xffffffffu, v[EPT], 1);
 	float h1 = __shfl_up_sync(0xffffffffu, v[EPT + 1], 1);
 	float h2 = __shfl_up_sync(0xffffffffu, v[EPT + 2], 1);
@@ -71,9 +79,7 @@ __global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict
 	}
 	else if (lane == 0)
 	{
-		h0 = ldf(x + base - 3);
-		h1 = ldf(x + base - 2);
-		h2 = ldf(x + base - 1);
+		h0 = g0; h1 = g1; h2 = g2;
 	}
 	v[0] = h0; v[1] = h1; v[2] = h2;
 
@@ -118,20 +124,50 @@ __global__ void __launch_bounds__(256) conv1d_seq_scalar_kernel(const T* __restr
 }
 
 // ---- token-major layout: channels contiguous, rows strided ---------------------------------------------------
-// One thread owns V consecutive channels (V = 16 bytes worth, or 1) and TL consecutive tokens, sliding a
-// (W-1)-row window through registers.
+// One thread owns V consecutive channels (16 bytes worth, or 1) and TL consecutive tokens. All TL + W - 1 row
+// fragments are loaded before the first use, so a thread keeps TL + W - 1 16-byte loads in flight.
+template <typename T, int V> struct RawVec;
+template <> struct RawVec<__half, 8> { Half8 v; };
+template <> struct RawVec<float, 4> { float4 v; };
+template <typename T> struct RawVec<T, 1> { T v; };
+
+template <typename T, int V>
+__device__ __forceinline__ void raw_load(RawVec<T, V>& r, const T* p)
+{
+	if constexpr (V == 1) r.v = *p;
+	else if constexpr (sizeof(T) == 2) r.v = *reinterpret_cast<const Half8*>(p);
+	else r.v = *reinterpret_cast<const float4*>(p);
+}
+template <typename T, int V>
+__device__ __forceinline__ void raw_unpack(const RawVec<T, V>& r, float* f)
+{
+	if constexpr (V == 1) f[0] = Cvt<T>::to_f32(r.v);
+	else if constexpr (sizeof(T) == 2) unpack8(r.v, f);
+	else { f[0] = r.v.x; f[1] = r.v.y; f[2] = r.v.z; f[3] = r.v.w; }
+}
+
 template <typename T, int V, int W, int TL>
 __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
 	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
-	int64_t seqlen, int64_t dims, int cvec /* ceil(dims / V) */)
+	int64_t seqlen, int64_t dims, int cvec /* ceil(dims / V) */, int64_t nwork /* cvec * token blocks */)
 {
-	const int cv = blockIdx.x * blockDim.x + threadIdx.x;
-	if (cv >= cvec) return;
+	const int64_t wid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (wid >= nwork) return;
+	const int cv = static_cast<int>(wid % cvec);
+	const int64_t tb = wid / cvec;
 	const int64_t c0 = static_cast<int64_t>(cv) * V;
-	const int64_t b = blockIdx.z;
-	const int64_t t0 = static_cast<int64_t>(blockIdx.y) * TL;
+	const int64_t b = blockIdx.y;
+	const int64_t t0 = tb * TL;
 	const T* xb = x + b * seqlen * xs;
 	T* yb = y + b * seqlen * ys;
+
+	RawVec<T, V> raw[TL + W - 1];
+#pragma unroll
+	for (int i = 0; i < TL + W - 1; ++i)
+	{
+		const int64_t t = t0 - (W - 1) + i;
+		if (t >= 0 && t < seqlen) raw_load<T, V>(raw[i], xb + t * xs + c0);
+	}
 
 	float wt[W][V], bs[V];
 #pragma unroll
@@ -149,8 +185,7 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 		const int64_t t = t0 - (W - 1) + k;
 		if (t >= 0)
 		{
-			if constexpr (V > 1) Vec16<T>::load(xb + t * xs + c0, win[k]);
-			else win[k][0] = ldf(xb + t * xs + c0);
+			raw_unpack<T, V>(raw[k], win[k]);
 		}
 		else
 		{
@@ -161,29 +196,30 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 		}
 	}
 
-#pragma unroll 4
+#pragma unroll
 	for (int i = 0; i < TL; ++i)
 	{
 		const int64_t t = t0 + i;
-		if (t >= seqlen) break;
-		if constexpr (V > 1) Vec16<T>::load(xb + t * xs + c0, win[W - 1]);
-		else win[W - 1][0] = ldf(xb + t * xs + c0);
-		float out[V];
-#pragma unroll
-		for (int c = 0; c < V; ++c)
+		if (t < seqlen)
 		{
-			float acc = 0.f;
+			raw_unpack<T, V>(raw[i + W - 1], win[W - 1]);
+			float out[V];
 #pragma unroll
-			for (int k = 0; k < W; ++k) acc += wt[k][c] * win[k][c];
-			acc += bs[c];
-			out[c] = silu_f32(acc);
+			for (int c = 0; c < V; ++c)
+			{
+				float acc = 0.f;
+#pragma unroll
+				for (int k = 0; k < W; ++k) acc += wt[k][c] * win[k][c];
+				acc += bs[c];
+				out[c] = silu_f32(acc);
+			}
+			if constexpr (V > 1) Vec16<T>::store(yb + t * ys + c0, out);
+			else stf(yb + t * ys + c0, out[0]);
+#pragma unroll
+			for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+				for (int c = 0; c < V; ++c) win[k][c] = win[k + 1][c];
 		}
-		if constexpr (V > 1) Vec16<T>::store(yb + t * ys + c0, out);
-		else stf(yb + t * ys + c0, out[0]);
-#pragma unroll
-		for (int k = 0; k < W - 1; ++k)
-#pragma unroll
-			for (int c = 0; c < V; ++c) win[k][c] = win[k + 1][c];
 	}
 
 	// the thread that consumed the last token holds the next conv_state in its window
@@ -267,16 +303,18 @@ template <typename T, int V>
 static int launch_tok(const T* x, int64_t xs, const T* w, const T* bias, T* y, int64_t ys, const T* init, T* fin,
 	int64_t batch, int64_t seqlen, int64_t dims, int W, cudaStream_t st)
 {
-	constexpr int TL = 16;
+	constexpr int TL = 8;
 	const int cvec = static_cast<int>(cdiv(dims, V));
-	const dim3 g(static_cast<unsigned>(cdiv(cvec, 128)), static_cast<unsigned>(cdiv(seqlen, TL)), static_cast<unsigned>(batch));
-	if (g.y > 65535u || g.z > 65535u) return B200_ERR_UNSUPPORTED;
+	const int64_t nwork = static_cast<int64_t>(cvec) * cdiv(seqlen, TL);
+	const int64_t blocks = cdiv(nwork, 128);
+	if (blocks > 0x7fffffffLL || batch > 65535) return B200_ERR_UNSUPPORTED;
+	const dim3 g(static_cast<unsigned>(blocks), static_cast<unsigned>(batch));
 	switch (W)
 	{
-	case 1: conv1d_tok_kernel<T, V, 1, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
-	case 2: conv1d_tok_kernel<T, V, 2, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
-	case 3: conv1d_tok_kernel<T, V, 3, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
-	default: conv1d_tok_kernel<T, V, 4, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec); break;
+	case 1: conv1d_tok_kernel<T, V, 1, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
+	case 2: conv1d_tok_kernel<T, V, 2, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
+	case 3: conv1d_tok_kernel<T, V, 3, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
+	default: conv1d_tok_kernel<T, V, 4, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
 	}
 	B200_LAUNCH_CHECK();
 	return B200_OK;

@@ -6,8 +6,7 @@
 
 namespace b200 {
 
-constexpr int kNormThreads = 256;
-constexpr int kNormCache = 4;  // 16-byte vectors cached per thread (covers groups up to 8192 f16 / 4096 f32 elements)
+constexpr int kNormCache = 4;  // 16-byte vectors cached per thread
 
 template <typename T> struct NV;
 template <> struct NV<__half>
@@ -30,21 +29,22 @@ template <> struct NV<float>
 	}
 };
 
+template <int THREADS>
 __device__ __forceinline__ float block_sum(float v, float* red)
 {
 	v = warp_sum(v);
 	const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 	if (lane == 0) red[wid] = v;
 	__syncthreads();
-	float t = (lane < kNormThreads / 32) ? red[lane] : 0.f;
+	float t = (lane < THREADS / 32) ? red[lane] : 0.f;
 	t = warp_sum(t);
 	return t;  // identical in every thread of every warp
 }
 
 // VEC: 16-byte vectors (rows and group starts 16-byte aligned). CACHED: the group fits the register cache.
-template <typename T, bool CACHED>
-__global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T* __restrict__ x, int64_t xs,
-	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* __restrict__ y, int64_t ys, int gsize, int ngroups, float eps)
+template <typename T, bool CACHED, int kNormThreads>
+__global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T* x, int64_t xs,
+	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* y /* may alias x */, int64_t ys, int gsize, int ngroups, float eps)
 {
 	constexpr int E = NV<T>::E;
 	__shared__ float red[kNormThreads / 32];
@@ -94,7 +94,7 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T
 			}
 		}
 	}
-	const float total = block_sum(ss, red);
+	const float total = block_sum<kNormThreads>(ss, red);
 	const float scale = rsqrtf(total / static_cast<float>(gsize) + eps);
 
 	if constexpr (CACHED)
@@ -129,9 +129,9 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T
 }
 
 // Any alignment / size.
-template <typename T>
-__global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_scalar_kernel(const T* __restrict__ x, int64_t xs,
-	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* __restrict__ y, int64_t ys, int gsize, int ngroups, float eps)
+template <typename T, int kNormThreads>
+__global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_scalar_kernel(const T* x, int64_t xs,
+	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* y /* may alias x */, int64_t ys, int gsize, int ngroups, float eps)
 {
 	__shared__ float red[kNormThreads / 32];
 	const int64_t row = blockIdx.x / ngroups;
@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_scalar_kernel(cons
 		const float gv = ldf(xr + i) * silu_f32(ldf(zr + i));
 		ss += gv * gv;
 	}
-	const float total = block_sum(ss, red);
+	const float total = block_sum<kNormThreads>(ss, red);
 	const float scale = rsqrtf(total / static_cast<float>(gsize) + eps);
 	for (int i = threadIdx.x; i < gsize; i += kNormThreads)
 	{
@@ -171,12 +171,15 @@ static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs,
 	const int gs = static_cast<int>(gsize);
 	const bool vec = aligned16(x) && aligned16(z) && aligned16(w) && aligned16(y) && xs % E == 0 && zs % E == 0 && ys % E == 0 &&
 		gsize % E == 0;
+	// smallest CTA whose register cache holds the group: more CTAs in flight per SM, shorter reduction
 	if (!vec)
-		gated_rmsnorm_scalar_kernel<T><<<g, kNormThreads, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
-	else if (gsize / E <= kNormCache * kNormThreads)
-		gated_rmsnorm_vec_kernel<T, true><<<g, kNormThreads, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+		gated_rmsnorm_scalar_kernel<T, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+	else if (gsize / E <= kNormCache * 128)
+		gated_rmsnorm_vec_kernel<T, true, 128><<<g, 128, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+	else if (gsize / E <= kNormCache * 256)
+		gated_rmsnorm_vec_kernel<T, true, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
 	else
-		gated_rmsnorm_vec_kernel<T, false><<<g, kNormThreads, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+		gated_rmsnorm_vec_kernel<T, false, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }

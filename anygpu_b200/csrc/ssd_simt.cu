@@ -6,16 +6,16 @@
 namespace b200 {
 
 // ---- stage 1: dt = softplus(dt_raw + bias); dAcs = cumsum_l(dt * A) within each chunk -------------------------
-// grid (b*nchunks, ceil(H/32)), 256 threads. Positions past seqlen hold dt_raw = 0 BEFORE bias and softplus,
+// grid (b*nchunks, ceil(H/8)), 256 threads. Positions past seqlen hold dt_raw = 0 BEFORE bias and softplus,
 // exactly as the reference pads (scripts/zamba2/mamba_chunk_scan_comb.py:38-45).
-constexpr int kCsHeads = 32;
+constexpr int kCsHeads = 8;
 
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
 	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
 	float* __restrict__ dt_out, float* __restrict__ dacs_out)
 {
-	extern __shared__ float sdt[];  // [Q][33]
+	extern __shared__ float sdt[];  // [Q][kCsHeads + 1]
 	const int64_t b = blockIdx.x / nchunks;
 	const int c = static_cast<int>(blockIdx.x % nchunks);
 	const int h0 = blockIdx.y * kCsHeads;
@@ -165,33 +165,66 @@ template int ssd_chunk_state_simt<__half>(const __half*, int64_t, const __half*,
 template int ssd_chunk_state_simt<float>(const float*, int64_t, const float*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
 
 // ---- stage 3: state passing across chunks --------------------------------------------------------------------
-// One thread per state element walks the chunks: states[c] <- state before chunk c; carries the running state in a
-// register. Bandwidth-bound (one read + one write of the chunk states), fully coalesced.
+// One thread per 4 consecutive state elements walks the chunks: states[c] <- state before chunk c, carrying the running
+// state in registers. Bandwidth-bound (one read + one write of the chunk states): the loads of 8 chunks are issued
+// together, ahead of the serial recurrence, so the dependent chain never waits on memory more than once per 8 chunks.
+constexpr int kSpBatch = 8;
+
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restrict__ states, __half* __restrict__ prev16,
 	const float* __restrict__ dacs, const float* __restrict__ init, float* __restrict__ fin, int H, int PN, int Q, int nchunks)
 {
-	const int i = blockIdx.x * blockDim.x + threadIdx.x;
+	const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
 	if (i >= PN) return;
 	const int h = blockIdx.y;
 	const int64_t b = blockIdx.z;
-	float s = init ? init[(b * H + h) * static_cast<int64_t>(PN) + i] : 0.f;
-	for (int c = 0; c < nchunks; ++c)
+	const int64_t cstride = static_cast<int64_t>(H) * PN;  // elements between consecutive chunks
+	float* sp = states + (b * nchunks * H + h) * static_cast<int64_t>(PN) + i;
+	__half* pp = prev16 ? prev16 + (b * nchunks * H + h) * static_cast<int64_t>(PN) + i : nullptr;
+	const float* dl = dacs + (b * H + h) * static_cast<int64_t>(nchunks) * Q + (Q - 1);  // last dAcs of chunk c at dl[c*Q]
+	float4 s = init ? *reinterpret_cast<const float4*>(init + (b * H + h) * static_cast<int64_t>(PN) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+	for (int c0 = 0; c0 < nchunks; c0 += kSpBatch)
 	{
-		float* p = states + ((b * nchunks + c) * H + h) * static_cast<int64_t>(PN) + i;
-		const float cur = *p;
-		*p = s;
-		if (prev16) prev16[((b * nchunks + c) * H + h) * static_cast<int64_t>(PN) + i] = __float2half_rn(s);
-		const float dec = expf(dacs[((b * H + h) * nchunks + c) * static_cast<int64_t>(Q) + Q - 1]);
-		s = s * dec + cur;
+		float4 cur[kSpBatch];
+		float dec[kSpBatch];
+#pragma unroll
+		for (int j = 0; j < kSpBatch; ++j)
+		{
+			if (c0 + j < nchunks)
+			{
+				cur[j] = *reinterpret_cast<const float4*>(sp + (c0 + j) * cstride);
+				dec[j] = dl[static_cast<int64_t>(c0 + j) * Q];
+			}
+		}
+#pragma unroll
+		for (int j = 0; j < kSpBatch; ++j)
+		{
+			if (c0 + j < nchunks)
+			{
+				*reinterpret_cast<float4*>(sp + (c0 + j) * cstride) = s;
+				if (pp)
+				{
+					__half2* q = reinterpret_cast<__half2*>(pp + (c0 + j) * cstride);
+					q[0] = __floats2half2_rn(s.x, s.y);
+					q[1] = __floats2half2_rn(s.z, s.w);
+				}
+				const float d = __expf(dec[j]);
+				s.x = s.x * d + cur[j].x;
+				s.y = s.y * d + cur[j].y;
+				s.z = s.z * d + cur[j].z;
+				s.w = s.w * d + cur[j].w;
+			}
+		}
 	}
-	if (fin) fin[(b * H + h) * static_cast<int64_t>(PN) + i] = s;
+	if (fin) *reinterpret_cast<float4*>(fin + (b * H + h) * static_cast<int64_t>(PN) + i) = s;
 }
 
 int ssd_state_passing(const float* initial_states, float* final_states, bool write_prev16, const SsdDims& d, const SsdWorkspace& w,
 	cudaStream_t st)
 {
 	const int PN = d.P * d.N;
-	const dim3 g(static_cast<unsigned>(cdiv(PN, 256)), static_cast<unsigned>(d.H), static_cast<unsigned>(d.batch));
+	if (PN % 4 != 0 || (initial_states && !aligned16(initial_states)) || (final_states && !aligned16(final_states)))
+		return B200_ERR_MISALIGNED;
+	const dim3 g(static_cast<unsigned>(cdiv(PN / 4, 256)), static_cast<unsigned>(d.H), static_cast<unsigned>(d.batch));
 	if (g.z > 65535u || g.y > 65535u) return B200_ERR_UNSUPPORTED;
 	ssd_state_passing_kernel<<<g, 256, 0, st>>>(w.states, write_prev16 ? w.prev16 : nullptr, w.dacs, initial_states, final_states, d.H,
 		PN, d.Q, d.nchunks);

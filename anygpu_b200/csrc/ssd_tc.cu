@@ -103,28 +103,46 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 		const int j = chunk >> 3, cj = chunk & 7;  // atom (= head of the pair), 16-byte chunk inside the atom row
 		const int64_t cbh = j ? cb1 : cb0;
 		const float last = j ? last1 : last0;
-		for (int l = threadIdx.x >> 4; l < Q; l += THREADS / 16)
+		// 8 rows per batch: all global loads of a batch are issued before the first use
+		constexpr int RB = 8, RSTEP = THREADS / 16;
+		for (int lbase = threadIdx.x >> 4; lbase < Q; lbase += RB * RSTEP)
 		{
-			Half8 v;
-			if (l < valid)
-			{
-				const float sc = __expf(last - dacs[cbh + l]) * dt[cbh + l];
-				const Half8 in = *reinterpret_cast<const Half8*>(x + (tok0 + l) * xs + static_cast<int64_t>(h0) * 64 + chunk * 8);
-				float f[8];
-				unpack8(in, f);
+			Half8 in[RB];
+			float sc[RB];
 #pragma unroll
-				for (int e = 0; e < 8; ++e) f[e] *= sc;
-				v = pack8(f);
-			}
-			else
+			for (int u = 0; u < RB; ++u)
 			{
-#pragma unroll
-				for (int e = 0; e < 4; ++e) v.h[e] = __floats2half2_rn(0.f, 0.f);
+				const int l = lbase + u * RSTEP;
+				if (l < valid)
+				{
+					in[u] = *reinterpret_cast<const Half8*>(x + (tok0 + l) * xs + static_cast<int64_t>(h0) * 64 + chunk * 8);
+					sc[u] = __expf(last - dacs[cbh + l]) * dt[cbh + l];
+				}
 			}
-			const int kb = l >> 6, lk = l & 63;
-			const uint32_t off = static_cast<uint32_t>(kb) * A_KB_BYTES + static_cast<uint32_t>(j) * (KB * 128) +
-				static_cast<uint32_t>(lk) * 128 + (static_cast<uint32_t>(cj ^ (lk & 7)) << 4);
-			*reinterpret_cast<Half8*>(a_gen + off) = v;
+#pragma unroll
+			for (int u = 0; u < RB; ++u)
+			{
+				const int l = lbase + u * RSTEP;
+				if (l >= Q) break;
+				Half8 v;
+				if (l < valid)
+				{
+					float f[8];
+					unpack8(in[u], f);
+#pragma unroll
+					for (int e = 0; e < 8; ++e) f[e] *= sc[u];
+					v = pack8(f);
+				}
+				else
+				{
+#pragma unroll
+					for (int e = 0; e < 4; ++e) v.h[e] = __floats2half2_rn(0.f, 0.f);
+				}
+				const int kb = l >> 6, lk = l & 63;
+				const uint32_t off = static_cast<uint32_t>(kb) * A_KB_BYTES + static_cast<uint32_t>(j) * (KB * 128) +
+					static_cast<uint32_t>(lk) * 128 + (static_cast<uint32_t>(cj ^ (lk & 7)) << 4);
+				*reinterpret_cast<Half8*>(a_gen + off) = v;
+			}
 		}
 	}
 	fence_proxy_async_smem();
