@@ -49,6 +49,9 @@ SIGNATURES = {
     "b200_mamba_chunk_scan_combined_workspace_bytes": (_sz, [_i64] * 7),
     "b200_mamba_chunk_scan_combined": (_int, [_int, _vp, _i64, _vp, _i64, _vp, _int, _vp, _i64, _vp, _i64, _vp, _vp, _vp,
                                               _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _vp, _sz, _vp]),
+    "b200_mamba_chunk_scan_combined_static_capacity": (_sz, []),
+    "b200_mamba_chunk_scan_combined_static": (_int, [_int, _vp, _i64, _vp, _i64, _vp, _int, _vp, _i64, _vp, _i64, _vp, _vp, _vp,
+                                                     _vp, _i64, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _int, _vp]),
     "b200_selective_state_update": (_int, [_int, _vp, _vp, _i64, _vp, _i64, _vp, _int, _vp, _i64, _vp, _i64, _vp, _vp, _vp, _i64,
                                            _i64, _i64, _i64, _i64, _i64, _int, _vp]),
     "b200_mamba2_mixer_prefill_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),

@@ -126,6 +126,23 @@ int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, c
 	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
 	void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same operator for callers that cannot provide a workspace. No counterpart in anyGPU (it allocates every operator
+ * output with cudaMalloc, srcs/core/tensor.hpp:80-84): this variant exists for hosts that may not allocate device memory at
+ * all - a plugin that only receives its input and output tensors from a runtime owning the allocator, code inside a region
+ * where cudaMalloc is not permitted, a binding whose pool is exhausted. The scratch is a fixed array inside the library's
+ * device image: b200_mamba_chunk_scan_combined_static_capacity() bytes (64 MiB) are held on every GPU that loads the
+ * library until the process exits. Problems whose workspace (b200_mamba_chunk_scan_combined_workspace_bytes) exceeds that
+ * capacity are rejected with B200_ERR_WORKSPACE. The call itself allocates nothing. Its FIRST call on each device looks up
+ * the array's device address (cudaGetSymbolAddress); make that first call outside any stream capture. All calls share the
+ * one array and it keeps the previous call's contents (harmless: each stage overwrites what the next one reads), so two calls
+ * whose kernels can overlap on the GPU - different streams, or different host threads - race on it: issue them on one stream. */
+size_t b200_mamba_chunk_scan_combined_static_capacity(void);
+int b200_mamba_chunk_scan_combined_static(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
+	const float* D, const float* dt_bias, const float* initial_states,
+	void* y, int64_t y_stride, float* final_states,
+	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus, void* stream);
+
 /* ---- single-token state recurrence (decode) -----------------------------------------------------------------
  * dt = softplus(dt_raw + dt_bias); h <- exp(dt A) h + dt x (x) B; y = h.C + D x, per (batch, head).
  * ssm_state [b,H,P,N] fp32 is updated in place. No counterpart in anyGPU; equals one step of the per-token form of
