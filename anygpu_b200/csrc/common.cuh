@@ -61,7 +61,9 @@ template <typename T> __device__ __forceinline__ float ldf(const T* p) { return 
 template <typename T> __device__ __forceinline__ void stf(T* p, float v) { *p = Cvt<T>::from_f32(v); }
 
 // silu(x) = x / (1 + exp(-x)), the form anyGPU uses (srcs/kernels/cuda/math_ops.cu:3-34).
-__device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + __expf(-v)); }
+// The quotient uses the fast reciprocal path (2 ulp): an IEEE division here makes the conv and norm kernels
+// instruction-bound instead of HBM-bound.
+__device__ __forceinline__ float silu_f32(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 
 // torch softplus (beta 1, threshold 20), as F.softplus in scripts/zamba2/mamba_chunk_scan_comb.py:45.
 __device__ __forceinline__ float softplus_f32(float v) { return v > 20.f ? v : log1pf(expf(v)); }
@@ -97,5 +99,33 @@ __device__ __forceinline__ Half8 pack8(const float* f)
 	for (int i = 0; i < 4; ++i) v.h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
 	return v;
 }
+
+// V consecutive elements of T moved with one access of V*sizeof(T) bytes (16, 8, 4 or 2).
+template <int BYTES> struct BitsOf;
+template <> struct BitsOf<16> { using type = uint4; };
+template <> struct BitsOf<8> { using type = uint2; };
+template <> struct BitsOf<4> { using type = uint32_t; };
+template <> struct BitsOf<2> { using type = uint16_t; };
+
+template <typename T, int V>
+struct Pack
+{
+	using B = typename BitsOf<V * sizeof(T)>::type;
+	B bits;
+	__device__ __forceinline__ void load(const T* p) { bits = *reinterpret_cast<const B*>(p); }
+	__device__ __forceinline__ void store(T* p) const { *reinterpret_cast<B*>(p) = bits; }
+	__device__ __forceinline__ void unpack(float* f) const
+	{
+		const T* e = reinterpret_cast<const T*>(&bits);
+#pragma unroll
+		for (int i = 0; i < V; ++i) f[i] = Cvt<T>::to_f32(e[i]);
+	}
+	__device__ __forceinline__ void pack(const float* f)
+	{
+		T* e = reinterpret_cast<T*>(&bits);
+#pragma unroll
+		for (int i = 0; i < V; ++i) e[i] = Cvt<T>::from_f32(f[i]);
+	}
+};
 
 }  // namespace b200

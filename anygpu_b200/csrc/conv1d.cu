@@ -124,28 +124,9 @@ __global__ void __launch_bounds__(256) conv1d_seq_scalar_kernel(const T* __restr
 }
 
 // ---- token-major layout: channels contiguous, rows strided ---------------------------------------------------
-// One thread owns V consecutive channels (16 bytes worth, or 1) and TL consecutive tokens. All TL + W - 1 row
-// fragments are loaded before the first use, so a thread keeps TL + W - 1 16-byte loads in flight.
-template <typename T, int V> struct RawVec;
-template <> struct RawVec<__half, 8> { Half8 v; };
-template <> struct RawVec<float, 4> { float4 v; };
-template <typename T> struct RawVec<T, 1> { T v; };
-
-template <typename T, int V>
-__device__ __forceinline__ void raw_load(RawVec<T, V>& r, const T* p)
-{
-	if constexpr (V == 1) r.v = *p;
-	else if constexpr (sizeof(T) == 2) r.v = *reinterpret_cast<const Half8*>(p);
-	else r.v = *reinterpret_cast<const float4*>(p);
-}
-template <typename T, int V>
-__device__ __forceinline__ void raw_unpack(const RawVec<T, V>& r, float* f)
-{
-	if constexpr (V == 1) f[0] = Cvt<T>::to_f32(r.v);
-	else if constexpr (sizeof(T) == 2) unpack8(r.v, f);
-	else { f[0] = r.v.x; f[1] = r.v.y; f[2] = r.v.z; f[3] = r.v.w; }
-}
-
+// One thread owns V consecutive channels (one 8-byte access for f16, 16-byte for f32, or a single element) and TL
+// consecutive tokens. All TL + W - 1 row fragments are loaded before the first use, so a thread keeps TL + W - 1
+// loads in flight while its register footprint stays small enough for ~28 resident warps per SM.
 template <typename T, int V, int W, int TL>
 __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
 	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
@@ -161,12 +142,12 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 	const T* xb = x + b * seqlen * xs;
 	T* yb = y + b * seqlen * ys;
 
-	RawVec<T, V> raw[TL + W - 1];
+	Pack<T, V> raw[TL + W - 1];
 #pragma unroll
 	for (int i = 0; i < TL + W - 1; ++i)
 	{
 		const int64_t t = t0 - (W - 1) + i;
-		if (t >= 0 && t < seqlen) raw_load<T, V>(raw[i], xb + t * xs + c0);
+		if (t >= 0 && t < seqlen) raw[i].load(xb + t * xs + c0);
 	}
 
 	float wt[W][V], bs[V];
@@ -185,7 +166,7 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 		const int64_t t = t0 - (W - 1) + k;
 		if (t >= 0)
 		{
-			raw_unpack<T, V>(raw[k], win[k]);
+			raw[k].unpack(win[k]);
 		}
 		else
 		{
@@ -202,7 +183,7 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 		const int64_t t = t0 + i;
 		if (t < seqlen)
 		{
-			raw_unpack<T, V>(raw[i + W - 1], win[W - 1]);
+			raw[i + W - 1].unpack(win[W - 1]);
 			float out[V];
 #pragma unroll
 			for (int c = 0; c < V; ++c)
@@ -213,8 +194,9 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 				acc += bs[c];
 				out[c] = silu_f32(acc);
 			}
-			if constexpr (V > 1) Vec16<T>::store(yb + t * ys + c0, out);
-			else stf(yb + t * ys + c0, out[0]);
+			Pack<T, V> o;
+			o.pack(out);
+			o.store(yb + t * ys + c0);
 #pragma unroll
 			for (int k = 0; k < W - 1; ++k)
 #pragma unroll
@@ -324,10 +306,12 @@ template <typename T>
 static int conv1d_tok(const void* xv, int64_t xs, const void* wv, const void* bv, void* yv, int64_t ys, const void* init,
 	void* fin, int64_t batch, int64_t seqlen, int64_t dims, int W, cudaStream_t st)
 {
-	constexpr int E = Vec16<T>::E;
-	const bool vec = aligned16(xv) && aligned16(yv) && xs % E == 0 && ys % E == 0 && dims % E == 0;
+	constexpr int V = 4;  // 8 bytes of f16 / 16 bytes of f32 per access
+	const uintptr_t amask = V * sizeof(T) - 1;
+	const bool vec = (reinterpret_cast<uintptr_t>(xv) & amask) == 0 && (reinterpret_cast<uintptr_t>(yv) & amask) == 0 && xs % V == 0 &&
+		ys % V == 0 && dims % V == 0;
 	if (vec)
-		return launch_tok<T, E>(static_cast<const T*>(xv), xs, static_cast<const T*>(wv), static_cast<const T*>(bv),
+		return launch_tok<T, V>(static_cast<const T*>(xv), xs, static_cast<const T*>(wv), static_cast<const T*>(bv),
 			static_cast<T*>(yv), ys, static_cast<const T*>(init), static_cast<T*>(fin), batch, seqlen, dims, W, st);
 	return launch_tok<T, 1>(static_cast<const T*>(xv), xs, static_cast<const T*>(wv), static_cast<const T*>(bv),
 		static_cast<T*>(yv), ys, static_cast<const T*>(init), static_cast<T*>(fin), batch, seqlen, dims, W, st);

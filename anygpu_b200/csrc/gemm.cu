@@ -3,7 +3,8 @@
 // f16: persistent, warp-specialised tcgen05 kernel. One CTA per SM walks 128x256 output tiles:
 //   warp 0    : TMA producer  - 128B-swizzled [128x64] X tiles and [256x64] W tiles into a 4-stage shared-memory ring
 //   warp 1    : MMA issuer    - tcgen05.mma (M128 N256 K16, f16 in, fp32 accumulate) into one of two TMEM accumulators
-//   warps 2-5 : epilogue      - tcgen05.ld the finished accumulator, round to f16, 16-byte stores; overlaps the next tile's MMAs
+//   warps 2-5 : epilogue      - tcgen05.ld the finished accumulator, round to f16, stage 32x64 sub-tiles in shared memory and
+//                               write them with TMA stores (full 128-byte lines); overlaps the next tile's MMAs
 // W is consumed as stored: (in,out) row-major tiles are fed MN-major, (out,in) row-major tiles K-major. Tails in M, N
 // and K come from TMA zero fill and predicated stores. Every mbarrier wait is bounded.
 //
@@ -19,14 +20,16 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack to align the ring to 1024 B
+constexpr int STG_BYTES = 32 * 128;      // per-warp output staging tile: 32 rows x 64 f16, 128B-swizzled
+constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;  // 4 epilogue warps x 2 buffers
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_TOTAL + 1024;  // + slack to align the ring to 1024 B
 constexpr int THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;  // two 256-column fp32 accumulators
 }  // namespace gemm
 
 template <int B_MN>
 __global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-	const __grid_constant__ CUtensorMap tmB, __half* __restrict__ Y, int64_t ldy, int M, int N, int K, int m_tiles, int n_tiles,
+	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M, int N, int K, int m_tiles, int n_tiles,
 	uint32_t* err_word)
 {
 	using namespace gemm;
@@ -155,8 +158,12 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(cons
 	else
 	{
 		const int q = warp & 3;  // TMEM lane quadrant this warp may read
+		uint8_t* stg = smem_raw + (ring - smem_u32(smem_raw)) + STAGES * STAGE_BYTES + q * (2 * STG_BYTES);
+		const uint32_t stg_s = ring + STAGES * STAGE_BYTES + q * (2 * STG_BYTES);
+		if (lane == 0) prefetch_tmap(&tmY);
 		int acc = 0;
 		uint32_t acc_phase = 0;
+		uint32_t nchunk = 0;
 		for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
 		{
 			const int m0 = (tile % m_tiles) * BM;
@@ -167,38 +174,44 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(cons
 				goto role_done;
 			}
 			tc_fence_after();
-			const int row = m0 + q * 32 + lane;
-			__half* yrow = Y + static_cast<int64_t>(row) * ldy + n0;
 			const uint32_t t_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
 #pragma unroll 1
-			for (int c = 0; c < BN / 32; ++c)
+			for (int c = 0; c < BN / 64; ++c)
 			{
-				if (n0 + c * 32 >= N) break;  // warp-uniform
-				uint32_t r[32];
-				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 32), r);
+				if (n0 + c * 64 >= N) break;  // warp-uniform
+				uint32_t r0[32], r1[32];
+				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64), r0);
+				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64 + 32), r1);
+				// the staging buffer written two sub-tiles ago must have been read by its store
+				if (lane == 0) bulk_wait_group_read<1>();
+				__syncwarp();
 				tmem_ld_wait();
-				if (row < M)
+				const uint32_t buf = nchunk & 1u;
+				uint8_t* srow = stg + buf * STG_BYTES + lane * 128;
+#pragma unroll
+				for (int v = 0; v < 8; ++v)
 				{
+					const uint32_t* src = v < 4 ? r0 + v * 8 : r1 + (v - 4) * 8;
+					Half8 h;
 #pragma unroll
-					for (int v = 0; v < 4; ++v)
-					{
-						const int col = n0 + c * 32 + v * 8;
-						if (col < N)  // N % 8 == 0, so a vector is either fully inside or fully outside
-						{
-							Half8 h;
-#pragma unroll
-							for (int e = 0; e < 4; ++e)
-								h.h[e] = __floats2half2_rn(__uint_as_float(r[v * 8 + 2 * e]), __uint_as_float(r[v * 8 + 2 * e + 1]));
-							*reinterpret_cast<Half8*>(yrow + c * 32 + v * 8) = h;
-						}
-					}
+					for (int e = 0; e < 4; ++e) h.h[e] = __floats2half2_rn(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
+					*reinterpret_cast<Half8*>(srow + ((v ^ (lane & 7)) << 4)) = h;
 				}
+				fence_proxy_async_smem();
+				__syncwarp();
+				if (lane == 0)
+				{
+					tma_store_2d(&tmY, stg_s + buf * STG_BYTES, n0 + c * 64, m0 + q * 32);  // clipped at M and N
+					bulk_commit_group();
+				}
+				++nchunk;
 			}
 			tc_fence_before();
 			__syncwarp();
 			if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[acc]));
 			if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
 		}
+		if (lane == 0) bulk_wait_group<0>();  // stores must have left shared memory before the CTA exits
 	}
 
 role_done:
@@ -224,8 +237,10 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y))
 		return B200_ERR_MISALIGNED;
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-	CUtensorMap tmA, tmB;
-	int rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
+	CUtensorMap tmA, tmB, tmY;
+	int rc = tmap_2d_f16(&tmY, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(ldy), 64, 32);
+	if (rc) return rc;
+	rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
 	if (rc) return rc;
 	if (w_layout == B200_W_NK)
 		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, BN);
@@ -243,7 +258,7 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 			B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
 			attr_set[0] = true;
 		}
-		gemm_f16_tcgen05_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, y, ldy, static_cast<int>(M), static_cast<int>(N),
+		gemm_f16_tcgen05_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, static_cast<int>(M), static_cast<int>(N),
 			static_cast<int>(K), m_tiles, n_tiles, device_error_word());
 	}
 	else
@@ -253,7 +268,7 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 			B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
 			attr_set[1] = true;
 		}
-		gemm_f16_tcgen05_kernel<1><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, y, ldy, static_cast<int>(M), static_cast<int>(N),
+		gemm_f16_tcgen05_kernel<1><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, static_cast<int>(M), static_cast<int>(N),
 			static_cast<int>(K), m_tiles, n_tiles, device_error_word());
 	}
 	B200_LAUNCH_CHECK();

@@ -5,7 +5,9 @@
 //   2. chunk state     : states[b,c,h,p,n] = sum_l B[l,n] exp(dAcs[last]-dAcs[l]) dt[l] x[l,p]      (:51-80)
 //   3. state passing   : running state across chunks; states[c] is replaced by the state BEFORE c   (:83-106)
 //   4. chunk scan      : y = (C.B^T o decay o causal).(dt x) + exp(dAcs) C.prev^T + D x            (:109-160)
-// Workspace layout: dt[b,H,nc,Q] f32 | dAcs[b,H,nc,Q] f32 | states[b,nc,H,P,N] f32 | prev16[b,nc,H,P,N] f16
+// Workspace layout: dt[b,H,nc,Q] f32 | dAcs[b,H,nc,Q] f32 | colf[b,H,nc,Q] f32 | states[b,nc,H,P,N] f32 | prev16[b,nc,H,P,N] f16
+// colf[l] = exp(dAcs[end of l's 64-block] - dAcs[l]) * dt[l]: the column factor of the decay for score blocks that lie
+// entirely below the diagonal, where exp(dAcs[l]-dAcs[s]) = exp(dAcs[l]-dAcs[end]) * exp(dAcs[end]-dAcs[s]) with both exponents <= 0.
 // (prev16: the state before each chunk rounded to f16, the tensor-core operand of stage 4; the reference rounds the
 // passed states to the activation dtype as well, scripts/zamba2/mamba_chunk_scan_comb.py:211).
 #pragma once
@@ -23,6 +25,7 @@ struct SsdWorkspace
 {
 	float* dt;
 	float* dacs;
+	float* colf;
 	float* states;
 	__half* prev16;
 	size_t bytes;
@@ -34,10 +37,12 @@ inline SsdWorkspace ssd_carve(void* base, const SsdDims& d)
 	const size_t n_dt = static_cast<size_t>(d.batch) * d.H * d.nchunks * d.Q;
 	const size_t n_st = static_cast<size_t>(d.batch) * d.nchunks * d.H * d.P * d.N;
 	const size_t o1 = align_up(n_dt * sizeof(float), 256);
-	const size_t o2 = o1 + align_up(n_dt * sizeof(float), 256);
+	const size_t oc = o1 + align_up(n_dt * sizeof(float), 256);
+	const size_t o2 = oc + align_up(n_dt * sizeof(float), 256);
 	char* p = static_cast<char*>(base);
 	w.dt = reinterpret_cast<float*>(p);
 	w.dacs = reinterpret_cast<float*>(p + o1);
+	w.colf = reinterpret_cast<float*>(p + oc);
 	w.states = reinterpret_cast<float*>(p + o2);
 	const size_t o3 = o2 + align_up(n_st * sizeof(float), 256);
 	w.prev16 = reinterpret_cast<__half*>(p + o3);

@@ -13,7 +13,7 @@ constexpr int kCsHeads = 8;
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
 	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
-	float* __restrict__ dt_out, float* __restrict__ dacs_out)
+	float* __restrict__ dt_out, float* __restrict__ dacs_out, float* __restrict__ colf_out)
 {
 	extern __shared__ float sdt[];  // [Q][kCsHeads + 1]
 	const int64_t b = blockIdx.x / nchunks;
@@ -61,6 +61,9 @@ __global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict_
 			if (lane >= o) incl += n;
 		}
 		const float excl = incl - run;
+		// dAcs at the end of this lane's 64-position block (Q % 64 == 0: ep divides 64, a block is 64/ep consecutive lanes)
+		const bool blocks64 = (Q % 64) == 0 && (64 % ep) == 0;
+		const float blk_end = blocks64 ? __shfl_sync(0xffffffffu, excl + run, lane | (64 / ep - 1)) : 0.f;
 		const int64_t base = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
 #pragma unroll
 		for (int i = 0; i < 8; ++i)
@@ -68,8 +71,10 @@ __global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict_
 			const int l = lane * ep + i;
 			if (i < ep && l < Q)
 			{
+				const float dv = sdt[l * (kCsHeads + 1) + hh];
 				dacs_out[base + l] = excl + loc[i];
-				dt_out[base + l] = sdt[l * (kCsHeads + 1) + hh];
+				dt_out[base + l] = dv;
+				if (blocks64) colf_out[base + l] = __expf(blk_end - (excl + loc[i])) * dv;
 			}
 		}
 	}
@@ -82,7 +87,7 @@ int ssd_dt_cumsum(const T* dt, int64_t dts, const float* A, int a_is_log, const 
 	const dim3 g(static_cast<unsigned>(d.batch * d.nchunks), static_cast<unsigned>(cdiv(d.H, kCsHeads)));
 	const size_t smem = static_cast<size_t>(d.Q) * (kCsHeads + 1) * sizeof(float);
 	ssd_dt_cumsum_kernel<T><<<g, 256, smem, st>>>(dt, dts, A, a_is_log, dt_bias, dt_softplus, d.seqlen, d.H, d.Q, d.nchunks,
-		w.dt, w.dacs);
+		w.dt, w.dacs, w.colf);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }

@@ -37,9 +37,9 @@ constexpr int A_KB_BYTES = KB * 128 * 2;    // [2 atoms][64 l][64 m] f16 = 16 Ki
 }  // namespace cstate
 
 template <int NSTATE>
-__global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(const __grid_constant__ CUtensorMap tmB,
-	const __half* __restrict__ x, int64_t xs, const float* __restrict__ dt, const float* __restrict__ dacs,
-	float* __restrict__ states, int64_t seqlen, int H, int G, int Q, int nchunks, uint32_t* err_word)
+__global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(const __grid_constant__ CUtensorMap tmX,
+	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmS, const float* __restrict__ dt,
+	const float* __restrict__ dacs, int64_t seqlen, int H, int G, int Q, int nchunks, uint32_t* err_word)
 {
 	using namespace cstate;
 	constexpr int KA = NSTATE / 64;              // 64-wide n atoms
@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 	__shared__ uint64_t bar_in, bar_done;
 	__shared__ uint32_t tmem_slot;
 	__shared__ int abort_flag;
+	__shared__ float s_scale[2][256];            // exp(dAcs[last] - dAcs[l]) * dt[l] for the two heads
 
 	const int nkb = Q / KB;
 	const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -55,15 +56,13 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 	const uint32_t b_s = base + static_cast<uint32_t>(nkb) * A_KB_BYTES;
 	uint8_t* a_gen = smem_raw + (base - smem_u32(smem_raw));
 
-	const int warp = threadIdx.x >> 5;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int hp = blockIdx.x % (H / 2);
 	const int64_t bc = blockIdx.x / (H / 2);
 	const int c = static_cast<int>(bc % nchunks);
 	const int64_t b = bc / nchunks;
 	const int h0 = hp * 2;
 	const int g = h0 / (H / G);
-	const int64_t tok0 = b * seqlen + static_cast<int64_t>(c) * Q;
-	const int valid = static_cast<int>(min(static_cast<int64_t>(Q), seqlen - static_cast<int64_t>(c) * Q));
 	volatile int* abortp = &abort_flag;
 
 	if (threadIdx.x == 0)
@@ -85,64 +84,52 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 
 	if (threadIdx.x == 0)
 	{
+		// raw x (both heads) and B tiles of the whole chunk; rows past the end of the sequence arrive as zeros
+		prefetch_tmap(&tmX);
 		prefetch_tmap(&tmB);
-		mbar_arrive_expect_tx(smem_u32(&bar_in), static_cast<uint32_t>(nkb) * B_KB_BYTES);
+		const uint32_t in = smem_u32(&bar_in);
+		mbar_arrive_expect_tx(in, static_cast<uint32_t>(nkb) * (A_KB_BYTES + B_KB_BYTES));
 		for (int kb = 0; kb < nkb; ++kb)
+		{
+#pragma unroll
+			for (int j = 0; j < 2; ++j)
+				tma_load_3d(a_s + kb * A_KB_BYTES + j * (KB * 128), &tmX, in, (h0 + j) * 64, c * Q + kb * KB, static_cast<int>(b));
 #pragma unroll
 			for (int a = 0; a < KA; ++a)
-				tma_load_3d(b_s + kb * B_KB_BYTES + a * (KB * 128), &tmB, smem_u32(&bar_in), g * NSTATE + a * 64, c * Q + kb * KB,
-					static_cast<int>(b));
+				tma_load_3d(b_s + kb * B_KB_BYTES + a * (KB * 128), &tmB, in, g * NSTATE + a * 64, c * Q + kb * KB, static_cast<int>(b));
+		}
 	}
-
-	// scaled x -> MN-major A tiles. 16 chunks of 8 m-values per l row (2 heads x 64 p).
+	// per-row scale factors while the tiles are in flight
 	{
 		const int64_t cb0 = ((b * H + h0) * nchunks + c) * static_cast<int64_t>(Q);
-		const int64_t cb1 = cb0 + static_cast<int64_t>(nchunks) * Q;
-		const float last0 = dacs[cb0 + Q - 1], last1 = dacs[cb1 + Q - 1];
-		const int chunk = threadIdx.x & 15;
-		const int j = chunk >> 3, cj = chunk & 7;  // atom (= head of the pair), 16-byte chunk inside the atom row
-		const int64_t cbh = j ? cb1 : cb0;
-		const float last = j ? last1 : last0;
-		// 8 rows per batch: all global loads of a batch are issued before the first use
-		constexpr int RB = 8, RSTEP = THREADS / 16;
-		for (int lbase = threadIdx.x >> 4; lbase < Q; lbase += RB * RSTEP)
+		for (int idx = threadIdx.x; idx < 2 * Q; idx += THREADS)
 		{
-			Half8 in[RB];
-			float sc[RB];
+			const int j = idx >= Q ? 1 : 0;
+			const int l = idx - j * Q;
+			const int64_t cbh = cb0 + static_cast<int64_t>(j) * nchunks * Q;
+			s_scale[j][l] = __expf(dacs[cbh + Q - 1] - dacs[cbh + l]) * dt[cbh + l];
+		}
+	}
+	__syncthreads();
+	const bool loaded = mbar_wait(smem_u32(&bar_in), 0, abortp);
+	if (loaded)
+	{
+		// scale x in place: the TMA layout (64 k-rows of 128 B per atom, 16-byte chunks XOR-swizzled by row) is the
+		// MN-major A-operand layout already, and a row-wise scale keeps every element where it is
+		const int chunk = threadIdx.x & 15;
+		const int j = chunk >> 3, cj = chunk & 7;
+		for (int l = threadIdx.x >> 4; l < Q; l += THREADS / 16)
+		{
+			const int kb = l >> 6, lk = l & 63;
+			const uint32_t off = static_cast<uint32_t>(kb) * A_KB_BYTES + static_cast<uint32_t>(j) * (KB * 128) +
+				static_cast<uint32_t>(lk) * 128 + (static_cast<uint32_t>(cj ^ (lk & 7)) << 4);
+			Half8* p = reinterpret_cast<Half8*>(a_gen + off);
+			float f[8];
+			unpack8(*p, f);
+			const float sc = s_scale[j][l];
 #pragma unroll
-			for (int u = 0; u < RB; ++u)
-			{
-				const int l = lbase + u * RSTEP;
-				if (l < valid)
-				{
-					in[u] = *reinterpret_cast<const Half8*>(x + (tok0 + l) * xs + static_cast<int64_t>(h0) * 64 + chunk * 8);
-					sc[u] = __expf(last - dacs[cbh + l]) * dt[cbh + l];
-				}
-			}
-#pragma unroll
-			for (int u = 0; u < RB; ++u)
-			{
-				const int l = lbase + u * RSTEP;
-				if (l >= Q) break;
-				Half8 v;
-				if (l < valid)
-				{
-					float f[8];
-					unpack8(in[u], f);
-#pragma unroll
-					for (int e = 0; e < 8; ++e) f[e] *= sc[u];
-					v = pack8(f);
-				}
-				else
-				{
-#pragma unroll
-					for (int e = 0; e < 4; ++e) v.h[e] = __floats2half2_rn(0.f, 0.f);
-				}
-				const int kb = l >> 6, lk = l & 63;
-				const uint32_t off = static_cast<uint32_t>(kb) * A_KB_BYTES + static_cast<uint32_t>(j) * (KB * 128) +
-					static_cast<uint32_t>(lk) * 128 + (static_cast<uint32_t>(cj ^ (lk & 7)) << 4);
-				*reinterpret_cast<Half8*>(a_gen + off) = v;
-			}
+			for (int e = 0; e < 8; ++e) f[e] *= sc;
+			*p = pack8(f);
 		}
 	}
 	fence_proxy_async_smem();
@@ -150,7 +137,7 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 
 	if (threadIdx.x == 0)
 	{
-		if (mbar_wait(smem_u32(&bar_in), 0, abortp))
+		if (loaded)
 		{
 			tc_fence_after();
 			constexpr uint32_t idesc = make_idesc_f16(128, NSTATE, 1, 1);
@@ -171,11 +158,11 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 		}
 	}
 	__syncwarp();
-	if (mbar_wait(smem_u32(&bar_done), 0, abortp))
+	if (loaded && mbar_wait(smem_u32(&bar_done), 0, abortp))
 	{
+		// the A tiles are dead now: each warp stages its 32 x NSTATE fp32 rows there and stores them with one TMA store
 		tc_fence_after();
-		const int m = threadIdx.x;  // row of D: head h0 + m/64, p = m%64
-		float* out = states + ((((b * nchunks + c) * H + h0 + (m >> 6)) * 64) + (m & 63)) * static_cast<int64_t>(NSTATE);
+		uint8_t* stg = a_gen + warp * (32 * NSTATE * 4);
 		const uint32_t t_row = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
 #pragma unroll 1
 		for (int cc = 0; cc < NSTATE / 32; ++cc)
@@ -183,13 +170,24 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 			uint32_t r[32];
 			tmem_ld_32x32(t_row + static_cast<uint32_t>(cc * 32), r);
 			tmem_ld_wait();
+			float4* dst = reinterpret_cast<float4*>(stg + lane * (NSTATE * 4) + cc * 128);
 #pragma unroll
 			for (int v = 0; v < 8; ++v)
-				*reinterpret_cast<float4*>(out + cc * 32 + v * 4) = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-					__uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+				dst[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]),
+					__uint_as_float(r[4 * v + 3]));
+		}
+		fence_proxy_async_smem();
+		__syncwarp();
+		if (lane == 0)
+		{
+			// states viewed as [b*nc*H*64 rows, NSTATE]; this warp owns 32 consecutive rows (head h0 + warp/2)
+			const int row0 = static_cast<int>(((b * nchunks + c) * H + h0) * 64) + warp * 32;
+			tma_store_2d(&tmS, a_s + warp * (32 * NSTATE * 4), 0, row0);
+			bulk_commit_group();
+			bulk_wait_group<0>();
 		}
 	}
-	else if ((threadIdx.x & 31) == 0)
+	else if (lane == 0)
 	{
 		report_timeout(err_word, kErrScanWait);
 	}
@@ -214,9 +212,12 @@ constexpr int NX = 4;     // X ring stages
 constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 compute
 constexpr int S_STAGE = LB * KB * 2;  // 16 KiB
 constexpr int X_STAGE = KB * 64 * 2;  // 8 KiB
+constexpr int H_FLOATS = 3 * 256;     // per-head dAcs | dt | colf rows of the chunk (Q <= 256)
 constexpr uint32_t TMEM_COLS = 512;   // CB [0,256) | Y0 Z0 [256,384) | Y1 Z1 [384,512)
 
-template <int NSTATE, int NS>
+constexpr int Y_STAGE = 32 * 64;      // per-warp output staging: 32 rows x 32 f16 (64 B rows, dense)
+
+template <int NSTATE, int NS, int NYB>
 struct Layout
 {
 	static constexpr int KA = NSTATE / 64;
@@ -228,23 +229,25 @@ struct Layout
 	static constexpr int OFF_S = OFF_B + B_BYTES;
 	static constexpr int OFF_X = OFF_S + NS * S_STAGE;
 	static constexpr int OFF_P = OFF_X + NX * X_STAGE;
-	static constexpr int TOTAL = OFF_P + 2 * P_BYTES + 1024;
+	static constexpr int OFF_H = OFF_P + 2 * P_BYTES;
+	static constexpr int OFF_Y = OFF_H + 2 * H_FLOATS * 4;   // [8 compute warps][NYB buffers][Y_STAGE]
+	static constexpr int TOTAL = OFF_Y + 8 * NYB * Y_STAGE + 1024;
 };
 }  // namespace cscan
 
-template <int NSTATE, int NS>
+template <int NSTATE, int NS, int NYB>
 __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(const __grid_constant__ CUtensorMap tmX,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmP,
-	const __half* __restrict__ x, int64_t xs, __half* __restrict__ y, int64_t ys, const float* __restrict__ D,
-	const float* __restrict__ dt, const float* __restrict__ dacs, int64_t seqlen, int H, int G, int Q, int nchunks,
-	int heads_per_cta, uint32_t* err_word)
+	const __grid_constant__ CUtensorMap tmY, const float* __restrict__ D,
+	const float* __restrict__ dt, const float* __restrict__ dacs, const float* __restrict__ colf, int64_t seqlen, int H, int G,
+	int Q, int nchunks, int heads_per_cta, uint32_t* err_word)
 {
 	using namespace cscan;
-	using L = Layout<NSTATE, NS>;
+	using L = Layout<NSTATE, NS, NYB>;
 	constexpr int KA = L::KA;
 	extern __shared__ uint8_t smem_raw[];
 	__shared__ uint64_t bar_in, bar_cb, s_full[NS], s_empty[NS], x_full[NX], x_empty[NX], p_full[2], p_empty[2], acc_full[2],
-		acc_empty[2];
+		acc_empty[2], h_full[2], h_empty[2];
 	__shared__ uint32_t tmem_slot;
 	__shared__ int abort_flag;
 
@@ -268,7 +271,6 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 	const int l0 = lb * LB;
 	const int s_count = l0 + LB;        // causal extent of this row block
 	const int nkb = s_count / KB;       // 2 or 4
-	const int64_t tok0 = b * seqlen + static_cast<int64_t>(c) * Q;
 	const int valid = static_cast<int>(min(static_cast<int64_t>(Q), seqlen - static_cast<int64_t>(c) * Q));
 
 	if (threadIdx.x == 0)
@@ -284,6 +286,8 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 			mbar_init(smem_u32(&p_empty[i]), 1);
 			mbar_init(smem_u32(&acc_full[i]), 1);
 			mbar_init(smem_u32(&acc_empty[i]), 8);
+			mbar_init(smem_u32(&h_full[i]), 1);
+			mbar_init(smem_u32(&h_empty[i]), 8);
 		}
 		fence_mbar_init();
 	}
@@ -320,6 +324,22 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 			for (int i = 0; i < nheads; ++i)
 			{
 				const int h = h_begin + i;
+				const int buf = i & 1;
+				// per-head rows of dAcs, dt and colf for this chunk
+				if (!mbar_wait(smem_u32(&h_empty[buf]), ((i >> 1) & 1) ^ 1u, abortp))
+				{
+					report_timeout(err_word, kErrProducerWait);
+					goto role_done;
+				}
+				{
+					const int64_t cbase = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+					const uint32_t hb = base + L::OFF_H + buf * (H_FLOATS * 4);
+					const uint32_t bytes = static_cast<uint32_t>(Q) * 4;
+					mbar_arrive_expect_tx(smem_u32(&h_full[buf]), 3 * bytes);
+					bulk_load_1d(hb, dacs + cbase, bytes, smem_u32(&h_full[buf]));
+					bulk_load_1d(hb + 1024, dt + cbase, bytes, smem_u32(&h_full[buf]));
+					bulk_load_1d(hb + 2048, colf + cbase, bytes, smem_u32(&h_full[buf]));
+				}
 				for (int kb = 0; kb < nkb; ++kb, ++kbc)
 				{
 					const int st = kbc % NX;
@@ -331,7 +351,6 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 					mbar_arrive_expect_tx(smem_u32(&x_full[st]), X_STAGE);
 					tma_load_3d(base + L::OFF_X + st * X_STAGE, &tmX, smem_u32(&x_full[st]), h * 64, c * Q + kb * KB, static_cast<int>(b));
 				}
-				const int buf = i & 1;
 				if (!mbar_wait(smem_u32(&p_empty[buf]), ((i >> 1) & 1) ^ 1u, abortp))
 				{
 					report_timeout(err_word, kErrProducerWait);
@@ -430,10 +449,18 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 		const int half = (warp - 2) >> 2;  // 0: warps 2-5, 1: warps 6-9
 		const int r = q * 32 + lane;      // row inside the block
 		const int l = l0 + r;
+		const int wrow0 = l0 + q * 32;    // first row of this warp
 		const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+		const int cw = warp - 2;          // compute warp index 0..7
+		uint8_t* ystg = gen + L::OFF_Y + cw * (NYB * Y_STAGE);
+		const uint32_t ystg_s = base + L::OFF_Y + cw * (NYB * Y_STAGE);
 		float dl2_prev = 0.f;
+		uint32_t nstore = 0;
 		bool cb_ready = false;
+		if (lane == 0) prefetch_tmap(&tmY);
 
+		// y[l, h, half*32 .. +31] = Y + exp(dAcs[l]) * Z, staged per warp and written by one TMA store (rows past the end
+		// of the sequence are clipped by the store). The D*x skip term is already inside Y: D sits on the diagonal of S.
 		auto epilogue = [&](int i, float dl2) -> bool {
 			const int buf = i & 1;
 			const int h = h_begin + i;
@@ -443,35 +470,44 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 			const uint32_t col = 256u + static_cast<uint32_t>(buf * 128 + half * 32);
 			tmem_ld_32x32(t_lane + col, yr);
 			tmem_ld_32x32(t_lane + col + 64u, zr);
+			if (lane == 0) bulk_wait_group_read<NYB - 1>();  // the staging buffer about to be rewritten has been read
 			tmem_ld_wait();
 			tc_fence_before();
 			__syncwarp();
 			if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));
-			if (l < valid)
+			const float dec = ex2_approx(dl2);
+			const uint32_t sb = (nstore % NYB) * Y_STAGE;
+#pragma unroll
+			for (int v = 0; v < 4; ++v)
 			{
-				const float dec = ex2_approx(dl2);
-				const float dh = D ? D[h] : 0.f;
-				const __half* xp = x + (tok0 + l) * xs + static_cast<int64_t>(h) * 64 + half * 32;
-				__half* yp = y + (tok0 + l) * ys + static_cast<int64_t>(h) * 64 + half * 32;
+				float o[8];
 #pragma unroll
-				for (int v = 0; v < 4; ++v)
-				{
-					float xv[8], o[8];
-					unpack8(*reinterpret_cast<const Half8*>(xp + v * 8), xv);
-#pragma unroll
-					for (int e = 0; e < 8; ++e)
-						o[e] = __uint_as_float(yr[v * 8 + e]) + dec * __uint_as_float(zr[v * 8 + e]) + dh * xv[e];
-					*reinterpret_cast<Half8*>(yp + v * 8) = pack8(o);
-				}
+				for (int e = 0; e < 8; ++e) o[e] = fmaf(dec, __uint_as_float(zr[v * 8 + e]), __uint_as_float(yr[v * 8 + e]));
+				*reinterpret_cast<Half8*>(ystg + sb + lane * 64 + v * 16) = pack8(o);
 			}
+			fence_proxy_async_smem();
+			__syncwarp();
+			if (lane == 0)
+			{
+				tma_store_3d(&tmY, ystg_s + sb, h * 64 + half * 32, c * Q + wrow0, static_cast<int>(b));
+				bulk_commit_group();
+			}
+			++nstore;
 			return true;
 		};
 
 		for (int i = 0; i < nheads; ++i)
 		{
 			const int h = h_begin + i;
-			const int64_t cbase = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
-			const float dl2 = dacs[cbase + l] * kLog2e;
+			const int buf = i & 1;
+			const float* hd = reinterpret_cast<const float*>(gen + L::OFF_H + buf * (H_FLOATS * 4));  // dAcs | dt | colf
+			const float dh = D ? __ldg(D + h) : 0.f;
+			if (!mbar_wait(smem_u32(&h_full[buf]), (i >> 1) & 1, abortp))
+			{
+				if (lane == 0) report_timeout(err_word, kErrScanWait);
+				goto role_done;
+			}
+			const float dl2 = hd[l] * kLog2e;
 			for (int kb = half; kb < nkb; kb += 2)
 			{
 				const int kbc = i * nkb + kb;
@@ -492,42 +528,90 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 				}
 				tc_fence_after();
 				uint8_t* srow = gen + L::OFF_S + ss * S_STAGE + r * 128;
-#pragma unroll
-				for (int c2 = 0; c2 < 2; ++c2)
+				const int s_first = kb * KB;
+				if (s_first > wrow0 + 31)
 				{
-					uint32_t cbv[32];
-					tmem_ld_32x32(t_lane + static_cast<uint32_t>(kb * KB + c2 * 32), cbv);
-					tmem_ld_wait();
-					const int s0 = kb * KB + c2 * 32;
-					const float4* dsp = reinterpret_cast<const float4*>(dacs + cbase + s0);
-					const float4* dtp = reinterpret_cast<const float4*>(dt + cbase + s0);
+					// the whole 32 x 64 block lies above the diagonal
+					Half8 zero;
 #pragma unroll
-					for (int v = 0; v < 4; ++v)  // 8 s-values -> one 16-byte chunk
+					for (int e = 0; e < 4; ++e) zero.h[e] = __floats2half2_rn(0.f, 0.f);
+#pragma unroll
+					for (int chunk = 0; chunk < 8; ++chunk) *reinterpret_cast<Half8*>(srow + (chunk << 4)) = zero;
+				}
+				else if (s_first + KB - 1 <= wrow0 - 1)
+				{
+					// entirely below the diagonal: decay = exp(dAcs[l] - dAcs[block end]) * colf[s], both factors <= 1
+					const float rk = ex2_approx(fmaf(hd[s_first + KB - 1], -kLog2e, dl2));
+#pragma unroll
+					for (int c2 = 0; c2 < 2; ++c2)
 					{
-						float o[8];
+						uint32_t cbv[32];
+						tmem_ld_32x32(t_lane + static_cast<uint32_t>(s_first + c2 * 32), cbv);
+						tmem_ld_wait();
+						const float4* cfp = reinterpret_cast<const float4*>(hd + 512 + s_first + c2 * 32);
 #pragma unroll
-						for (int hq = 0; hq < 2; ++hq)
+						for (int v = 0; v < 4; ++v)
 						{
-							const float4 ds = __ldg(dsp + v * 2 + hq);
-							const float4 dv = __ldg(dtp + v * 2 + hq);
-							const float dsa[4] = { ds.x, ds.y, ds.z, ds.w };
-							const float dta[4] = { dv.x, dv.y, dv.z, dv.w };
+							float o[8];
 #pragma unroll
-							for (int e = 0; e < 4; ++e)
+							for (int hq = 0; hq < 2; ++hq)
 							{
-								const int j = v * 8 + hq * 4 + e;
-								const float w = ex2_approx(fmaf(dsa[e], -kLog2e, dl2)) * dta[e];
-								o[hq * 4 + e] = (s0 + j <= l) ? __uint_as_float(cbv[j]) * w : 0.f;
+								const float4 cf = cfp[v * 2 + hq];
+								const float cfa[4] = { cf.x, cf.y, cf.z, cf.w };
+#pragma unroll
+								for (int e = 0; e < 4; ++e) o[hq * 4 + e] = __uint_as_float(cbv[v * 8 + hq * 4 + e]) * (rk * cfa[e]);
 							}
+							const int chunk = c2 * 4 + v;
+							*reinterpret_cast<Half8*>(srow + ((chunk ^ (r & 7)) << 4)) = pack8(o);
 						}
-						const int chunk = c2 * 4 + v;
-						*reinterpret_cast<Half8*>(srow + ((chunk ^ (r & 7)) << 4)) = pack8(o);
+					}
+				}
+				else
+				{
+					// block crossed by the diagonal: exact exp of the (non-positive) difference, causal mask, and the
+					// D skip connection as S[l,l] += D (so that S.x carries D*x)
+#pragma unroll
+					for (int c2 = 0; c2 < 2; ++c2)
+					{
+						uint32_t cbv[32];
+						tmem_ld_32x32(t_lane + static_cast<uint32_t>(s_first + c2 * 32), cbv);
+						tmem_ld_wait();
+						const int s0 = s_first + c2 * 32;
+						const float4* dsp = reinterpret_cast<const float4*>(hd + s0);
+						const float4* dtp = reinterpret_cast<const float4*>(hd + 256 + s0);
+#pragma unroll
+						for (int v = 0; v < 4; ++v)  // 8 s-values -> one 16-byte chunk
+						{
+							float o[8];
+#pragma unroll
+							for (int hq = 0; hq < 2; ++hq)
+							{
+								const float4 ds = dsp[v * 2 + hq];
+								const float4 dv = dtp[v * 2 + hq];
+								const float dsa[4] = { ds.x, ds.y, ds.z, ds.w };
+								const float dta[4] = { dv.x, dv.y, dv.z, dv.w };
+#pragma unroll
+								for (int e = 0; e < 4; ++e)
+								{
+									const int j = v * 8 + hq * 4 + e;
+									const float w = ex2_approx(fmaf(dsa[e], -kLog2e, dl2)) * dta[e];
+									float val = (s0 + j <= l) ? __uint_as_float(cbv[j]) * w : 0.f;
+									if (s0 + j == l) val += dh;
+									o[hq * 4 + e] = val;
+								}
+							}
+							const int chunk = c2 * 4 + v;
+							*reinterpret_cast<Half8*>(srow + ((chunk ^ (r & 7)) << 4)) = pack8(o);
+						}
 					}
 				}
 				fence_proxy_async_smem();
 				__syncwarp();
 				if (lane == 0) mbar_arrive(smem_u32(&s_full[ss]));
 			}
+			// this warp no longer reads the per-head rows
+			__syncwarp();
+			if (lane == 0) mbar_arrive(smem_u32(&h_empty[buf]));
 			if (i > 0 && !epilogue(i - 1, dl2_prev))
 			{
 				if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
@@ -539,6 +623,7 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 		{
 			if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
 		}
+		if (lane == 0) bulk_wait_group<0>();  // stores must have left shared memory before the CTA exits
 	}
 
 role_done:
@@ -572,9 +657,14 @@ bool ssd_tc_supported(const SsdDims& d, const void* x, int64_t xs, const void* B
 
 int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
 {
-	CUtensorMap tmB;
-	int rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, static_cast<uint64_t>(d.seqlen), static_cast<uint64_t>(d.batch),
-		static_cast<uint64_t>(bs), static_cast<uint64_t>(d.seqlen) * bs, 64, 64);
+	CUtensorMap tmX, tmB, tmS;
+	const uint64_t L = static_cast<uint64_t>(d.seqlen), Bt = static_cast<uint64_t>(d.batch);
+	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(xs), L * xs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(bs), L * bs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_2d_f32_linear(&tmS, w.states, static_cast<uint64_t>(d.batch) * d.nchunks * d.H * 64, static_cast<uint64_t>(d.N),
+		static_cast<uint64_t>(d.N), static_cast<uint32_t>(d.N), 32);
 	if (rc) return rc;
 	const int nkb = d.Q / 64;
 	const unsigned grid = static_cast<unsigned>(d.batch * d.nchunks * (d.H / 2));
@@ -583,16 +673,16 @@ int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs
 		const int smem = nkb * (cstate::A_KB_BYTES + 64 * 128) + 1024;
 		static bool set = false;
 		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_state_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (cstate::A_KB_BYTES + 64 * 128) + 1024)); set = true; }
-		ssd_chunk_state_tc_kernel<64><<<grid, cstate::THREADS, smem, st>>>(tmB, x, xs, w.dt, w.dacs, w.states, d.seqlen, d.H, d.G, d.Q,
-			d.nchunks, device_error_word());
+		ssd_chunk_state_tc_kernel<64><<<grid, cstate::THREADS, smem, st>>>(tmX, tmB, tmS, w.dt, w.dacs, d.seqlen, d.H, d.G, d.Q, d.nchunks,
+			device_error_word());
 	}
 	else
 	{
 		const int smem = nkb * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024;
 		static bool set = false;
 		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_state_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024)); set = true; }
-		ssd_chunk_state_tc_kernel<128><<<grid, cstate::THREADS, smem, st>>>(tmB, x, xs, w.dt, w.dacs, w.states, d.seqlen, d.H, d.G, d.Q,
-			d.nchunks, device_error_word());
+		ssd_chunk_state_tc_kernel<128><<<grid, cstate::THREADS, smem, st>>>(tmX, tmB, tmS, w.dt, w.dacs, d.seqlen, d.H, d.G, d.Q, d.nchunks,
+			device_error_word());
 	}
 	B200_LAUNCH_CHECK();
 	return B200_OK;
@@ -601,7 +691,7 @@ int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs
 int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D, __half* y,
 	int64_t ys, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
 {
-	CUtensorMap tmX, tmB, tmC, tmP;
+	CUtensorMap tmX, tmB, tmC, tmP, tmY;
 	const uint64_t L = static_cast<uint64_t>(d.seqlen), Bt = static_cast<uint64_t>(d.batch);
 	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(xs), L * xs, 64, 64);
 	if (rc) return rc;
@@ -612,6 +702,8 @@ int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs,
 	rc = tmap_2d_f16(&tmP, w.prev16, static_cast<uint64_t>(d.batch) * d.nchunks * d.H * 64, static_cast<uint64_t>(d.N),
 		static_cast<uint64_t>(d.N), 64, 64);
 	if (rc) return rc;
+	rc = tmap_3d_f16_linear(&tmY, y, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(ys), L * ys, 32, 32);
+	if (rc) return rc;
 	const int lblocks = d.Q / cscan::LB;
 	const int hpg = d.H / d.G;
 	// enough CTAs to fill the machine, but as many heads per CTA as possible so that CB is computed rarely
@@ -621,18 +713,18 @@ int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs,
 	const dim3 grid(static_cast<unsigned>(base_ctas), static_cast<unsigned>(cdiv(hpg, hpc)));
 	if (d.N == 64)
 	{
-		using Lt = cscan::Layout<64, 4>;
+		using Lt = cscan::Layout<64, 4, 2>;
 		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<64, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
-		ssd_chunk_scan_tc_kernel<64, 4><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, x, xs, y, ys, D, w.dt, w.dacs, d.seqlen,
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<64, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		ssd_chunk_scan_tc_kernel<64, 4, 2><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
 			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
 	}
 	else
 	{
-		using Lt = cscan::Layout<128, 2>;
+		using Lt = cscan::Layout<128, 2, 1>;
 		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
-		ssd_chunk_scan_tc_kernel<128, 2><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, x, xs, y, ys, D, w.dt, w.dacs, d.seqlen,
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<128, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		ssd_chunk_scan_tc_kernel<128, 2, 1><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
 			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
 	}
 	B200_LAUNCH_CHECK();

@@ -90,6 +90,41 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
 		: "memory");
 }
 
+// Tiled stores shared -> global (bulk async-group completion). Rows / columns outside the tensor are clipped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int x, int y)
+{
+	asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+		::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y)
+		: "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* m, uint32_t src, int x, int y, int z)
+{
+	asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+		::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y), "r"(z)
+		: "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read()
+{
+	asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Waits until at most N of this thread's bulk groups are still in flight at all (global writes performed).
+template <int N>
+__device__ __forceinline__ void bulk_wait_group()
+{
+	asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// 1-D bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes), completion on `bar`.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+{
+	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+		::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+		: "memory");
+}
+
 // ---- tensor memory -----------------------------------------------------------------------------------------
 // Whole-warp calls. ncols: power of two in [32, 512].
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols)
@@ -175,5 +210,11 @@ int tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 // Out-of-range coordinates in any dimension read zeros, so a per-sequence row tail never picks up the next sequence.
 int tmap_3d_f16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems, uint64_t s2_elems,
 	uint32_t box0, uint32_t box1);
+
+// Unswizzled maps used by TMA STORES of small per-warp tiles (rows of box0 elements, dense in shared memory).
+int tmap_3d_f16_linear(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems,
+	uint64_t s2_elems, uint32_t box0, uint32_t box1);
+int tmap_2d_f32_linear(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
+	uint32_t box_rows);
 
 }  // namespace b200

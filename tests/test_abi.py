@@ -58,7 +58,7 @@ def test_null_and_shape_validation_needs_no_gpu():
 def test_workspace_queries():
     lib = capi.load()
     n = lib.b200_mamba_chunk_scan_combined_workspace_bytes(4, 2048, 64, 64, 1, 64, 256)
-    assert n == 2 * 4 * 64 * 2048 * 4 + 4 * 8 * 64 * 64 * 64 * (4 + 2)
+    assert n == 3 * 4 * 64 * 2048 * 4 + 4 * 8 * 64 * 64 * 64 * (4 + 2)
     cfg = capi.Mamba2Config(2048, 4096, 64, 64, 64, 1, 4, 256, 0, 1e-5)
     T = 4 * 2048
     want = T * 8384 * 2 + T * 4224 * 2 + T * 4096 * 2 + n
