@@ -16,24 +16,36 @@ namespace b200 {
 // ---- f16 tcgen05 kernel -----------------------------------------------------------------------------------
 
 namespace gemm {
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2;  // 16 KiB
-constexpr int B_BYTES = BN * BK * 2;  // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BK = 64;
+constexpr int A_BYTES = BM * BK * 2;     // 16 KiB
 constexpr int STG_BYTES = 32 * 128;      // per-warp output staging tile: 32 rows x 64 f16, 128B-swizzled
-constexpr int STG_TOTAL = 4 * 2 * STG_BYTES;  // 4 epilogue warps x 2 buffers
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_TOTAL + 1024;  // + slack to align the ring to 1024 B
 constexpr int THREADS = 192;
-constexpr uint32_t TMEM_COLS = 512;  // two 256-column fp32 accumulators
+
+// Two tile shapes: 128x256 (one CTA per SM) for large problems, 128x64 (two CTAs per SM, all CTAs resident at once)
+// for skinny ones such as the decode projections, where the job is to stream W once at full HBM bandwidth.
+template <int BN_, int STAGES_, int STG_BUFS_, int MIN_CTAS_>
+struct Cfg
+{
+	static constexpr int BN = BN_, STAGES = STAGES_, STG_BUFS = STG_BUFS_, MIN_CTAS = MIN_CTAS_;
+	static constexpr int B_BYTES = BN * BK * 2;
+	static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+	static constexpr int STG_TOTAL = 4 * STG_BUFS * STG_BYTES;
+	static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_TOTAL + 1024;  // + slack to align the ring to 1024 B
+	static constexpr uint32_t TMEM_COLS = 2 * BN;  // two fp32 accumulators
+};
+using CfgWide = Cfg<256, 4, 2, 1>;
+using CfgSkinny = Cfg<64, 3, 2, 2>;  // 3 x 24 KiB ring + 32 KiB staging: two CTAs fit one SM
 }  // namespace gemm
 
-template <int B_MN>
-__global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+template <int B_MN, class C>
+__global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M, int N, int K, int m_tiles, int n_tiles,
 	uint32_t* err_word)
 {
 	using namespace gemm;
 	using namespace tc;
+	constexpr int BN = C::BN, STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, STG_BUFS = C::STG_BUFS;
+	constexpr uint32_t TMEM_COLS = C::TMEM_COLS;
 	extern __shared__ uint8_t smem_raw[];
 	__shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2];
 	__shared__ uint32_t tmem_slot;
@@ -96,12 +108,12 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(cons
 					tma_load_2d(a_s, &tmA, full, kb * BK, m0);
 					if (B_MN == 0)
 					{
-						tma_load_2d(b_s, &tmB, full, kb * BK, n0);  // W^T [N,K]: one [256 n x 64 k] box
+						tma_load_2d(b_s, &tmB, full, kb * BK, n0);  // W^T [N,K]: one [BN n x 64 k] box
 					}
 					else
 					{
 #pragma unroll
-						for (int j = 0; j < BN / 64; ++j)  // W [K,N]: four [64 k x 64 n] boxes
+						for (int j = 0; j < BN / 64; ++j)  // W [K,N]: BN/64 boxes of [64 k x 64 n]
 							tma_load_2d(b_s + j * (BK * 128), &tmB, full, n0 + j * 64, kb * BK);
 					}
 					if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -158,8 +170,8 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(cons
 	else
 	{
 		const int q = warp & 3;  // TMEM lane quadrant this warp may read
-		uint8_t* stg = smem_raw + (ring - smem_u32(smem_raw)) + STAGES * STAGE_BYTES + q * (2 * STG_BYTES);
-		const uint32_t stg_s = ring + STAGES * STAGE_BYTES + q * (2 * STG_BYTES);
+		uint8_t* stg = smem_raw + (ring - smem_u32(smem_raw)) + STAGES * STAGE_BYTES + q * (STG_BUFS * STG_BYTES);
+		const uint32_t stg_s = ring + STAGES * STAGE_BYTES + q * (STG_BUFS * STG_BYTES);
 		if (lane == 0) prefetch_tmap(&tmY);
 		int acc = 0;
 		uint32_t acc_phase = 0;
@@ -182,11 +194,11 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) gemm_f16_tcgen05_kernel(cons
 				uint32_t r0[32], r1[32];
 				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64), r0);
 				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64 + 32), r1);
-				// the staging buffer written two sub-tiles ago must have been read by its store
-				if (lane == 0) bulk_wait_group_read<1>();
+				// the staging buffer about to be rewritten must have been read by its store
+				if (lane == 0) bulk_wait_group_read<STG_BUFS - 1>();
 				__syncwarp();
 				tmem_ld_wait();
-				const uint32_t buf = nchunk & 1u;
+				const uint32_t buf = nchunk % STG_BUFS;
 				uint8_t* srow = stg + buf * STG_BYTES + lane * 128;
 #pragma unroll
 				for (int v = 0; v < 8; ++v)
@@ -230,6 +242,25 @@ role_done:
 	}
 }
 
+template <int B_MN, class C>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st)
+{
+	using namespace gemm;
+	static bool attr_set = false;
+	if (!attr_set)
+	{
+		B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<B_MN, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+		attr_set = true;
+	}
+	const int m_tiles = static_cast<int>(cdiv(M, BM)), n_tiles = static_cast<int>(cdiv(N, C::BN));
+	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+	const int64_t slots = static_cast<int64_t>(kNumSMs) * C::MIN_CTAS;
+	const unsigned grid = static_cast<unsigned>(tiles < slots ? tiles : slots);
+	gemm_f16_tcgen05_kernel<B_MN, C><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles, n_tiles, device_error_word());
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
 static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout, __half* y, int64_t ldy, int64_t M, int64_t K,
 	int64_t N, cudaStream_t st)
 {
@@ -237,42 +268,23 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y))
 		return B200_ERR_MISALIGNED;
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	// wide tiles once they fill most of the machine; otherwise skinny tiles, two CTAs per SM
+	const bool wide = cdiv(M, BM) * cdiv(N, 256) >= 96;
+	const uint32_t bn = wide ? 256 : 64;
 	CUtensorMap tmA, tmB, tmY;
 	int rc = tmap_2d_f16(&tmY, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(ldy), 64, 32);
 	if (rc) return rc;
 	rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
 	if (rc) return rc;
 	if (w_layout == B200_W_NK)
-		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, BN);
+		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, bn);
 	else
 		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
 	if (rc) return rc;
-	const int m_tiles = static_cast<int>(cdiv(M, BM)), n_tiles = static_cast<int>(cdiv(N, BN));
-	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
-	const unsigned grid = static_cast<unsigned>(tiles < kNumSMs ? tiles : kNumSMs);
-	static bool attr_set[2] = { false, false };
+	const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
 	if (w_layout == B200_W_NK)
-	{
-		if (!attr_set[0])
-		{
-			B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-			attr_set[0] = true;
-		}
-		gemm_f16_tcgen05_kernel<0><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, static_cast<int>(M), static_cast<int>(N),
-			static_cast<int>(K), m_tiles, n_tiles, device_error_word());
-	}
-	else
-	{
-		if (!attr_set[1])
-		{
-			B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-			attr_set[1] = true;
-		}
-		gemm_f16_tcgen05_kernel<1><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, static_cast<int>(M), static_cast<int>(N),
-			static_cast<int>(K), m_tiles, n_tiles, device_error_word());
-	}
-	B200_LAUNCH_CHECK();
-	return B200_OK;
+		return wide ? launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
+	return wide ? launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
 }
 
 // ---- f32 SIMT kernel --------------------------------------------------------------------------------------

@@ -6,55 +6,70 @@
 
 namespace b200 {
 
-// LPR lanes share one (b,h,p) row of N = 4*LPR states. LPR is a power of two <= 32.
-template <typename T, int LPR>
+// LPR lanes share one (b,h,p) row of N = 4*LPR states (LPR a power of two <= 32). A thread owns RPT rows, 256/LPR
+// rows apart, and issues all of their 128-bit state loads before the first use, so that enough bytes are in flight
+// per SM to cover HBM latency. B and C are read as one 8-byte (f16) or 16-byte (f32) vector per thread.
+template <typename T, int LPR, int RPT>
 __global__ void __launch_bounds__(256) ssm_update_vec_kernel(float* __restrict__ state, const T* __restrict__ x, int64_t xs,
 	const T* __restrict__ dt, int64_t dts, const float* __restrict__ A, int a_is_log, const T* __restrict__ Bm, int64_t bs,
 	const T* __restrict__ Cm, int64_t cs, const float* __restrict__ D, const float* __restrict__ dt_bias, T* __restrict__ y,
-	int64_t ys, int64_t nrows /* b*H*P */, int H, int P, int G, int dt_softplus)
+	int64_t ys, int H, int P, int G, int dt_softplus)
 {
 	constexpr int N = 4 * LPR;
-	const int64_t gt = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-	const int64_t row = gt / LPR;
-	const int sub = static_cast<int>(gt % LPR);
-	const bool active = row < nrows;
-	float acc = 0.f;
-	int64_t b = 0;
-	int h = 0, p = 0;
-	float xv = 0.f;
-	if (active)
-	{
-		p = static_cast<int>(row % P);
-		const int64_t bh = row / P;
-		h = static_cast<int>(bh % H);
-		b = bh / H;
-		const int g = h / (H / G);
-		float dtv = ldf(dt + b * dts + h);
-		if (dt_bias) dtv += dt_bias[h];
-		if (dt_softplus) dtv = softplus_f32(dtv);
-		const float a = a_is_log ? -expf(A[h]) : A[h];
-		const float dA = expf(dtv * a);
-		xv = ldf(x + b * xs + static_cast<int64_t>(h) * P + p);
-		const float dx = dtv * xv;
-		float4* sp = reinterpret_cast<float4*>(state + row * N) + sub;
-		float4 s = *sp;
-		const T* bp = Bm + b * bs + static_cast<int64_t>(g) * N + sub * 4;
-		const T* cp = Cm + b * cs + static_cast<int64_t>(g) * N + sub * 4;
-		const float b0 = ldf(bp), b1 = ldf(bp + 1), b2 = ldf(bp + 2), b3 = ldf(bp + 3);
-		const float c0 = ldf(cp), c1 = ldf(cp + 1), c2 = ldf(cp + 2), c3 = ldf(cp + 3);
-		s.x = s.x * dA + dx * b0;
-		s.y = s.y * dA + dx * b1;
-		s.z = s.z * dA + dx * b2;
-		s.w = s.w * dA + dx * b3;
-		*sp = s;
-		acc = s.x * c0 + s.y * c1 + s.z * c2 + s.w * c3;
-	}
+	constexpr int ROWS_PER_PASS = 256 / LPR;  // rows covered by the CTA per pass
+	const int64_t bh = blockIdx.x;            // one CTA per (batch, head)
+	const int h = static_cast<int>(bh % H);
+	const int64_t b = bh / H;
+	const int g = h / (H / G);
+	const int sub = threadIdx.x % LPR;
+	const int prow = threadIdx.x / LPR;
+	float* sbase = state + bh * static_cast<int64_t>(P) * N;
+
+	float4 s[RPT];
 #pragma unroll
-	for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-	if (active && sub == 0)
+	for (int i = 0; i < RPT; ++i)
 	{
-		if (D) acc += D[h] * xv;
-		stf(y + b * ys + static_cast<int64_t>(h) * P + p, acc);
+		const int p = prow + i * ROWS_PER_PASS;
+		if (p < P) s[i] = *(reinterpret_cast<const float4*>(sbase + static_cast<int64_t>(p) * N) + sub);
+	}
+	Pack<T, 4> bv, cv;
+	bv.load(Bm + b * bs + static_cast<int64_t>(g) * N + sub * 4);
+	cv.load(Cm + b * cs + static_cast<int64_t>(g) * N + sub * 4);
+	float dtv = ldf(dt + b * dts + h);
+	float xv[RPT];
+#pragma unroll
+	for (int i = 0; i < RPT; ++i)
+	{
+		const int p = prow + i * ROWS_PER_PASS;
+		xv[i] = p < P ? ldf(x + b * xs + static_cast<int64_t>(h) * P + p) : 0.f;
+	}
+	if (dt_bias) dtv += dt_bias[h];
+	if (dt_softplus) dtv = softplus_f32(dtv);
+	const float a = a_is_log ? -expf(A[h]) : A[h];
+	const float dA = expf(dtv * a);
+	const float dh = D ? D[h] : 0.f;
+	float bf[4], cf[4];
+	bv.unpack(bf);
+	cv.unpack(cf);
+#pragma unroll
+	for (int i = 0; i < RPT; ++i)
+	{
+		const int p = prow + i * ROWS_PER_PASS;
+		float acc = 0.f;
+		if (p < P)
+		{
+			const float dx = dtv * xv[i];
+			float4 v = s[i];
+			v.x = v.x * dA + dx * bf[0];
+			v.y = v.y * dA + dx * bf[1];
+			v.z = v.z * dA + dx * bf[2];
+			v.w = v.w * dA + dx * bf[3];
+			*(reinterpret_cast<float4*>(sbase + static_cast<int64_t>(p) * N) + sub) = v;
+			acc = v.x * cf[0] + v.y * cf[1] + v.z * cf[2] + v.w * cf[3];
+		}
+#pragma unroll
+		for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+		if (p < P && sub == 0) stf(y + b * ys + static_cast<int64_t>(h) * P + p, acc + dh * xv[i]);
 	}
 }
 
@@ -104,16 +119,34 @@ static int ssm_update(float* state, const void* x, int64_t xs, const void* dt, i
 	const int h = static_cast<int>(H), p = static_cast<int>(P), g = static_cast<int>(G);
 #define B200_SSM_LAUNCH(LPR)                                                                                       \
 	{                                                                                                              \
-		const int64_t blocks = cdiv(nrows * LPR, 256);                                                             \
+		constexpr int RPP = 256 / LPR;                                                                             \
+		const int64_t blocks = batch * H;                                                                          \
 		if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;                                                    \
-		ssm_update_vec_kernel<T, LPR><<<static_cast<unsigned>(blocks), 256, 0, st>>>(state, xp, xs, dtp, dts, A,   \
-			a_is_log, bp, bs, cp, cs, D, dt_bias, yp, ys, nrows, h, p, g, dt_softplus);                            \
+		const unsigned gb = static_cast<unsigned>(blocks);                                                         \
+		if (P <= RPP)                                                                                              \
+			ssm_update_vec_kernel<T, LPR, 1><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
+				yp, ys, h, p, g, dt_softplus);                                                                     \
+		else if (P <= 2 * RPP)                                                                                     \
+			ssm_update_vec_kernel<T, LPR, 2><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
+				yp, ys, h, p, g, dt_softplus);                                                                     \
+		else if (P <= 4 * RPP)                                                                                     \
+			ssm_update_vec_kernel<T, LPR, 4><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
+				yp, ys, h, p, g, dt_softplus);                                                                     \
+		else if (P <= 8 * RPP)                                                                                     \
+			ssm_update_vec_kernel<T, LPR, 8><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
+				yp, ys, h, p, g, dt_softplus);                                                                     \
+		else                                                                                                       \
+			vec_ok = false;                                                                                        \
 	}
-	if (aligned16(state) && N == 128) B200_SSM_LAUNCH(32)
-	else if (aligned16(state) && N == 64) B200_SSM_LAUNCH(16)
-	else if (aligned16(state) && N == 32) B200_SSM_LAUNCH(8)
-	else if (aligned16(state) && N == 16) B200_SSM_LAUNCH(4)
-	else
+	// B and C are read as 4-element vectors: their rows must keep 4-element alignment
+	const size_t vbytes = 4 * sizeof(T);
+	bool vec_ok = aligned16(state) && (reinterpret_cast<uintptr_t>(Bm) % vbytes) == 0 && (reinterpret_cast<uintptr_t>(Cm) % vbytes) == 0 &&
+		bs % 4 == 0 && cs % 4 == 0 && (N == 128 || N == 64 || N == 32 || N == 16);
+	if (vec_ok && N == 128) B200_SSM_LAUNCH(32)
+	else if (vec_ok && N == 64) B200_SSM_LAUNCH(16)
+	else if (vec_ok && N == 32) B200_SSM_LAUNCH(8)
+	else if (vec_ok && N == 16) B200_SSM_LAUNCH(4)
+	if (!vec_ok)
 	{
 		const int64_t blocks = cdiv(nrows, 256);
 		if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
