@@ -178,6 +178,7 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
     from anygpu_b200 import capi, ops
+    from anygpu_b200 import dist as bdist
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -206,11 +207,7 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
     def max_over_ranks(v):
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+        return bdist.max_over_ranks(v, device="cuda")
 
     # ---- device-resident timing (the headline `value`) -------------------------------------------------------
     for i in range(args.warmup):
