@@ -3,6 +3,8 @@
 //   prefill: in_proj GEMM -> causal conv1d+SiLU (token-major) -> SSD chunked scan -> gated RMSNorm -> out_proj GEMM
 //   decode : in_proj GEMM -> conv_state update -> ssm_state recurrence -> gated RMSNorm -> out_proj GEMM
 // Six to eight launches on one stream, no allocation, no host synchronisation.
+#include <vector>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -172,6 +174,43 @@ extern "C" size_t b200_mamba2_mixer_prefill_host_workspace_bytes(const b200_mamb
 	return 2 * io + carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
 }
 
+// Copy engines of the host-buffer entry point: one stream for host->device, one for device->host, created once per
+// device, plus per-sequence events. The three activities of consecutive sequences overlap:
+//   copy-in(i+1)  ||  mixer(i)  ||  copy-out(i-1)
+namespace b200 {
+struct HostPipe
+{
+	cudaStream_t s_in = nullptr, s_out = nullptr;
+	cudaEvent_t ev_start = nullptr, ev_end = nullptr;
+	std::vector<cudaEvent_t> ev_in, ev_done;
+};
+static int host_pipe(HostPipe** out, int64_t nchunks)
+{
+	static HostPipe pipes[64];
+	int dev = 0;
+	B200_CUDA_TRY(cudaGetDevice(&dev));
+	if (dev < 0 || dev >= 64) return B200_ERR_UNSUPPORTED;
+	HostPipe& p = pipes[dev];
+	if (!p.s_in)
+	{
+		B200_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_in, cudaStreamNonBlocking));
+		B200_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_out, cudaStreamNonBlocking));
+		B200_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_start, cudaEventDisableTiming));
+		B200_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_end, cudaEventDisableTiming));
+	}
+	while (static_cast<int64_t>(p.ev_in.size()) < nchunks)
+	{
+		cudaEvent_t a, b;
+		B200_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
+		B200_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+		p.ev_in.push_back(a);
+		p.ev_done.push_back(b);
+	}
+	*out = &p;
+	return B200_OK;
+}
+}  // namespace b200
+
 extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
 	void* workspace, size_t workspace_bytes, void* stream)
@@ -187,12 +226,39 @@ extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_confi
 	const size_t inner = carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
 	if (workspace_bytes < 2 * io + inner) return B200_ERR_WORKSPACE;
 	char* p = static_cast<char*>(workspace);
+	char* u_dev = p;
+	char* out_dev = p + io;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
-	B200_CUDA_TRY(cudaMemcpyAsync(p, u_host, io_bytes, cudaMemcpyHostToDevice, st));
-	const int rc = b200_mamba2_mixer_prefill(dtype, cfg, w, p, p + io, batch, seqlen, nullptr, nullptr, nullptr, p + 2 * io, inner,
-		stream);
+
+	// one sequence per pipeline step (sequences are independent through every stage of the mixer)
+	HostPipe* hp = nullptr;
+	int rc = host_pipe(&hp, batch);
 	if (rc) return rc;
-	B200_CUDA_TRY(cudaMemcpyAsync(out_host, p + io, io_bytes, cudaMemcpyDeviceToHost, st));
+	const size_t seq_bytes = static_cast<size_t>(seqlen) * cfg->d_model * m.esz;
+	const char* uh = static_cast<const char*>(u_host);
+	char* oh = static_cast<char*>(out_host);
+	// the copy streams start after whatever the caller already queued on `stream`
+	B200_CUDA_TRY(cudaEventRecord(hp->ev_start, st));
+	B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_in, hp->ev_start, 0));
+	B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_start, 0));
+	for (int64_t i = 0; i < batch; ++i)
+	{
+		B200_CUDA_TRY(cudaMemcpyAsync(u_dev + i * seq_bytes, uh + i * seq_bytes, seq_bytes, cudaMemcpyHostToDevice, hp->s_in));
+		B200_CUDA_TRY(cudaEventRecord(hp->ev_in[i], hp->s_in));
+	}
+	for (int64_t i = 0; i < batch; ++i)
+	{
+		B200_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev_in[i], 0));
+		rc = b200_mamba2_mixer_prefill(dtype, cfg, w, u_dev + i * seq_bytes, out_dev + i * seq_bytes, 1, seqlen, nullptr, nullptr, nullptr,
+			p + 2 * io, inner, stream);
+		if (rc) return rc;
+		B200_CUDA_TRY(cudaEventRecord(hp->ev_done[i], st));
+		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_done[i], 0));
+		B200_CUDA_TRY(cudaMemcpyAsync(oh + i * seq_bytes, out_dev + i * seq_bytes, seq_bytes, cudaMemcpyDeviceToHost, hp->s_out));
+	}
+	// work queued on `stream` after this call (and a synchronisation of `stream`) sees the finished output
+	B200_CUDA_TRY(cudaEventRecord(hp->ev_end, hp->s_out));
+	B200_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev_end, 0));
 	return B200_OK;
 }
 

@@ -186,7 +186,10 @@ int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cfg, const b2
 	const float* initial_states, void* conv_state_out, float* ssm_state_out,
 	void* workspace, size_t workspace_bytes, void* stream);
 /* Same call for callers holding HOST tensors (anyGPU's Tensor<dtype,CPU>::copy_to_cuda / copy_to_host pattern,
- * srcs/core/tensor.hpp:318-370): copies u_host in, runs the mixer, copies out_host back, all on `stream`.
+ * srcs/core/tensor.hpp:318-370): copies u_host in, runs the mixer, copies out_host back. The call is asynchronous and
+ * ordered on `stream` (work queued on `stream` afterwards, or a synchronisation of it, sees out_host complete); inside,
+ * the sequences of the batch are pipelined over two library-owned copy streams so that the copy-in of sequence i+1, the
+ * mixer of sequence i and the copy-out of sequence i-1 overlap. Pinned host memory is needed for that overlap.
  * The workspace must be b200_mamba2_mixer_prefill_host_workspace_bytes large (it also holds the staging tensors). */
 size_t b200_mamba2_mixer_prefill_host_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen);
 int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
