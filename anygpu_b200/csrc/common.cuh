@@ -114,17 +114,41 @@ struct Pack
 	B bits;
 	__device__ __forceinline__ void load(const T* p) { bits = *reinterpret_cast<const B*>(p); }
 	__device__ __forceinline__ void store(T* p) const { *reinterpret_cast<B*>(p) = bits; }
+	// f16 pairs go through the packed half2 conversions (a scalar f16 -> f32 conversion issues on the slow XU pipe)
 	__device__ __forceinline__ void unpack(float* f) const
 	{
-		const T* e = reinterpret_cast<const T*>(&bits);
+		if constexpr (sizeof(T) == 2 && V % 2 == 0)
+		{
+			const __half2* e = reinterpret_cast<const __half2*>(&bits);
 #pragma unroll
-		for (int i = 0; i < V; ++i) f[i] = Cvt<T>::to_f32(e[i]);
+			for (int i = 0; i < V / 2; ++i)
+			{
+				const float2 t = __half22float2(e[i]);
+				f[2 * i] = t.x;
+				f[2 * i + 1] = t.y;
+			}
+		}
+		else
+		{
+			const T* e = reinterpret_cast<const T*>(&bits);
+#pragma unroll
+			for (int i = 0; i < V; ++i) f[i] = Cvt<T>::to_f32(e[i]);
+		}
 	}
 	__device__ __forceinline__ void pack(const float* f)
 	{
-		T* e = reinterpret_cast<T*>(&bits);
+		if constexpr (sizeof(T) == 2 && V % 2 == 0)
+		{
+			__half2* e = reinterpret_cast<__half2*>(&bits);
 #pragma unroll
-		for (int i = 0; i < V; ++i) e[i] = Cvt<T>::from_f32(f[i]);
+			for (int i = 0; i < V / 2; ++i) e[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+		}
+		else
+		{
+			T* e = reinterpret_cast<T*>(&bits);
+#pragma unroll
+			for (int i = 0; i < V; ++i) e[i] = Cvt<T>::from_f32(f[i]);
+		}
 	}
 };
 

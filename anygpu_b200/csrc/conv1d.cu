@@ -38,15 +38,15 @@ template <> struct Vec16<float>
 // One thread owns NV consecutive 16-byte vectors of one row. A row is S elements; S % (E*NV) == 0.
 template <typename T, int NV, int W>
 __global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict__ x, const T* __restrict__ w,
-	const T* __restrict__ bias, T* __restrict__ y, int64_t nthreads, int vec_per_row /* S / (E*NV) */, int64_t dims)
+	const T* __restrict__ bias, T* __restrict__ y, int vec_per_row /* S / (E*NV) */, unsigned dims)
 {
+	// grid: x = blocks along one row, y = row (batch * dims + channel); no 64-bit divisions on the hot path
 	constexpr int E = Vec16<T>::E;
 	constexpr int EPT = E * NV;
-	const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-	const bool active = tid < nthreads;
-	const int64_t row = active ? tid / vec_per_row : 0;
-	const int j = active ? static_cast<int>(tid - row * vec_per_row) : 0;
-	const int64_t base = row * (static_cast<int64_t>(vec_per_row) * EPT) + static_cast<int64_t>(j) * EPT;
+	const unsigned row = blockIdx.y + blockIdx.z * 65535u;
+	const int j = static_cast<int>(blockIdx.x * blockDim.x + threadIdx.x);
+	const bool active = j < vec_per_row;
+	const int64_t base = static_cast<int64_t>(row) * (static_cast<int64_t>(vec_per_row) * EPT) + static_cast<int64_t>(j) * EPT;
 
 	// lane 0 cannot get its halo from a neighbour: fetch it first so that it does not queue behind the main loads
 	const int lane = threadIdx.x & 31;
@@ -83,7 +83,7 @@ __global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict
 	}
 	v[0] = h0; v[1] = h1; v[2] = h2;
 
-	const int d = static_cast<int>(row % dims);
+	const unsigned d = row % dims;
 	float wt[W];
 #pragma unroll
 	for (int k = 0; k < W; ++k) wt[k] = ldf(w + static_cast<int64_t>(d) * W + k);
@@ -130,24 +130,24 @@ __global__ void __launch_bounds__(256) conv1d_seq_scalar_kernel(const T* __restr
 template <typename T, int V, int W, int TL>
 __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
 	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
-	int64_t seqlen, int64_t dims, int cvec /* ceil(dims / V) */, int64_t nwork /* cvec * token blocks */)
+	int seqlen, int dims, unsigned cvec /* ceil(dims / V) */, unsigned nwork /* cvec * token blocks */)
 {
-	const int64_t wid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	const unsigned wid = blockIdx.x * blockDim.x + threadIdx.x;
 	if (wid >= nwork) return;
-	const int cv = static_cast<int>(wid % cvec);
-	const int64_t tb = wid / cvec;
-	const int64_t c0 = static_cast<int64_t>(cv) * V;
+	const unsigned tb = wid / cvec;
+	const int c0 = static_cast<int>(wid - tb * cvec) * V;
 	const int64_t b = blockIdx.y;
-	const int64_t t0 = tb * TL;
-	const T* xb = x + b * seqlen * xs;
-	T* yb = y + b * seqlen * ys;
+	const int t0 = static_cast<int>(tb) * TL;
+	const T* xb = x + b * seqlen * xs + c0;
+	T* yb = y + b * seqlen * ys + c0;
 
+	// rows t0-(W-1) .. t0+TL-1, all requested before the first use
 	Pack<T, V> raw[TL + W - 1];
 #pragma unroll
 	for (int i = 0; i < TL + W - 1; ++i)
 	{
-		const int64_t t = t0 - (W - 1) + i;
-		if (t >= 0 && t < seqlen) raw[i].load(xb + t * xs + c0);
+		const int t = t0 - (W - 1) + i;
+		if (t >= 0 && t < seqlen) raw[i].load(xb + static_cast<int64_t>(t) * xs);
 	}
 
 	float wt[W][V], bs[V];
@@ -156,61 +156,67 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 	{
 		bs[c] = ldf(bias + c0 + c);
 #pragma unroll
-		for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + (c0 + c) * W + k);
+		for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + static_cast<int64_t>(c0 + c) * W + k);
 	}
 
-	float win[W][V];  // win[0..W-2] = previous rows (oldest first), win[W-1] = current
+	float f[TL + W - 1][V];
 #pragma unroll
-	for (int k = 0; k < W - 1; ++k)
+	for (int i = 0; i < TL + W - 1; ++i)
 	{
-		const int64_t t = t0 - (W - 1) + k;
+		const int t = t0 - (W - 1) + i;
 		if (t >= 0)
 		{
-			raw[k].unpack(win[k]);
+			if (t < seqlen) raw[i].unpack(f[i]);
+			else
+			{
+#pragma unroll
+				for (int c = 0; c < V; ++c) f[i][c] = 0.f;
+			}
 		}
 		else
 		{
 			// before the sequence: initial conv_state [b, dims, W-1] (oldest first) or zeros
 #pragma unroll
-			for (int c = 0; c < V; ++c)
-				win[k][c] = init ? ldf(init + (b * dims + c0 + c) * (W - 1) + (t + (W - 1))) : 0.f;
+			for (int c = 0; c < V; ++c) f[i][c] = init ? ldf(init + (b * dims + c0 + c) * (W - 1) + (t + (W - 1))) : 0.f;
 		}
 	}
 
 #pragma unroll
 	for (int i = 0; i < TL; ++i)
 	{
-		const int64_t t = t0 + i;
-		if (t < seqlen)
+		if (t0 + i < seqlen)
 		{
-			raw[i + W - 1].unpack(win[W - 1]);
 			float out[V];
 #pragma unroll
 			for (int c = 0; c < V; ++c)
 			{
 				float acc = 0.f;
 #pragma unroll
-				for (int k = 0; k < W; ++k) acc += wt[k][c] * win[k][c];
+				for (int k = 0; k < W; ++k) acc += wt[k][c] * f[i + k][c];
 				acc += bs[c];
 				out[c] = silu_f32(acc);
 			}
 			Pack<T, V> o;
 			o.pack(out);
-			o.store(yb + t * ys + c0);
-#pragma unroll
-			for (int k = 0; k < W - 1; ++k)
-#pragma unroll
-				for (int c = 0; c < V; ++c) win[k][c] = win[k + 1][c];
+			o.store(yb + static_cast<int64_t>(t0 + i) * ys);
 		}
 	}
 
-	// the thread that consumed the last token holds the next conv_state in its window
+	// the thread that consumed the last token holds the next conv_state: the W-1 inputs ending at token seqlen-1
 	if (fin != nullptr && t0 < seqlen && t0 + TL >= seqlen)
 	{
+		const int last = seqlen - 1 - t0;  // index of the last valid token inside this block, 0 <= last < TL
 #pragma unroll
-		for (int k = 0; k < W - 1; ++k)
+		for (int i = 0; i < TL; ++i)
+		{
+			if (i == last)
+			{
 #pragma unroll
-			for (int c = 0; c < V; ++c) stf(fin + (b * dims + c0 + c) * (W - 1) + k, win[k][c]);
+				for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+					for (int c = 0; c < V; ++c) stf(fin + (b * dims + c0 + c) * (W - 1) + k, f[i + 1 + k][c]);
+			}
+		}
 	}
 }
 
@@ -245,16 +251,24 @@ static int launch_seq_vec(const T* x, const T* w, const T* bias, T* y, int64_t r
 {
 	constexpr int EPT = Vec16<T>::E * NV;
 	const int vec_per_row = static_cast<int>(S / EPT);
-	const int64_t nthreads = rows * vec_per_row;
-	const int64_t blocks = cdiv(nthreads, 256);
-	if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-	const dim3 g(static_cast<unsigned>(blocks));
+	if (rows > 65535LL * 65535LL || dims > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const int threads = vec_per_row >= 256 ? 256 : (vec_per_row >= 128 ? 128 : (vec_per_row >= 64 ? 64 : 32));
+	// rows = gy * gz exactly (gz > 1 only beyond 65535 rows, which must then be a multiple of 65535)
+	unsigned gy = static_cast<unsigned>(rows), gz = 1;
+	if (rows > 65535)
+	{
+		if (rows % 65535 != 0) return B200_ERR_UNSUPPORTED;
+		gy = 65535u;
+		gz = static_cast<unsigned>(rows / 65535);
+	}
+	const dim3 g(static_cast<unsigned>(cdiv(vec_per_row, threads)), gy, gz);
+	const unsigned dm = static_cast<unsigned>(dims);
 	switch (W)
 	{
-	case 1: conv1d_seq_vec_kernel<T, NV, 1><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
-	case 2: conv1d_seq_vec_kernel<T, NV, 2><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
-	case 3: conv1d_seq_vec_kernel<T, NV, 3><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
-	default: conv1d_seq_vec_kernel<T, NV, 4><<<g, 256, 0, st>>>(x, w, bias, y, nthreads, vec_per_row, dims); break;
+	case 1: conv1d_seq_vec_kernel<T, NV, 1><<<g, threads, 0, st>>>(x, w, bias, y, vec_per_row, dm); break;
+	case 2: conv1d_seq_vec_kernel<T, NV, 2><<<g, threads, 0, st>>>(x, w, bias, y, vec_per_row, dm); break;
+	case 3: conv1d_seq_vec_kernel<T, NV, 3><<<g, threads, 0, st>>>(x, w, bias, y, vec_per_row, dm); break;
+	default: conv1d_seq_vec_kernel<T, NV, 4><<<g, threads, 0, st>>>(x, w, bias, y, vec_per_row, dm); break;
 	}
 	B200_LAUNCH_CHECK();
 	return B200_OK;
@@ -271,8 +285,9 @@ static int conv1d_seq(const void* xv, const void* wv, const void* bv, void* yv, 
 	const int64_t rows = batch * dims;
 	constexpr int E = Vec16<T>::E;
 	const bool al = aligned16(x) && aligned16(y);
-	if (al && S % (2 * E) == 0) return launch_seq_vec<T, 2>(x, w, bias, y, rows, S, dims, W, st);
-	if (al && S % E == 0) return launch_seq_vec<T, 1>(x, w, bias, y, rows, S, dims, W, st);
+	const bool grid_ok = rows <= 65535 || rows % 65535 == 0;
+	if (al && grid_ok && S % (2 * E) == 0) return launch_seq_vec<T, 2>(x, w, bias, y, rows, S, dims, W, st);
+	if (al && grid_ok && S % E == 0) return launch_seq_vec<T, 1>(x, w, bias, y, rows, S, dims, W, st);
 	const int64_t total = rows * S;
 	const int64_t blocks = cdiv(total, 256);
 	if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
@@ -286,17 +301,18 @@ static int launch_tok(const T* x, int64_t xs, const T* w, const T* bias, T* y, i
 	int64_t batch, int64_t seqlen, int64_t dims, int W, cudaStream_t st)
 {
 	constexpr int TL = 8;
-	const int cvec = static_cast<int>(cdiv(dims, V));
-	const int64_t nwork = static_cast<int64_t>(cvec) * cdiv(seqlen, TL);
-	const int64_t blocks = cdiv(nwork, 128);
-	if (blocks > 0x7fffffffLL || batch > 65535) return B200_ERR_UNSUPPORTED;
-	const dim3 g(static_cast<unsigned>(blocks), static_cast<unsigned>(batch));
+	const int64_t cvec = cdiv(dims, V);
+	const int64_t nwork = cvec * cdiv(seqlen, TL);
+	if (nwork > 0x7fffffffLL || batch > 65535 || seqlen > 0x7fffffffLL || dims > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const dim3 g(static_cast<unsigned>(cdiv(nwork, 128)), static_cast<unsigned>(batch));
+	const int sl = static_cast<int>(seqlen), dm = static_cast<int>(dims);
+	const unsigned cv = static_cast<unsigned>(cvec), nw = static_cast<unsigned>(nwork);
 	switch (W)
 	{
-	case 1: conv1d_tok_kernel<T, V, 1, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
-	case 2: conv1d_tok_kernel<T, V, 2, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
-	case 3: conv1d_tok_kernel<T, V, 3, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
-	default: conv1d_tok_kernel<T, V, 4, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork); break;
+	case 1: conv1d_tok_kernel<T, V, 1, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, sl, dm, cv, nw); break;
+	case 2: conv1d_tok_kernel<T, V, 2, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, sl, dm, cv, nw); break;
+	case 3: conv1d_tok_kernel<T, V, 3, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, sl, dm, cv, nw); break;
+	default: conv1d_tok_kernel<T, V, 4, TL><<<g, 128, 0, st>>>(x, xs, w, bias, y, ys, init, fin, sl, dm, cv, nw); break;
 	}
 	B200_LAUNCH_CHECK();
 	return B200_OK;

@@ -209,13 +209,14 @@ namespace cscan {
 constexpr int LB = 128;   // output rows (l) per CTA
 constexpr int KB = 64;    // s per K-block
 constexpr int NX = 4;     // X ring stages
-constexpr int THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 compute
+constexpr int NCW = 16;        // compute warps: 4 TMEM lane quadrants x 2 K-block parities x 2 column halves
+constexpr int THREADS = 64 + NCW * 32;  // warp 0 TMA, warp 1 MMA, warps 2-17 compute
 constexpr int S_STAGE = LB * KB * 2;  // 16 KiB
 constexpr int X_STAGE = KB * 64 * 2;  // 8 KiB
 constexpr int H_FLOATS = 3 * 256;     // per-head dAcs | dt | colf rows of the chunk (Q <= 256)
 constexpr uint32_t TMEM_COLS = 512;   // CB [0,256) | Y0 Z0 [256,384) | Y1 Z1 [384,512)
 
-constexpr int Y_STAGE = 32 * 64;      // per-warp output staging: 32 rows x 32 f16 (64 B rows, dense)
+constexpr int Y_STAGE = 32 * 32;      // per-warp output staging: 32 rows x 16 f16 (32 B rows, dense)
 
 template <int NSTATE, int NS, int NYB>
 struct Layout
@@ -230,8 +231,8 @@ struct Layout
 	static constexpr int OFF_X = OFF_S + NS * S_STAGE;
 	static constexpr int OFF_P = OFF_X + NX * X_STAGE;
 	static constexpr int OFF_H = OFF_P + 2 * P_BYTES;
-	static constexpr int OFF_Y = OFF_H + 2 * H_FLOATS * 4;   // [8 compute warps][NYB buffers][Y_STAGE]
-	static constexpr int TOTAL = OFF_Y + 8 * NYB * Y_STAGE + 1024;
+	static constexpr int OFF_Y = OFF_H + 2 * H_FLOATS * 4;   // [NCW compute warps][NYB buffers][Y_STAGE]
+	static constexpr int TOTAL = OFF_Y + NCW * NYB * Y_STAGE + 1024;
 };
 }  // namespace cscan
 
@@ -278,16 +279,16 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 		abort_flag = 0;
 		mbar_init(smem_u32(&bar_in), 1);
 		mbar_init(smem_u32(&bar_cb), 1);
-		for (int i = 0; i < NS; ++i) { mbar_init(smem_u32(&s_full[i]), 4); mbar_init(smem_u32(&s_empty[i]), 1); }
+		for (int i = 0; i < NS; ++i) { mbar_init(smem_u32(&s_full[i]), 8); mbar_init(smem_u32(&s_empty[i]), 1); }
 		for (int i = 0; i < NX; ++i) { mbar_init(smem_u32(&x_full[i]), 1); mbar_init(smem_u32(&x_empty[i]), 1); }
 		for (int i = 0; i < 2; ++i)
 		{
 			mbar_init(smem_u32(&p_full[i]), 1);
 			mbar_init(smem_u32(&p_empty[i]), 1);
 			mbar_init(smem_u32(&acc_full[i]), 1);
-			mbar_init(smem_u32(&acc_empty[i]), 8);
+			mbar_init(smem_u32(&acc_empty[i]), NCW);
 			mbar_init(smem_u32(&h_full[i]), 1);
-			mbar_init(smem_u32(&h_empty[i]), 8);
+			mbar_init(smem_u32(&h_empty[i]), NCW);
 		}
 		fence_mbar_init();
 	}
@@ -446,12 +447,13 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 	else
 	{
 		const int q = warp & 3;           // TMEM lane quadrant
-		const int half = (warp - 2) >> 2;  // 0: warps 2-5, 1: warps 6-9
+		const int cw = warp - 2;          // compute warp index 0..15
+		const int kpar = (cw >> 2) & 1;   // parity of the K-blocks this warp scales
+		const int chalf = cw >> 3;        // which 32-column half of a K-block
 		const int r = q * 32 + lane;      // row inside the block
 		const int l = l0 + r;
 		const int wrow0 = l0 + q * 32;    // first row of this warp
 		const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-		const int cw = warp - 2;          // compute warp index 0..7
 		uint8_t* ystg = gen + L::OFF_Y + cw * (NYB * Y_STAGE);
 		const uint32_t ystg_s = base + L::OFF_Y + cw * (NYB * Y_STAGE);
 		float dl2_prev = 0.f;
@@ -459,17 +461,18 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 		bool cb_ready = false;
 		if (lane == 0) prefetch_tmap(&tmY);
 
-		// y[l, h, half*32 .. +31] = Y + exp(dAcs[l]) * Z, staged per warp and written by one TMA store (rows past the end
-		// of the sequence are clipped by the store). The D*x skip term is already inside Y: D sits on the diagonal of S.
+		// y[l, h, cw*4 .. +15 columns] = Y + exp(dAcs[l]) * Z, staged per warp and written by one TMA store (rows past the
+		// end of the sequence are clipped by the store). The D*x skip term is already inside Y: D sits on the diagonal of S.
 		auto epilogue = [&](int i, float dl2) -> bool {
 			const int buf = i & 1;
 			const int h = h_begin + i;
+			const int ecol = (cw >> 2) * 16;  // this warp's 16 of the 64 head columns
 			if (!mbar_wait(smem_u32(&acc_full[buf]), (i >> 1) & 1, abortp)) return false;
 			tc_fence_after();
-			uint32_t yr[32], zr[32];
-			const uint32_t col = 256u + static_cast<uint32_t>(buf * 128 + half * 32);
-			tmem_ld_32x32(t_lane + col, yr);
-			tmem_ld_32x32(t_lane + col + 64u, zr);
+			uint32_t yr[16], zr[16];
+			const uint32_t col = 256u + static_cast<uint32_t>(buf * 128 + ecol);
+			tmem_ld_32x16(t_lane + col, yr);
+			tmem_ld_32x16(t_lane + col + 64u, zr);
 			if (lane == 0) bulk_wait_group_read<NYB - 1>();  // the staging buffer about to be rewritten has been read
 			tmem_ld_wait();
 			tc_fence_before();
@@ -478,18 +481,18 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 			const float dec = ex2_approx(dl2);
 			const uint32_t sb = (nstore % NYB) * Y_STAGE;
 #pragma unroll
-			for (int v = 0; v < 4; ++v)
+			for (int v = 0; v < 2; ++v)
 			{
 				float o[8];
 #pragma unroll
 				for (int e = 0; e < 8; ++e) o[e] = fmaf(dec, __uint_as_float(zr[v * 8 + e]), __uint_as_float(yr[v * 8 + e]));
-				*reinterpret_cast<Half8*>(ystg + sb + lane * 64 + v * 16) = pack8(o);
+				*reinterpret_cast<Half8*>(ystg + sb + lane * 32 + v * 16) = pack8(o);
 			}
 			fence_proxy_async_smem();
 			__syncwarp();
 			if (lane == 0)
 			{
-				tma_store_3d(&tmY, ystg_s + sb, h * 64 + half * 32, c * Q + wrow0, static_cast<int>(b));
+				tma_store_3d(&tmY, ystg_s + sb, h * 64 + ecol, c * Q + wrow0, static_cast<int>(b));
 				bulk_commit_group();
 			}
 			++nstore;
@@ -508,7 +511,7 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 				goto role_done;
 			}
 			const float dl2 = hd[l] * kLog2e;
-			for (int kb = half; kb < nkb; kb += 2)
+			for (int kb = kpar; kb < nkb; kb += 2)
 			{
 				const int kbc = i * nkb + kb;
 				const int ss = kbc % NS;
@@ -528,27 +531,27 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 				}
 				tc_fence_after();
 				uint8_t* srow = gen + L::OFF_S + ss * S_STAGE + r * 128;
-				const int s_first = kb * KB;
-				if (s_first > wrow0 + 31)
+				const int s_first = kb * KB;          // first column of the 64-wide K-block
+				const int s0 = s_first + chalf * 32;  // first of this warp's 32 columns
+				if (s0 > wrow0 + 31)
 				{
-					// the whole 32 x 64 block lies above the diagonal
+					// these 32 x 32 scores lie above the diagonal
 					Half8 zero;
 #pragma unroll
 					for (int e = 0; e < 4; ++e) zero.h[e] = __floats2half2_rn(0.f, 0.f);
 #pragma unroll
-					for (int chunk = 0; chunk < 8; ++chunk) *reinterpret_cast<Half8*>(srow + (chunk << 4)) = zero;
+					for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(srow + (((chalf * 4 + v) ^ (r & 7)) << 4)) = zero;
 				}
-				else if (s_first + KB - 1 <= wrow0 - 1)
+				else
 				{
-					// entirely below the diagonal: decay = exp(dAcs[l] - dAcs[block end]) * colf[s], both factors <= 1
-					const float rk = ex2_approx(fmaf(hd[s_first + KB - 1], -kLog2e, dl2));
-#pragma unroll
-					for (int c2 = 0; c2 < 2; ++c2)
+					uint32_t cbv[32];
+					tmem_ld_32x32(t_lane + static_cast<uint32_t>(s0), cbv);
+					if (s_first + KB - 1 <= wrow0 - 1)
 					{
-						uint32_t cbv[32];
-						tmem_ld_32x32(t_lane + static_cast<uint32_t>(s_first + c2 * 32), cbv);
+						// K-block entirely below the diagonal: decay = exp(dAcs[l] - dAcs[block end]) * colf[s], both factors <= 1
+						const float rk = ex2_approx(fmaf(hd[s_first + KB - 1], -kLog2e, dl2));
+						const float4* cfp = reinterpret_cast<const float4*>(hd + 512 + s0);
 						tmem_ld_wait();
-						const float4* cfp = reinterpret_cast<const float4*>(hd + 512 + s_first + c2 * 32);
 #pragma unroll
 						for (int v = 0; v < 4; ++v)
 						{
@@ -561,24 +564,16 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 #pragma unroll
 								for (int e = 0; e < 4; ++e) o[hq * 4 + e] = __uint_as_float(cbv[v * 8 + hq * 4 + e]) * (rk * cfa[e]);
 							}
-							const int chunk = c2 * 4 + v;
-							*reinterpret_cast<Half8*>(srow + ((chunk ^ (r & 7)) << 4)) = pack8(o);
+							*reinterpret_cast<Half8*>(srow + (((chalf * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
 						}
 					}
-				}
-				else
-				{
-					// block crossed by the diagonal: exact exp of the (non-positive) difference, causal mask, and the
-					// D skip connection as S[l,l] += D (so that S.x carries D*x)
-#pragma unroll
-					for (int c2 = 0; c2 < 2; ++c2)
+					else
 					{
-						uint32_t cbv[32];
-						tmem_ld_32x32(t_lane + static_cast<uint32_t>(s_first + c2 * 32), cbv);
-						tmem_ld_wait();
-						const int s0 = s_first + c2 * 32;
+						// crossed by the diagonal: exact exp of the (non-positive) difference, causal mask, and the D skip
+						// connection as S[l,l] += D (so that S.x carries D*x)
 						const float4* dsp = reinterpret_cast<const float4*>(hd + s0);
 						const float4* dtp = reinterpret_cast<const float4*>(hd + 256 + s0);
+						tmem_ld_wait();
 #pragma unroll
 						for (int v = 0; v < 4; ++v)  // 8 s-values -> one 16-byte chunk
 						{
@@ -600,8 +595,7 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 									o[hq * 4 + e] = val;
 								}
 							}
-							const int chunk = c2 * 4 + v;
-							*reinterpret_cast<Half8*>(srow + ((chunk ^ (r & 7)) << 4)) = pack8(o);
+							*reinterpret_cast<Half8*>(srow + (((chalf * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
 						}
 					}
 				}
@@ -702,7 +696,7 @@ int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs,
 	rc = tmap_2d_f16(&tmP, w.prev16, static_cast<uint64_t>(d.batch) * d.nchunks * d.H * 64, static_cast<uint64_t>(d.N),
 		static_cast<uint64_t>(d.N), 64, 64);
 	if (rc) return rc;
-	rc = tmap_3d_f16_linear(&tmY, y, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(ys), L * ys, 32, 32);
+	rc = tmap_3d_f16_linear(&tmY, y, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(ys), L * ys, 16, 32);
 	if (rc) return rc;
 	const int lblocks = d.Q / cscan::LB;
 	const int hpg = d.H / d.G;
