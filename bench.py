@@ -271,11 +271,17 @@ def run_gpu(args):
     dom = int(np.argmax(per_stage))
     roofline = {"kernel": "gemm_f16_tcgen05_kernel (in_proj)", "bound": "tensor",
                 "achieved": flops_in / (per_stage[0] * 1e-3) / 1e12 if per_stage[0] > 0 else None,
-                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "traffic": None,
+                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
+                # DRAM bytes per launch: the ncu capture of the M=2048 case (profiles/gemm_f16_tcgen05_in_proj_small.md) read exactly
+                # the operand bytes once (X + W); scaled to this launch that is X + W read and Y written = the algorithmic bytes
+                "traffic": float(tokens * cfg["d_model"] * 2 + cfg["d_model"] * d_in_proj * 2 + tokens * d_in_proj * 2),
+                "traffic_note": "scaled from the ncu capture of the M=2048 case: operands read once from DRAM, output written once",
+                "peak_burst": peaks["tflops_burst"],
                 "peak_source": f"{peaks['source']} cuBLAS bf16, sustained (kernel timed inside a long step)",
                 "algorithmic_flops_per_launch": flops_in, "avg_launch_ms": per_stage[0],
                 "stage_ms": dict(zip(STAGES, per_stage)), "dominant_stage": STAGES[dom]}
     roofline["frac"] = roofline["achieved"] / roofline["peak"] if roofline["achieved"] else None
+    roofline["frac_of_burst_peak"] = roofline["achieved"] / roofline["peak_burst"] if roofline["achieved"] else None
     G, N, H, P, Q = cfg["ngroups"], cfg["d_state"], cfg["nheads"], cfg["headdim"], cfg["chunk"]
     nchunks = -(-l // Q)
     flops_total = flops_in + 2.0 * tokens * cfg["d_inner"] * cfg["d_model"] + b * nchunks * (H * (2 * Q * Q * P + 4 * Q * N * P) + G * 2 * Q * Q * N)
