@@ -155,6 +155,42 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_scalar_kernel(cons
 	}
 }
 
+// ---- tensor-parallel split of the gated RMSNorm --------------------------------------------------------------------
+// When d_inner is sharded over ranks, the statistic mean(g^2) spans ranks. The normalisation factor is one scalar per
+// token, so it commutes with the out_proj that follows: each rank emits g*w un-normalised together with its partial
+// sum of squares; after the all-reduce of (out_proj partials, sums of squares) one row scaling finishes the job.
+template <typename T>
+__global__ void __launch_bounds__(128) gated_mul_sumsq_kernel(const T* x, int64_t xs, const T* __restrict__ z, int64_t zs,
+	const T* __restrict__ w, T* y /* may alias x */, int64_t ys, float* __restrict__ sumsq, int d)
+{
+	__shared__ float red[4];
+	const int64_t row = blockIdx.x;
+	const T* xr = x + row * xs;
+	const T* zr = z + row * zs;
+	T* yr = y + row * ys;
+	float ss = 0.f;
+	for (int i = threadIdx.x; i < d; i += 128)
+	{
+		const float gv = ldf(xr + i) * silu_f32(ldf(zr + i));
+		ss += gv * gv;
+		stf(yr + i, gv * ldf(w + i));
+	}
+	const float total = block_sum<128>(ss, red);
+	if (threadIdx.x == 0) sumsq[row] = total;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) row_scale_rsqrt_kernel(T* __restrict__ out, int64_t ld, const float* __restrict__ sumsq,
+	int64_t rows, int cols, float inv_d, float eps)
+{
+	const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= rows * cols) return;
+	const int64_t r = i / cols;
+	const int c = static_cast<int>(i - r * cols);
+	T* p = out + r * ld + c;
+	stf(p, ldf(p) * rsqrtf(sumsq[r] * inv_d + eps));
+}
+
 template <typename T>
 static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs, const void* wv, void* yv, int64_t ys,
 	int64_t rows, int64_t d, int64_t gsize, float eps, cudaStream_t st)
@@ -180,6 +216,36 @@ static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs,
 		gated_rmsnorm_vec_kernel<T, true, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
 	else
 		gated_rmsnorm_vec_kernel<T, false, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+int gated_mul_sumsq(int dtype, const void* x, int64_t xs, const void* z, int64_t zs, const void* w, void* y, int64_t ys,
+	float* sumsq, int64_t rows, int64_t d, cudaStream_t st)
+{
+	if (rows > 0x7fffffffLL || d > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const unsigned g = static_cast<unsigned>(rows);
+	if (dtype == B200_F16)
+		gated_mul_sumsq_kernel<__half><<<g, 128, 0, st>>>(static_cast<const __half*>(x), xs, static_cast<const __half*>(z), zs,
+			static_cast<const __half*>(w), static_cast<__half*>(y), ys, sumsq, static_cast<int>(d));
+	else
+		gated_mul_sumsq_kernel<float><<<g, 128, 0, st>>>(static_cast<const float*>(x), xs, static_cast<const float*>(z), zs,
+			static_cast<const float*>(w), static_cast<float*>(y), ys, sumsq, static_cast<int>(d));
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+int row_scale_rsqrt(int dtype, void* out, int64_t ld, const float* sumsq, int64_t rows, int64_t cols, float inv_d, float eps,
+	cudaStream_t st)
+{
+	const int64_t blocks = cdiv(rows * cols, 256);
+	if (blocks > 0x7fffffffLL || cols > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	if (dtype == B200_F16)
+		row_scale_rsqrt_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<__half*>(out), ld, sumsq, rows,
+			static_cast<int>(cols), inv_d, eps);
+	else
+		row_scale_rsqrt_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), ld, sumsq, rows,
+			static_cast<int>(cols), inv_d, eps);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }

@@ -262,6 +262,96 @@ extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_confi
 	return B200_OK;
 }
 
+// ---- head-sharded tensor parallelism ---------------------------------------------------------------------------------
+namespace b200 {
+int gated_mul_sumsq(int dtype, const void* x, int64_t xs, const void* z, int64_t zs, const void* w, void* y, int64_t ys,
+	float* sumsq, int64_t rows, int64_t d, cudaStream_t st);
+int row_scale_rsqrt(int dtype, void* out, int64_t ld, const float* sumsq, int64_t rows, int64_t cols, float inv_d, float eps,
+	cudaStream_t st);
+
+struct TpWs
+{
+	char* zxbcdt;
+	char* xbc;
+	char* y;
+	char* ssd;
+	size_t ssd_bytes, bytes;
+	int64_t ldz;  // row stride of the local in_proj output: d_in_proj rounded up to 8 elements
+};
+static TpWs carve_tp(void* base, const b200_mamba2_config* c, const MixerDims& m, int64_t batch, int64_t seqlen)
+{
+	TpWs w;
+	const size_t T = static_cast<size_t>(batch) * seqlen;
+	w.ldz = (m.d_in_proj + 7) / 8 * 8;
+	char* p = static_cast<char*>(base);
+	size_t off = 0;
+	w.zxbcdt = p + off; off += align_up(T * w.ldz * m.esz, 256);
+	w.xbc = p + off; off += align_up(T * m.conv_dim * m.esz, 256);
+	w.y = p + off; off += align_up(T * c->d_inner * m.esz, 256);
+	w.ssd = p + off;
+	w.ssd_bytes = b200_mamba_chunk_scan_combined_workspace_bytes(batch, seqlen, c->nheads, c->headdim, c->ngroups, c->d_state, c->chunk);
+	off += w.ssd_bytes;
+	w.bytes = off;
+	return w;
+}
+}  // namespace b200
+
+extern "C" size_t b200_mamba2_mixer_prefill_tp_workspace_bytes(const b200_mamba2_config* cfg_local, int dtype, int64_t batch,
+	int64_t seqlen)
+{
+	MixerDims m;
+	if (!dims_ok(cfg_local, dtype, &m) || batch <= 0 || seqlen <= 0) return 0;
+	return carve_tp(nullptr, cfg_local, m, batch, seqlen).bytes;
+}
+
+extern "C" int b200_mamba2_mixer_prefill_tp_partial(int dtype, const b200_mamba2_config* cfg_local, const b200_mamba2_weights* w,
+	const void* u, void* partial_out, float* sumsq, int64_t batch, int64_t seqlen, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg_local || !w || !u || !partial_out || !sumsq) return B200_ERR_NULL;
+	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
+		!w->out_proj_weight)
+		return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg_local, dtype, &m) || batch < 0 || seqlen < 0) return B200_ERR_BAD_SHAPE;
+	if (cfg_local->norm_group_size != 0 && cfg_local->norm_group_size != cfg_local->d_inner) return B200_ERR_UNSUPPORTED;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const TpWs ws = carve_tp(workspace, cfg_local, m, batch, seqlen);
+	if (workspace_bytes < ws.bytes) return B200_ERR_WORKSPACE;
+	const int64_t T = batch * seqlen;
+	const int64_t d_inner = cfg_local->d_inner, GN = cfg_local->ngroups * cfg_local->d_state;
+	const size_t e = m.esz;
+	int rc = b200_linear(dtype, u, cfg_local->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, ws.ldz, T, cfg_local->d_model,
+		ws.ldz, stream);
+	if (rc) return rc;
+	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, ws.ldz, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim, nullptr,
+		conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg_local->d_conv), stream);
+	if (rc) return rc;
+	rc = b200_mamba_chunk_scan_combined(dtype, ws.xbc, m.conv_dim, ws.zxbcdt + (d_inner + m.conv_dim) * e, ws.ldz, w->A_log, 1,
+		ws.xbc + d_inner * e, m.conv_dim, ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, nullptr, ws.y, d_inner,
+		ssm_state_out, batch, seqlen, cfg_local->nheads, cfg_local->headdim, cfg_local->ngroups, cfg_local->d_state, cfg_local->chunk, 1,
+		ws.ssd, ws.ssd_bytes, stream);
+	if (rc) return rc;
+	rc = gated_mul_sumsq(dtype, ws.y, d_inner, ws.zxbcdt, ws.ldz, w->norm_weight, ws.y, d_inner, sumsq, T, d_inner,
+		static_cast<cudaStream_t>(stream));
+	if (rc) return rc;
+	return b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, partial_out, cfg_local->d_model, T, d_inner,
+		cfg_local->d_model, stream);
+}
+
+extern "C" int b200_mamba2_mixer_tp_finish(int dtype, void* out, const float* sumsq, int64_t rows, int64_t d_model,
+	int64_t d_inner_global, float eps, void* stream)
+{
+	if (!out || !sumsq) return B200_ERR_NULL;
+	if (rows < 0 || d_model <= 0 || d_inner_global <= 0) return B200_ERR_BAD_SHAPE;
+	if (dtype != B200_F16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+	if (rows == 0) return B200_OK;
+	return row_scale_rsqrt(dtype, out, d_model, sumsq, rows, d_model, 1.0f / static_cast<float>(d_inner_global), eps,
+		static_cast<cudaStream_t>(stream));
+}
+
 extern "C" size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch)
 {
 	MixerDims m;

@@ -241,6 +241,39 @@ class Mamba2Mixer:
         return out
 
 
+class Mamba2MixerTP:
+    """One rank of the head-sharded (tensor-parallel) prefill mixer. `cfg_local` / `weights` are the rank's local sizes and
+    slices (anygpu_b200.synth.tp_local_config / shard_weights_tp). `partial` runs everything up to the rank's out_proj addend;
+    the caller sums `partial_out` and `sumsq` over ranks (one all-reduce each) and calls `finish`."""
+
+    def __init__(self, cfg_local, weights, d_inner_global):
+        self.cfg, self.w, self.d_inner_global = cfg_local, weights, d_inner_global
+        self.c_cfg, self.c_w = make_config(cfg_local), weights.c_struct()
+        self.dtype, self.device = weights.in_proj_weight.dtype, weights.in_proj_weight.device
+        self._ws = None
+
+    def partial(self, u, partial_out=None, sumsq=None):
+        b, l, d_model = u.shape
+        assert u.is_contiguous() and u.dtype == self.dtype
+        lib = capi.load()
+        nbytes = lib.b200_mamba2_mixer_prefill_tp_workspace_bytes(ctypes.byref(self.c_cfg), _DT[self.dtype], b, l)
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = _workspace(nbytes, self.device)
+        if partial_out is None:
+            partial_out = torch.empty_like(u)
+        if sumsq is None:
+            sumsq = torch.empty(b * l, dtype=torch.float32, device=u.device)
+        capi.call("b200_mamba2_mixer_prefill_tp_partial", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w), _p(u),
+                  _p(partial_out), _p(sumsq), b, l, None, None, _p(self._ws), self._ws.numel(), _stream())
+        return partial_out, sumsq
+
+    def finish(self, out_sum, sumsq_sum):
+        rows = sumsq_sum.numel()
+        capi.call("b200_mamba2_mixer_tp_finish", _DT[self.dtype], _p(out_sum), _p(sumsq_sum), rows, out_sum.shape[-1],
+                  self.d_inner_global, float(self.cfg["eps"]), _stream())
+        return out_sum
+
+
 def tensor_zamba_mamba2_mixer(weights, cache, hidden_states, cfg):
     """Functional form in the argument order of anyGPU's Zamba2 blocks (weights, cache, hidden states, config)."""
     m = Mamba2Mixer(cfg, weights)

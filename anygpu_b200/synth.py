@@ -76,3 +76,43 @@ def make_decode_state(cfg, seed=0, batch=None):
 def to_f16_values(a):
     """fp32 array holding exactly the values an f16 copy would hold."""
     return np.asarray(a, np.float32).astype(np.float16).astype(np.float32)
+
+
+def tp_local_config(cfg, tp):
+    """Local mixer sizes of one rank of a head-sharded layer: nheads/tp heads, their share of d_inner and the group(s) they use."""
+    H, G = cfg["nheads"], cfg["ngroups"]
+    assert H % tp == 0 and cfg["d_inner"] % tp == 0
+    Hl, hpg = H // tp, H // G
+    assert (Hl <= hpg and hpg % Hl == 0) or (Hl % hpg == 0), "a rank's heads must sit inside one group or cover whole groups"
+    Gl = 1 if Hl <= hpg else Hl // hpg
+    return dict(cfg, d_inner=cfg["d_inner"] // tp, nheads=Hl, ngroups=Gl, norm_group_size=0)
+
+
+def shard_weights_tp(w, cfg, tp, rank):
+    """Slices of the (in,out)-layout weights that rank `rank` of `tp` owns: in_proj columns z_r | x_r | B,C of its group(s) |
+    dt_r (zero-padded to a multiple of 8 columns), conv rows for the same channels, head slices of dt_bias / A_log / D,
+    its slice of the norm weight and its rows of out_proj."""
+    d_inner, H, G, N = cfg["d_inner"], cfg["nheads"], cfg["ngroups"], cfg["d_state"]
+    loc = tp_local_config(cfg, tp)
+    dl, Hl, Gl = loc["d_inner"], loc["nheads"], loc["ngroups"]
+    hpg = H // G
+    g0 = (rank * Hl) // hpg
+    ch = np.arange(rank * dl, (rank + 1) * dl)                       # the rank's x / z channels
+    grp = np.arange(g0 * N, (g0 + Gl) * N)                           # its B (and C) columns inside the G*N block
+    heads = np.arange(rank * Hl, (rank + 1) * Hl)
+    conv_rows = np.concatenate([ch, d_inner + grp, d_inner + G * N + grp])
+    cols = np.concatenate([ch, d_inner + conv_rows, 2 * d_inner + 2 * G * N + heads])
+    w_in = w["in_proj_weight"][:, cols]
+    pad = (-w_in.shape[1]) % 8
+    if pad:
+        w_in = np.concatenate([w_in, np.zeros((w_in.shape[0], pad), w_in.dtype)], axis=1)
+    return {
+        "in_proj_weight": np.ascontiguousarray(w_in),
+        "conv1d_weight": np.ascontiguousarray(w["conv1d_weight"][conv_rows]),
+        "conv1d_bias": np.ascontiguousarray(w["conv1d_bias"][conv_rows]),
+        "dt_bias": np.ascontiguousarray(w["dt_bias"][heads]),
+        "A_log": np.ascontiguousarray(w["A_log"][heads]),
+        "D": np.ascontiguousarray(w["D"][heads]),
+        "norm_weight": np.ascontiguousarray(w["norm_weight"][ch]),
+        "out_proj_weight": np.ascontiguousarray(w["out_proj_weight"][ch]),
+    }

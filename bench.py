@@ -310,6 +310,90 @@ def run_gpu(args):
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# head-sharded tensor parallelism (cfg4): every rank holds the whole batch and 1/N of the heads
+# ---------------------------------------------------------------------------------------------------------------
+
+def run_tp(args):
+    """`--mode tp` under torchrun with N ranks: the Zamba2-7B-shaped layer with nheads/N heads per rank. Per chunk of sequences:
+    local mixer up to the out_proj addend -> NCCL all-reduce (sum) of the addends and of the per-token sums of squares ->
+    row scaling. The all-reduce of chunk i runs on NCCL's stream while chunk i+1 computes. Strong scaling: the batch is fixed."""
+    import torch
+    import torch.distributed as dist
+    from anygpu_b200 import capi, ops
+    from anygpu_b200 import dist as bdist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = capi.load()
+    cfg = dict(synth.CONFIGS["cfg4"], batch=args.tp_batch)
+    b, l = cfg["batch"], cfg["seqlen"]
+    w_np = synth.make_weights(cfg, 0)
+    loc = synth.tp_local_config(cfg, world)
+    wl = ops.ZambaMamba2weights.from_numpy(synth.shard_weights_tp(w_np, cfg, world, rank), torch.float16)
+    del w_np
+    mixer = ops.Mamba2MixerTP(loc, wl, cfg["d_inner"])
+    g = torch.Generator(device="cuda").manual_seed(0)  # same input on every rank
+    u = torch.randn(b, l, cfg["d_model"], device="cuda", generator=g).half()
+    out = torch.empty_like(u)
+    ss = torch.empty(b * l, device="cuda")
+    chunk = min(args.tp_chunk, b)
+
+    def step():
+        pending = None
+        for c0 in range(0, b, chunk):
+            sl = slice(c0, min(c0 + chunk, b))
+            rows = slice(sl.start * l, sl.stop * l)
+            mixer.partial(u[sl], partial_out=out[sl], sumsq=ss[rows])
+            works = []
+            if world > 1:
+                works = [dist.all_reduce(out[sl], async_op=True), dist.all_reduce(ss[rows], async_op=True)]
+            if pending is not None:
+                psl, prows, pw = pending
+                for wk in pw:
+                    wk.wait()
+                mixer.finish(out[psl], ss[prows])
+            pending = (sl, rows, works)
+        psl, prows, pw = pending
+        for wk in pw:
+            wk.wait()
+        mixer.finish(out[psl], ss[prows])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = bdist.max_over_ranks(e0.elapsed_time(e1), device="cuda")
+    capi.check("b200_last_device_error", lib.b200_last_device_error(None, None))
+    chk = float(out.float().abs().mean())
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": b * l * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "f16", "data": "synthetic", "checksum_mean_abs": chk,
+                          "config": {"workload": f"cfg4: Zamba2-7B-shaped mixer prefill, batch {b} x seqlen {l} on every rank, "
+                                                 f"{cfg['nheads']} heads sharded {world}-way, ngroups {cfg['ngroups']}",
+                                     "global_batch": b, "seq_len": l,
+                                     "parallelism": f"tp{world}: head-sharded, NCCL all-reduce of out_proj addends (f16) and of the "
+                                                    f"per-token sum of squares, chunks of {chunk} sequences overlapped with compute"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # single-operator mode (micro-benchmarks of the other configurations; small cases for profiler captures)
 # ---------------------------------------------------------------------------------------------------------------
 
@@ -419,11 +503,16 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="dp", choices=["dp", "tp"], help="dp: batch-sharded (default); tp: head-sharded cfg4 layer")
+    ap.add_argument("--tp-batch", type=int, default=32)
+    ap.add_argument("--tp-chunk", type=int, default=4)
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
     args = ap.parse_args()
     if args.kernel:
         return run_kernel(args)
+    if args.mode == "tp" and args.impl == "b200":
+        return run_tp(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -196,6 +196,22 @@ int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, con
 	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
 	void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- head-sharded tensor parallelism (prefill) -----------------------------------------------------------------
+ * No counterpart in anyGPU (single device only, srcs/core/core.cpp:115-122). Rank r of TP owns nheads/TP heads: cfg_local
+ * carries the LOCAL sizes (d_inner/TP, nheads/TP, the groups those heads use) and w the matching slices: in_proj columns
+ * z_r | x_r | B,C of the rank's group(s) | dt_r (the row stride of that weight and of the local in_proj output is
+ * d_in_proj_local rounded up to a multiple of 8, extra columns zero), conv / dt_bias / A_log / D / norm slices, out_proj rows.
+ * _partial runs everything up to out_proj on the local heads and returns partial_out [T, d_model] (the rank's addend of
+ * the un-normalised output) and sumsq [T] (its part of sum_j (y*silu(z))_j^2). The caller all-reduces both (sum) and calls
+ * _finish, which scales row t by rsqrt(sumsq[t] / d_inner_global + eps): exactly the whole-row gated RMSNorm of the
+ * unsharded layer, because the normalisation factor is a per-token scalar and commutes with out_proj. */
+size_t b200_mamba2_mixer_prefill_tp_workspace_bytes(const b200_mamba2_config* cfg_local, int dtype, int64_t batch, int64_t seqlen);
+int b200_mamba2_mixer_prefill_tp_partial(int dtype, const b200_mamba2_config* cfg_local, const b200_mamba2_weights* w,
+	const void* u, void* partial_out, float* sumsq, int64_t batch, int64_t seqlen, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream);
+int b200_mamba2_mixer_tp_finish(int dtype, void* out, const float* sumsq, int64_t rows, int64_t d_model, int64_t d_inner_global,
+	float eps, void* stream);
+
 size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch);
 /* One token per sequence: u_t [batch, d_model] -> out_t [batch, d_model]; conv_state [b, conv_dim, d_conv-1] (dtype) and
  * ssm_state [b,H,P,N] fp32 are advanced in place. */

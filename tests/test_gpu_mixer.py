@@ -120,3 +120,29 @@ def test_prefill_then_decode_continues_the_sequence(ops):
     got = np.stack(outs, axis=1)
     assert_close_f16(got, full["out"][:, 128:], "decode continues prefill", max_fail_fraction=2e-3)
     assert rel_l2(got, full["out"][:, 128:]) < 3e-3
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+def test_head_sharded_tp_ranks_emulated_on_one_gpu(ops, tp):
+    """Tensor parallelism without a second GPU: the ranks run one after the other on this device and their partial outputs
+    and partial sums of squares are added by hand (what the all-reduce does). The result must match the unsharded mixer."""
+    cfg = dict(SMALL, nheads=8, ngroups=2, d_state=64, seqlen=256, chunk=128, batch=2)
+    w = f16w(synth.make_weights(cfg, 6))
+    u = synth.to_f16_values(synth.make_input(cfg, 6))
+    want = orc.mixer_prefill(u, w, cfg, f16io=True)["out"]
+    ud = torch.from_numpy(u).cuda().half()
+    whole = host(ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16)).prefill(ud))
+    loc = synth.tp_local_config(cfg, tp)
+    out_sum = torch.zeros(cfg["batch"], cfg["seqlen"], cfg["d_model"], device="cuda", dtype=torch.float32)
+    ss_sum = torch.zeros(cfg["batch"] * cfg["seqlen"], device="cuda")
+    last = None
+    for r in range(tp):
+        wl = ops.ZambaMamba2weights.from_numpy(synth.shard_weights_tp(w, cfg, tp, r), torch.float16)
+        last = ops.Mamba2MixerTP(loc, wl, cfg["d_inner"])
+        po, ss = last.partial(ud)
+        out_sum += po.float()
+        ss_sum += ss
+    got = host(last.finish(out_sum.half(), ss_sum))
+    assert_close_f16(got, want, f"tp{tp} vs oracle", max_fail_fraction=2e-4)
+    assert rel_l2(got, want) < 2e-3
+    assert rel_l2(got, whole) < 2e-3
