@@ -242,6 +242,245 @@ role_done:
 	}
 }
 
+// ---- CTA-pair variant (cta_group::2) ---------------------------------------------------------------------------------
+// Two CTAs of a cluster own one 256x256 output tile: each loads its 128 rows of X and HALF of the W tile (128 of the 256
+// output columns), the leader CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' shared memory, and
+// each CTA's TMEM receives its 128 rows x 256 columns. Per output tile the pair fetches half the W bytes that two
+// independent CTAs would, which lifts the L2 -> shared-memory bound of the single-CTA kernel. No load is multicast.
+namespace gemm2 {
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;        // this CTA's rows of X: 16 KiB
+constexpr int B_BYTES = (BN / 2) * BK * 2;  // this CTA's half of the W tile: 16 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STG_BYTES = 32 * 128;
+constexpr int STG_BUFS = 2;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * STG_BUFS * STG_BYTES + 1024;
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+}  // namespace gemm2
+
+template <int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) gemm_f16_tcgen05_pair_kernel(
+	const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M,
+	int N, int K, int m_tiles /* of 256 rows */, int n_tiles, uint32_t* err_word)
+{
+	using namespace gemm2;
+	using namespace tc;
+	extern __shared__ uint8_t smem_raw[];
+	__shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2];
+	__shared__ uint32_t tmem_slot;
+	__shared__ int abort_flag;
+
+	const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const uint32_t rank = cluster_ctarank();  // 0 = leader
+	const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+	const int k_blocks = (K + BK - 1) / BK;
+	const int num_tiles = m_tiles * n_tiles;
+	volatile int* abortp = &abort_flag;
+
+	if (threadIdx.x == 0)
+	{
+		abort_flag = 0;
+		for (int s = 0; s < STAGES; ++s)
+		{
+			mbar_init(smem_u32(&bar_full[s]), 1);   // used in the leader only: its own arrive.expect_tx covers both CTAs' bytes
+			mbar_init(smem_u32(&bar_empty[s]), 1);  // one pair-wide commit per use
+		}
+		for (int a = 0; a < 2; ++a)
+		{
+			mbar_init(smem_u32(&bar_tfull[a]), 1);
+			mbar_init(smem_u32(&bar_tempty[a]), 8);  // leader only: 4 epilogue warps of each CTA
+		}
+		fence_mbar_init();
+	}
+	if (warp == 1)
+	{
+		tmem_alloc_pair(smem_u32(&tmem_slot), TMEM_COLS);
+		tmem_relinquish_pair();
+	}
+	tc_fence_before();
+	__syncthreads();
+	cluster_sync();  // the peer's barriers exist before anything is signalled across CTAs
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_slot;
+
+	if (warp == 0)
+	{
+		if (lane == 0)
+		{
+			prefetch_tmap(&tmA);
+			prefetch_tmap(&tmB);
+			int stage = 0;
+			uint32_t phase = 0;
+			for (int tile = pair; tile < num_tiles; tile += npairs)
+			{
+				const int m0 = (tile % m_tiles) * (2 * BM) + static_cast<int>(rank) * BM;
+				const int n0 = (tile / m_tiles) * BN + static_cast<int>(rank) * (BN / 2);
+				for (int kb = 0; kb < k_blocks; ++kb)
+				{
+					if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp))
+					{
+						report_timeout(err_word, kErrProducerWait);
+						goto role_done;
+					}
+					// completion bytes of BOTH CTAs are counted on the leader's barrier
+					const uint32_t full = map_to_cta(smem_u32(&bar_full[stage]), 0);
+					const uint32_t a_s = ring + stage * STAGE_BYTES;
+					const uint32_t b_s = a_s + A_BYTES;
+					if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bar_full[stage]), 2 * STAGE_BYTES);
+					tma_load_2d_pair(a_s, &tmA, full, kb * BK, m0);
+					if (B_MN == 0)
+					{
+						tma_load_2d_pair(b_s, &tmB, full, kb * BK, n0);  // W^T [N,K]: [128 n x 64 k]
+					}
+					else
+					{
+#pragma unroll
+						for (int j = 0; j < BN / 2 / 64; ++j)  // W [K,N]: two boxes of [64 k x 64 n]
+							tma_load_2d_pair(b_s + j * (BK * 128), &tmB, full, n0 + j * 64, kb * BK);
+					}
+					if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+				}
+			}
+		}
+	}
+	else if (warp == 1)
+	{
+		if (lane == 0 && rank == 0)
+		{
+			constexpr uint32_t idesc = make_idesc_f16(2 * BM, BN, B_MN);
+			int stage = 0;
+			uint32_t phase = 0;
+			int acc = 0;
+			uint32_t acc_phase = 0;
+			for (int tile = pair; tile < num_tiles; tile += npairs)
+			{
+				if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1u, abortp))
+				{
+					report_timeout(err_word, kErrMmaWaitTmem);
+					goto role_done;
+				}
+				tc_fence_after();
+				const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+				for (int kb = 0; kb < k_blocks; ++kb)
+				{
+					if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp))
+					{
+						report_timeout(err_word, kErrMmaWaitFull);
+						goto role_done;
+					}
+					tc_fence_after();
+					const uint32_t a_s = ring + stage * STAGE_BYTES;
+					const uint32_t b_s = a_s + A_BYTES;
+					const uint64_t a_desc = make_smem_desc_sw128(a_s, 16, 1024);
+					const uint64_t b_desc = B_MN ? make_smem_desc_sw128(b_s, BK * 128, 1024) : make_smem_desc_sw128(b_s, 16, 1024);
+#pragma unroll
+					for (int k = 0; k < BK / 16; ++k)
+					{
+						const uint64_t a_k = a_desc + static_cast<uint64_t>(k * 2);
+						const uint64_t b_k = b_desc + static_cast<uint64_t>(B_MN ? k * 128 : k * 2);
+						mma_f16_ss_pair(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
+					}
+					mma_commit_pair(smem_u32(&bar_empty[stage]), 3);  // frees the stage in both CTAs
+					if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+				}
+				mma_commit_pair(smem_u32(&bar_tfull[acc]), 3);  // accumulators complete in both CTAs
+				if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+			}
+		}
+	}
+	else
+	{
+		const int q = warp & 3;
+		uint8_t* stg = smem_raw + (ring - smem_u32(smem_raw)) + STAGES * STAGE_BYTES + q * (STG_BUFS * STG_BYTES);
+		const uint32_t stg_s = ring + STAGES * STAGE_BYTES + q * (STG_BUFS * STG_BYTES);
+		if (lane == 0) prefetch_tmap(&tmY);
+		int acc = 0;
+		uint32_t acc_phase = 0;
+		uint32_t nchunk = 0;
+		for (int tile = pair; tile < num_tiles; tile += npairs)
+		{
+			const int m0 = (tile % m_tiles) * (2 * BM) + static_cast<int>(rank) * BM;
+			const int n0 = (tile / m_tiles) * BN;
+			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp))
+			{
+				if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
+				goto role_done;
+			}
+			tc_fence_after();
+			const uint32_t t_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+			for (int c = 0; c < BN / 64; ++c)
+			{
+				if (n0 + c * 64 >= N) break;  // warp-uniform
+				uint32_t r0[32], r1[32];
+				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64), r0);
+				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64 + 32), r1);
+				if (lane == 0) bulk_wait_group_read<STG_BUFS - 1>();
+				__syncwarp();
+				tmem_ld_wait();
+				const uint32_t buf = nchunk % STG_BUFS;
+				uint8_t* srow = stg + buf * STG_BYTES + lane * 128;
+#pragma unroll
+				for (int v = 0; v < 8; ++v)
+				{
+					const uint32_t* src = v < 4 ? r0 + v * 8 : r1 + (v - 4) * 8;
+					Half8 h;
+#pragma unroll
+					for (int e = 0; e < 4; ++e) h.h[e] = __floats2half2_rn(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
+					*reinterpret_cast<Half8*>(srow + ((v ^ (lane & 7)) << 4)) = h;
+				}
+				fence_proxy_async_smem();
+				__syncwarp();
+				if (lane == 0)
+				{
+					tma_store_2d(&tmY, stg_s + buf * STG_BYTES, n0 + c * 64, m0 + q * 32);
+					bulk_commit_group();
+				}
+				++nchunk;
+			}
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_tempty[acc]), 0));  // the leader's MMA thread waits on it
+			if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+		}
+		if (lane == 0) bulk_wait_group<0>();
+	}
+
+role_done:
+	__syncwarp();
+	if (*abortp)
+		for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+	tc_fence_before();
+	__syncthreads();
+	cluster_sync();  // neither CTA releases shared or tensor memory while the peer may still touch it
+	if (warp == 1)
+	{
+		tc_fence_after();
+		tmem_dealloc_pair(tmem_base, TMEM_COLS);
+	}
+}
+
+template <int B_MN>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st)
+{
+	using namespace gemm2;
+	static bool attr_set = false;
+	if (!attr_set)
+	{
+		B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_pair_kernel<B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+		attr_set = true;
+	}
+	const int m_tiles = static_cast<int>(cdiv(M, 2 * BM)), n_tiles = static_cast<int>(cdiv(N, BN));
+	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
+	const int64_t pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
+	gemm_f16_tcgen05_pair_kernel<B_MN><<<static_cast<unsigned>(2 * pairs), THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles,
+		n_tiles, device_error_word());
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
 template <int B_MN, class C>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st)
 {
@@ -270,7 +509,8 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 	// wide tiles once they fill most of the machine; otherwise skinny tiles, two CTAs per SM
 	const bool wide = cdiv(M, BM) * cdiv(N, 256) >= 96;
-	const uint32_t bn = wide ? 256 : 64;
+	const bool paired = cdiv(M, 256) * cdiv(N, 256) >= kNumSMs / 2;  // CTA pairs on 256x256 tiles
+	const uint32_t bn = paired ? 128 : (wide ? 256 : 64);
 	CUtensorMap tmA, tmB, tmY;
 	int rc = tmap_2d_f16(&tmY, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(ldy), 64, 32);
 	if (rc) return rc;
@@ -282,6 +522,7 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
 	if (rc) return rc;
 	const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+	if (paired) return w_layout == B200_W_NK ? launch_gemm_pair<0>(tmA, tmB, tmY, m, n, k, st) : launch_gemm_pair<1>(tmA, tmB, tmY, m, n, k, st);
 	if (w_layout == B200_W_NK)
 		return wide ? launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
 	return wide ? launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);

@@ -175,7 +175,8 @@ def test_linear_f32_golden(ops, golden_dir):
 
 
 @pytest.mark.parametrize("M,K,N", [(128, 64, 256), (128, 256, 256), (256, 512, 512), (64, 2560, 1064), (200, 264, 1064),
-                                   (8, 64, 8), (300, 72, 520), (1024, 2048, 8384)])
+                                   (8, 64, 8), (300, 72, 520), (1024, 2048, 8384),
+                                   (2304, 264, 2056), (2200, 512, 2312), (4096, 4096, 2048)])
 @pytest.mark.parametrize("layout", ["KN", "NK"])
 def test_linear_f16_tcgen05(ops, M, K, N, layout):
     r = np.random.default_rng(M + K + N)
