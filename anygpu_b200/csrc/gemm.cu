@@ -1,6 +1,8 @@
 // Y[M,N] = X[M,K] . W for the in_proj / out_proj of the Mamba2 mixer.
 //
-// f16: persistent, warp-specialised tcgen05 kernel. One CTA per SM walks 128x256 output tiles:
+// f16: persistent, warp-specialised tcgen05 kernels. Large problems run on CTA pairs (cta_group::2, 256x256 tiles, see
+// gemm_f16_tcgen05_pair_kernel); mid-size ones on one CTA per SM walking 128x256 output tiles; skinny ones (decode) on
+// 128x64 tiles with a deep ring so that enough weight bytes are in flight to stream W at HBM rate. Roles per CTA:
 //   warp 0    : TMA producer  - 128B-swizzled [128x64] X tiles and [256x64] W tiles into a 4-stage shared-memory ring
 //   warp 1    : MMA issuer    - tcgen05.mma (M128 N256 K16, f16 in, fp32 accumulate) into one of two TMEM accumulators
 //   warps 2-5 : epilogue      - tcgen05.ld the finished accumulator, round to f16, stage 32x64 sub-tiles in shared memory and
@@ -17,16 +19,18 @@ namespace b200 {
 
 namespace gemm {
 constexpr int BM = 128, BK = 64;
-constexpr int A_BYTES = BM * BK * 2;     // 16 KiB
 constexpr int STG_BYTES = 32 * 128;      // per-warp output staging tile: 32 rows x 64 f16, 128B-swizzled
 constexpr int THREADS = 192;
 
 // Two tile shapes: 128x256 (one CTA per SM) for large problems, 128x64 (two CTAs per SM, all CTAs resident at once)
 // for skinny ones such as the decode projections, where the job is to stream W once at full HBM bandwidth.
-template <int BN_, int STAGES_, int STG_BUFS_, int MIN_CTAS_>
+// A_ROWS: rows of X fetched per stage. With M <= 64 only 64 rows are loaded; the MMA still reads 128 rows of shared memory
+// (the second half is whatever follows in the ring) and the accumulator rows it produces from them are never stored.
+template <int BN_, int STAGES_, int STG_BUFS_, int MIN_CTAS_, int A_ROWS_ = 128>
 struct Cfg
 {
-	static constexpr int BN = BN_, STAGES = STAGES_, STG_BUFS = STG_BUFS_, MIN_CTAS = MIN_CTAS_;
+	static constexpr int BN = BN_, STAGES = STAGES_, STG_BUFS = STG_BUFS_, MIN_CTAS = MIN_CTAS_, A_ROWS = A_ROWS_;
+	static constexpr int A_BYTES = A_ROWS * BK * 2;
 	static constexpr int B_BYTES = BN * BK * 2;
 	static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 	static constexpr int STG_TOTAL = 4 * STG_BUFS * STG_BYTES;
@@ -34,7 +38,8 @@ struct Cfg
 	static constexpr uint32_t TMEM_COLS = 2 * BN;  // two fp32 accumulators
 };
 using CfgWide = Cfg<256, 4, 2, 1>;
-using CfgSkinny = Cfg<64, 3, 2, 2>;  // 3 x 24 KiB ring + 32 KiB staging: two CTAs fit one SM
+using CfgSkinny = Cfg<64, 8, 1, 1>;        // 8 x 24 KiB ring
+using CfgSkinny64 = Cfg<64, 13, 1, 1, 64>;  // M <= 64: 13 x 16 KiB ring, 104 KiB of W in flight per SM
 }  // namespace gemm
 
 template <int B_MN, class C>
@@ -44,7 +49,7 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 {
 	using namespace gemm;
 	using namespace tc;
-	constexpr int BN = C::BN, STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, STG_BUFS = C::STG_BUFS;
+	constexpr int BN = C::BN, STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, STG_BUFS = C::STG_BUFS, A_BYTES = C::A_BYTES;
 	constexpr uint32_t TMEM_COLS = C::TMEM_COLS;
 	extern __shared__ uint8_t smem_raw[];
 	__shared__ uint64_t bar_full[STAGES], bar_empty[STAGES], bar_tfull[2], bar_tempty[2];
@@ -511,10 +516,11 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	const bool wide = cdiv(M, BM) * cdiv(N, 256) >= 96;
 	const bool paired = cdiv(M, 256) * cdiv(N, 256) >= kNumSMs / 2;  // CTA pairs on 256x256 tiles
 	const uint32_t bn = paired ? 128 : (wide ? 256 : 64);
+	const bool tiny_m = !paired && !wide && M <= 64;
 	CUtensorMap tmA, tmB, tmY;
 	int rc = tmap_2d_f16(&tmY, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(ldy), 64, 32);
 	if (rc) return rc;
-	rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
+	rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, tiny_m ? 64 : BM);
 	if (rc) return rc;
 	if (w_layout == B200_W_NK)
 		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, bn);
@@ -524,8 +530,12 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
 	if (paired) return w_layout == B200_W_NK ? launch_gemm_pair<0>(tmA, tmB, tmY, m, n, k, st) : launch_gemm_pair<1>(tmA, tmB, tmY, m, n, k, st);
 	if (w_layout == B200_W_NK)
-		return wide ? launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
-	return wide ? launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
+	{
+		if (wide) return launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st);
+		return tiny_m ? launch_gemm<0, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
+	}
+	if (wide) return launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st);
+	return tiny_m ? launch_gemm<1, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
 }
 
 // ---- f32 SIMT kernel --------------------------------------------------------------------------------------
