@@ -30,6 +30,11 @@ static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
 	return true;
 }
 
+size_t linear_f16_splitk_workspace_bytes(int64_t M, int64_t K, int64_t N);
+bool linear_f16_splitk_applies(int64_t M, int64_t K, int64_t N);
+int linear_f16_splitk(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+	float* acc, cudaStream_t st);
+
 // ---- optional per-stage timing of the prefill mixer (CUDA events on the caller's stream) -------------------------
 constexpr int kStages = 5;       // in_proj, conv1d, ssd, gated_rmsnorm, out_proj
 constexpr int kTimingSlots = 256;  // mixer calls recorded between two collects
@@ -356,8 +361,10 @@ extern "C" size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_con
 {
 	MixerDims m;
 	if (!dims_ok(cfg, dtype, &m) || batch <= 0) return 0;
+	const size_t p_in = linear_f16_splitk_workspace_bytes(batch, cfg->d_model, m.d_in_proj);
+	const size_t p_out = linear_f16_splitk_workspace_bytes(batch, cfg->d_inner, cfg->d_model);
 	return align_up(batch * m.d_in_proj * m.esz, 256) + align_up(batch * m.conv_dim * m.esz, 256) +
-		align_up(batch * cfg->d_inner * m.esz, 256);
+		align_up(batch * cfg->d_inner * m.esz, 256) + (p_in > p_out ? p_in : p_out);
 }
 
 extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
@@ -378,10 +385,18 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	char* zx = static_cast<char*>(workspace);
 	char* xbc = zx + align_up(batch * m.d_in_proj * e, 256);
 	char* y = xbc + align_up(batch * m.conv_dim * e, 256);
+	float* acc = reinterpret_cast<float*>(y + align_up(batch * cfg->d_inner * e, 256));  // fp32 partial tiles of the split-K projections
 	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-	int rc = b200_linear(dtype, u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model,
-		m.d_in_proj, stream);
+	// a few tokens against large weights: the projections are weight-streaming problems -> split-K so every SM pulls on HBM
+	int rc;
+	if (dtype == B200_F16 && linear_f16_splitk_applies(batch, cfg->d_model, m.d_in_proj))
+		rc = linear_f16_splitk(u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model, m.d_in_proj,
+			acc, st);
+	else
+		rc = b200_linear(dtype, u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model,
+			m.d_in_proj, stream);
 	if (rc) return rc;
 	rc = b200_causal_conv1d_update(dtype, zx + d_inner * e, m.d_in_proj, conv_state, w->conv1d_weight, w->conv1d_bias, xbc,
 		m.conv_dim, batch, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
@@ -393,6 +408,9 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	rc = b200_gated_rmsnorm(dtype, y, d_inner, zx, m.d_in_proj, w->norm_weight, y, d_inner, batch, d_inner, cfg->norm_group_size,
 		cfg->eps, stream);
 	if (rc) return rc;
+	if (dtype == B200_F16 && linear_f16_splitk_applies(batch, d_inner, cfg->d_model))
+		return linear_f16_splitk(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model, acc,
+			st);
 	return b200_linear(dtype, y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
 		stream);
 }

@@ -240,6 +240,21 @@ class Mamba2Mixer:
                   _p(cache.conv_state), _p(cache.ssm_state), b, _p(ws), ws.numel(), _stream())
         return out
 
+    def capture_decode(self, u_t, cache, out):
+        """Records one decode step into a CUDA graph over the fixed buffers `u_t`, `cache` and `out`; `.replay()` of the returned
+        graph then advances the cache by one token with a single launch from the host (a decode step is a handful of
+        microsecond-scale kernels, so launching them one by one costs as much host time as they take on the device). The cache
+        holds the same values after this call as before it."""
+        keep = (cache.conv_state.clone(), cache.ssm_state.clone())
+        self.decode(u_t, cache, out=out)  # first use: workspace, kernel attributes and tensor maps are set up outside the capture
+        cache.conv_state.copy_(keep[0])
+        cache.ssm_state.copy_(keep[1])
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.decode(u_t, cache, out=out)
+        return graph
+
 
 class Mamba2MixerTP:
     """One rank of the head-sharded (tensor-parallel) prefill mixer. `cfg_local` / `weights` are the rank's local sizes and

@@ -468,7 +468,11 @@ def run_kernel(args):
         cache = ops.ZambaMambaCache(torch.from_numpy(cs).cuda().half(), torch.from_numpy(ss).cuda())
         u = rn(c3["batch"], c3["d_model"])
         o = torch.empty_like(u)
-        fn = lambda i: mixer.decode(u, cache, out=o)
+        if args.graph:
+            graph = mixer.capture_decode(u, cache, o)
+            fn = lambda i: graph.replay()
+        else:
+            fn = lambda i: mixer.decode(u, cache, out=o)
         cd3, dip3 = synth.dims(c3)
         bytes_alg = (c3["d_model"] * dip3 + c3["d_inner"] * c3["d_model"]) * 2 + 2 * ss.size * 4 + 2 * cs.size * 2
     else:
@@ -485,7 +489,7 @@ def run_kernel(args):
     ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
     med, mn = ms[len(ms) // 2], ms[0]
     capi.check("b200_last_device_error", capi.load().b200_last_device_error(None, None))
-    out = {"kernel": k, "small": bool(args.small), "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
+    out = {"kernel": k, "small": bool(args.small), "graph": bool(args.graph), "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
     if bytes_alg:
         out.update(algorithmic_bytes=bytes_alg, gbs_median=bytes_alg / (med * 1e-3) / 1e9, hbm_peak_gbs=peaks["hbm_gbs"],
                    frac_of_hbm_peak=bytes_alg / (med * 1e-3) / 1e9 / peaks["hbm_gbs"], peak_source=peaks["source"])
@@ -508,6 +512,7 @@ def main():
     ap.add_argument("--tp-chunk", type=int, default=4)
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
+    ap.add_argument("--graph", action="store_true", help="with --kernel decode: replay the step from a CUDA graph")
     args = ap.parse_args()
     if args.kernel:
         return run_kernel(args)

@@ -83,16 +83,18 @@ def test_mixer_prefill_host_call_equals_device_call(ops):
     assert torch.equal(dev_out, out_pin)
 
 
-@pytest.mark.parametrize("dtype", ["f16", "f32"])
+@pytest.mark.parametrize("dtype", ["f16", "f16_nk", "f32"])
 def test_mixer_decode_steps(ops, dtype):
     cfg = dict(SMALL, batch=5)
+    layout = ops.W_NK if dtype == "f16_nk" else ops.W_KN
+    dtype = dtype[:3]
     td = torch.float16 if dtype == "f16" else torch.float32
     w = synth.make_weights(cfg, 3)
     cs, ss = synth.make_decode_state(cfg, 3)
     us = synth.make_input(cfg, 3, batch=5, seqlen=6)
     if dtype == "f16":
         w, cs, us = f16w(w), synth.to_f16_values(cs), synth.to_f16_values(us)
-    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, td))
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, td, layout=layout))
     cache = ops.ZambaMambaCache(torch.from_numpy(cs).cuda().to(td), torch.from_numpy(ss).cuda())
     ocs, oss = cs.copy(), ss.copy()
     for t in range(us.shape[1]):
@@ -105,6 +107,27 @@ def test_mixer_decode_steps(ops, dtype):
             assert_abs(got, want, f"decode step {t}", 1e-3)
     assert_abs(host(cache.ssm_state), oss, "ssm state after decode", 2e-3)
     assert_close_f16(host(cache.conv_state), ocs, "conv state after decode")
+
+
+def test_decode_replayed_from_a_cuda_graph_equals_eager_decode(ops):
+    cfg = dict(SMALL, batch=3)
+    w = f16w(synth.make_weights(cfg, 7))
+    cs, ss = synth.make_decode_state(cfg, 7)
+    us = torch.from_numpy(synth.make_input(cfg, 7, batch=3, seqlen=4)).cuda().half()
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16))
+    mk = lambda: ops.ZambaMambaCache(torch.from_numpy(cs).cuda().half(), torch.from_numpy(ss).cuda())
+    eager_cache, graph_cache = mk(), mk()
+    u_buf, o_buf = torch.empty_like(us[:, 0]), torch.empty_like(us[:, 0])
+    u_buf.copy_(us[:, 0])
+    graph = mixer.capture_decode(u_buf, graph_cache, o_buf)
+    assert torch.equal(graph_cache.ssm_state, eager_cache.ssm_state)  # capturing does not advance the cache
+    for t in range(us.shape[1]):
+        want = mixer.decode(us[:, t].contiguous(), eager_cache).clone()
+        u_buf.copy_(us[:, t])
+        graph.replay()
+        assert torch.equal(o_buf, want), t
+    assert torch.equal(graph_cache.ssm_state, eager_cache.ssm_state)
+    assert torch.equal(graph_cache.conv_state, eager_cache.conv_state)
 
 
 def test_prefill_then_decode_continues_the_sequence(ops):
