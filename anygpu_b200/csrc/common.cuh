@@ -43,6 +43,24 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
 // Device-side error word set by bounded waits (0 = none).
 uint32_t* device_error_word();
 
+// Kernel launch with programmatic stream serialization (see pdl_wait below); `pdl` false gives a normal launch.
+bool pdl_enabled();  // false when the environment variable B200_NO_PDL is set to 1
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args)
+{
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = grid;
+	cfg.blockDim = block;
+	cfg.dynamicSmemBytes = smem;
+	cfg.stream = st;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attr[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = attr;
+	cfg.numAttrs = pdl ? 1 : 0;
+	return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---- device side -----------------------------------------------------------------------------------------
 
 template <typename T> struct Cvt;
@@ -67,6 +85,14 @@ __device__ __forceinline__ float silu_f32(float v) { return __fdividef(v, 1.0f +
 
 // torch softplus (beta 1, threshold 20), as F.softplus in scripts/zamba2/mamba_chunk_scan_comb.py:45.
 __device__ __forceinline__ float softplus_f32(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// Programmatic dependent launch: a kernel launched with programmatic stream serialization may start while the kernel before
+// it in the stream still runs. pdl_wait() blocks until that kernel has completed and its writes are visible (a no-op for a
+// normal launch); pdl_launch_dependents() lets the kernel after this one start once every CTA here has issued it or exited.
+// Rules kept by every kernel of such a chain: only constant data (weights) is touched before pdl_wait(), and every CTA
+// executes pdl_wait() before it exits, so that completion of a kernel implies completion of everything before it.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v)
 {

@@ -45,7 +45,7 @@ using CfgSkinny64 = Cfg<64, 13, 1, 1, 64>;  // M <= 64: 13 x 16 KiB ring, 104 Ki
 template <int B_MN, class C>
 __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M, int N, int K, int m_tiles, int n_tiles,
-	uint32_t* err_word, int splits, float* __restrict__ y_acc)
+	uint32_t* err_word)
 {
 	using namespace gemm;
 	using namespace tc;
@@ -58,10 +58,8 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 
 	const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-	// split-K (skinny problems): work item = (output tile, K slice); partial sums are added into the fp32 buffer y_acc
-	const int k_blocks_total = (K + BK - 1) / BK;
-	const int kbps = (k_blocks_total + splits - 1) / splits;  // K blocks per slice; the host guarantees no empty slice
-	const int num_tiles = m_tiles * n_tiles * splits;
+	const int k_blocks = (K + BK - 1) / BK;
+	const int num_tiles = m_tiles * n_tiles;
 	volatile int* abortp = &abort_flag;
 
 	if (threadIdx.x == 0)
@@ -99,12 +97,9 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 			uint32_t phase = 0;
 			for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
 			{
-				const int ot = tile / splits;
-				const int kb_begin = (tile - ot * splits) * kbps;
-				const int kb_end = min(kb_begin + kbps, k_blocks_total);
-				const int m0 = (ot % m_tiles) * BM;
-				const int n0 = (ot / m_tiles) * BN;
-				for (int kb = kb_begin; kb < kb_end; ++kb)
+				const int m0 = (tile % m_tiles) * BM;
+				const int n0 = (tile / m_tiles) * BN;
+				for (int kb = 0; kb < k_blocks; ++kb)
 				{
 					if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp))
 					{
@@ -149,9 +144,7 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 				}
 				tc_fence_after();
 				const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-				const int kb_begin = (tile % splits) * kbps;
-				const int kb_end = min(kb_begin + kbps, k_blocks_total);
-				for (int kb = kb_begin; kb < kb_end; ++kb)
+				for (int kb = 0; kb < k_blocks; ++kb)
 				{
 					if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp))
 					{
@@ -169,7 +162,7 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 						// K-major: 16 f16 = 32 B along the swizzled row; MN-major: 16 k-rows = two 1024-byte groups
 						const uint64_t a_k = a_desc + static_cast<uint64_t>(k * 2);
 						const uint64_t b_k = b_desc + static_cast<uint64_t>(B_MN ? k * 128 : k * 2);
-						mma_f16_ss(d_tmem, a_k, b_k, idesc, (kb != kb_begin || k != 0) ? 1u : 0u);
+						mma_f16_ss(d_tmem, a_k, b_k, idesc, (kb | k) != 0 ? 1u : 0u);
 					}
 					mma_commit(smem_u32(&bar_empty[stage]));  // frees the stage once these MMAs have read it
 					if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -190,9 +183,8 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 		uint32_t nchunk = 0;
 		for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
 		{
-			const int ot = tile / splits;
-			const int m0 = (ot % m_tiles) * BM;
-			const int n0 = (ot / m_tiles) * BN;
+			const int m0 = (tile % m_tiles) * BM;
+			const int n0 = (tile / m_tiles) * BN;
 			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp))
 			{
 				if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
@@ -207,26 +199,6 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 				uint32_t r0[32], r1[32];
 				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64), r0);
 				tmem_ld_32x32(t_base + static_cast<uint32_t>(c * 64 + 32), r1);
-				if (y_acc != nullptr)
-				{
-					// split-K: this K slice's partial sums go to slice `tile % splits` of the fp32 buffer [splits, M, N]
-					tmem_ld_wait();
-					const int row = m0 + q * 32 + lane;
-					if (row < M)
-					{
-						float* dst = y_acc + (static_cast<int64_t>(tile - ot * splits) * M + row) * N + n0 + c * 64;
-#pragma unroll
-						for (int v = 0; v < 16; ++v)
-						{
-							if (n0 + c * 64 + v * 4 < N)  // N % 8 == 0
-							{
-								const uint32_t* src = v < 8 ? r0 + v * 4 : r1 + (v - 8) * 4;
-								*reinterpret_cast<uint4*>(dst + v * 4) = make_uint4(src[0], src[1], src[2], src[3]);
-							}
-						}
-					}
-					continue;
-				}
 				// the staging buffer about to be rewritten must have been read by its store
 				if (lane == 0) bulk_wait_group_read<STG_BUFS - 1>();
 				__syncwarp();
@@ -515,8 +487,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 }
 
 template <int B_MN, class C>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st,
-	int splits = 1, float* y_acc = nullptr)
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st)
 {
 	using namespace gemm;
 	static bool attr_set = false;
@@ -526,11 +497,10 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 		attr_set = true;
 	}
 	const int m_tiles = static_cast<int>(cdiv(M, BM)), n_tiles = static_cast<int>(cdiv(N, C::BN));
-	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles * splits;
+	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
 	const int64_t slots = static_cast<int64_t>(kNumSMs) * C::MIN_CTAS;
 	const unsigned grid = static_cast<unsigned>(tiles < slots ? tiles : slots);
-	gemm_f16_tcgen05_kernel<B_MN, C><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles, n_tiles, device_error_word(),
-		splits, y_acc);
+	gemm_f16_tcgen05_kernel<B_MN, C><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles, n_tiles, device_error_word());
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }
@@ -566,83 +536,6 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	}
 	if (wide) return launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st);
 	return tiny_m ? launch_gemm<1, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
-}
-
-// ---- split-K for skinny problems (decode: a handful of tokens against a large weight) -------------------------------------
-// With M <= 128 there are only ceil(N/256) output tiles, far fewer than SMs, and the job is to stream W from HBM once.
-// K is cut into slices so that tiles x slices fills the machine; every CTA reads 512-byte runs of W rows (four 128-byte boxes
-// side by side) and writes its fp32 partial tile to slice s of a [slices, M, N] buffer; a small kernel adds the slices in a
-// fixed order (the result does not depend on scheduling) and rounds to f16. The partials live and die in L2.
-__global__ void __launch_bounds__(256) splitk_reduce_f16_kernel(const float* __restrict__ part, __half* __restrict__ dst, int64_t ldd,
-	int M, int N, int splits)
-{
-	const int64_t mn = static_cast<int64_t>(M) * N;
-	const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
-	if (i >= mn) return;
-	const int64_t r = i / N;
-	const int c = static_cast<int>(i - r * N);  // N % 8 == 0: the 8 elements stay inside one row
-	float f[8] = { 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f };
-#pragma unroll 4
-	for (int s = 0; s < splits; ++s)
-	{
-		const float4 a = *reinterpret_cast<const float4*>(part + s * mn + i);
-		const float4 b = *reinterpret_cast<const float4*>(part + s * mn + i + 4);
-		f[0] += a.x; f[1] += a.y; f[2] += a.z; f[3] += a.w;
-		f[4] += b.x; f[5] += b.y; f[6] += b.z; f[7] += b.w;
-	}
-	*reinterpret_cast<Half8*>(dst + r * ldd + c) = pack8(f);
-}
-
-// K slices for an [M <= 128, K] x [K, N] problem: as many as fill the SMs, none empty.
-static int splitk_slices(int64_t K, int64_t N)
-{
-	const int k_blocks = static_cast<int>(cdiv(K, gemm::BK));
-	const int n_tiles = static_cast<int>(cdiv(N, 256));
-	int splits = kNumSMs / n_tiles;
-	if (splits > k_blocks) splits = k_blocks;
-	if (splits < 1) splits = 1;
-	const int kbps = (k_blocks + splits - 1) / splits;
-	return (k_blocks + kbps - 1) / kbps;
-}
-
-size_t linear_f16_splitk_workspace_bytes(int64_t M, int64_t K, int64_t N)
-{
-	return align_up(static_cast<size_t>(splitk_slices(K, N)) * M * N * sizeof(float), 256);
-}
-
-bool linear_f16_splitk_applies(int64_t M, int64_t K, int64_t N)
-{
-	return M <= 128 && cdiv(N, 256) * 2 <= kNumSMs && K >= 4 * 64;
-}
-
-int linear_f16_splitk(const void* xv, int64_t ldx, const void* wv, int w_layout, void* yv, int64_t ldy, int64_t M, int64_t K, int64_t N,
-	float* part, cudaStream_t st)
-{
-	using namespace gemm;
-	const __half* x = static_cast<const __half*>(xv);
-	const __half* w = static_cast<const __half*>(wv);
-	__half* y = static_cast<__half*>(yv);
-	if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y) || !aligned16(part))
-		return B200_ERR_MISALIGNED;
-	CUtensorMap tmA, tmB, tmY;
-	int rc = tmap_2d_f16(&tmY, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(ldy), 64, 32);  // unused by this mode
-	if (rc) return rc;
-	rc = tmap_2d_f16(&tmA, x, static_cast<uint64_t>(M), static_cast<uint64_t>(K), static_cast<uint64_t>(ldx), BK, BM);
-	if (rc) return rc;
-	if (w_layout == B200_W_NK)
-		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(N), static_cast<uint64_t>(K), static_cast<uint64_t>(K), BK, 256);
-	else
-		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
-	if (rc) return rc;
-	const int splits = splitk_slices(K, N);
-	const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
-	rc = w_layout == B200_W_NK ? launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st, splits, part)
-	                           : launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st, splits, part);
-	if (rc) return rc;
-	const int64_t blocks = cdiv(M * N / 8, 256);
-	splitk_reduce_f16_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(part, y, ldy, m, n, splits);
-	B200_LAUNCH_CHECK();
-	return B200_OK;
 }
 
 // ---- f32 SIMT kernel --------------------------------------------------------------------------------------

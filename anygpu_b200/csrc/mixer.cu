@@ -30,10 +30,18 @@ static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
 	return true;
 }
 
-size_t linear_f16_splitk_workspace_bytes(int64_t M, int64_t K, int64_t N);
-bool linear_f16_splitk_applies(int64_t M, int64_t K, int64_t N);
-int linear_f16_splitk(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
-	float* acc, cudaStream_t st);
+// fused decode stages (gemm_decode.cu, ssm_update.cu)
+bool decode_linear_applies(int dtype, int64_t M, int64_t K, int64_t N);
+size_t decode_linear_partial_bytes(int64_t M, int64_t K, int64_t N);
+int decode_in_proj_conv(const void* x, int64_t ldx, const void* w, int w_layout, void* zx, int64_t ldz, int64_t M, int64_t K, int64_t N,
+	int64_t conv_lo, int64_t conv_dim, int conv_width, void* conv_state, const void* conv_w, const void* conv_b, void* xbc, float* part,
+	cudaStream_t st);
+int decode_out_proj_scale(const void* x, int64_t ldx, const void* w, int w_layout, void* out, int64_t ldo, int64_t M, int64_t K, int64_t N,
+	const float* sumsq, int nsumsq, int64_t norm_dim, float eps, float* part, cudaStream_t st);
+bool ssm_update_gated_applies(int64_t P, int64_t N, int64_t G);
+int ssm_update_gated_f16(float* state, const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm,
+	int64_t bs, const void* Cm, int64_t cs, const float* D, const float* dt_bias, void* y, int64_t ys, const void* z, int64_t zs,
+	const void* norm_w, float* sumsq, int64_t batch, int64_t H, int64_t P, int64_t G, int64_t N, int dt_softplus, cudaStream_t st);
 
 // ---- optional per-stage timing of the prefill mixer (CUDA events on the caller's stream) -------------------------
 constexpr int kStages = 5;       // in_proj, conv1d, ssd, gated_rmsnorm, out_proj
@@ -357,16 +365,44 @@ extern "C" int b200_mamba2_mixer_tp_finish(int dtype, void* out, const float* su
 		static_cast<cudaStream_t>(stream));
 }
 
+// Decode workspace: zx | xbc | y | fp32 partial tiles of the stream-K projections | per-(row, head) sums of squares.
+struct DecodeLayout
+{
+	size_t zx, xbc, y, part, sumsq, total;
+};
+
+static DecodeLayout decode_layout(const b200_mamba2_config* cfg, const MixerDims& m, int dtype, int64_t batch)
+{
+	DecodeLayout L;
+	size_t off = 0;
+	L.zx = off;
+	off += align_up(batch * m.d_in_proj * m.esz, 256);
+	L.xbc = off;
+	off += align_up(batch * m.conv_dim * m.esz, 256);
+	L.y = off;
+	off += align_up(batch * cfg->d_inner * m.esz, 256);
+	size_t p_in = 0, p_out = 0;
+	if (decode_linear_applies(dtype, batch, cfg->d_model, m.d_in_proj)) p_in = decode_linear_partial_bytes(batch, cfg->d_model, m.d_in_proj);
+	if (decode_linear_applies(dtype, batch, cfg->d_inner, cfg->d_model)) p_out = decode_linear_partial_bytes(batch, cfg->d_inner, cfg->d_model);
+	L.part = off;
+	off += p_in > p_out ? p_in : p_out;
+	L.sumsq = off;
+	off += align_up(batch * cfg->nheads * sizeof(float), 256);
+	L.total = off;
+	return L;
+}
+
 extern "C" size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch)
 {
 	MixerDims m;
 	if (!dims_ok(cfg, dtype, &m) || batch <= 0) return 0;
-	const size_t p_in = linear_f16_splitk_workspace_bytes(batch, cfg->d_model, m.d_in_proj);
-	const size_t p_out = linear_f16_splitk_workspace_bytes(batch, cfg->d_inner, cfg->d_model);
-	return align_up(batch * m.d_in_proj * m.esz, 256) + align_up(batch * m.conv_dim * m.esz, 256) +
-		align_up(batch * cfg->d_inner * m.esz, 256) + (p_in > p_out ? p_in : p_out);
+	return decode_layout(cfg, m, dtype, batch).total;
 }
 
+// One token per sequence. With f16 tensors and at most 128 sequences the step is five launches:
+//   stream-K in_proj -> slice sum + rolling conv1d/SiLU -> recurrence + gate (+ sums of squares) -> stream-K out_proj ->
+//   slice sum + RMSNorm row scale.
+// Otherwise the operators run one by one (linear, conv update, recurrence, gated RMSNorm, linear).
 extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
 	void* workspace, size_t workspace_bytes, void* stream)
@@ -380,27 +416,47 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	if (batch == 0) return B200_OK;
 	if (!workspace) return B200_ERR_WORKSPACE;
 	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
-	if (workspace_bytes < b200_mamba2_mixer_decode_workspace_bytes(cfg, dtype, batch)) return B200_ERR_WORKSPACE;
+	const DecodeLayout L = decode_layout(cfg, m, dtype, batch);
+	if (workspace_bytes < L.total) return B200_ERR_WORKSPACE;
 	const size_t e = m.esz;
-	char* zx = static_cast<char*>(workspace);
-	char* xbc = zx + align_up(batch * m.d_in_proj * e, 256);
-	char* y = xbc + align_up(batch * m.conv_dim * e, 256);
-	float* acc = reinterpret_cast<float*>(y + align_up(batch * cfg->d_inner * e, 256));  // fp32 partial tiles of the split-K projections
+	char* base = static_cast<char*>(workspace);
+	char* zx = base + L.zx;
+	char* xbc = base + L.xbc;
+	char* y = base + L.y;
+	float* part = reinterpret_cast<float*>(base + L.part);
+	float* sumsq = reinterpret_cast<float*>(base + L.sumsq);
 	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	const bool fuse_in = decode_linear_applies(dtype, batch, cfg->d_model, m.d_in_proj) && d_inner % 8 == 0 && m.conv_dim % 8 == 0;
+	const bool fuse_out = decode_linear_applies(dtype, batch, d_inner, cfg->d_model);
+	const bool whole_row_norm = cfg->norm_group_size == 0 || cfg->norm_group_size == d_inner;
+	const bool fuse_gate = fuse_out && whole_row_norm && ssm_update_gated_applies(cfg->headdim, cfg->d_state, cfg->ngroups) && GN % 8 == 0;
 
-	// a few tokens against large weights: the projections are weight-streaming problems -> split-K so every SM pulls on HBM
 	int rc;
-	if (dtype == B200_F16 && linear_f16_splitk_applies(batch, cfg->d_model, m.d_in_proj))
-		rc = linear_f16_splitk(u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model, m.d_in_proj,
-			acc, st);
+	if (fuse_in)
+	{
+		rc = decode_in_proj_conv(u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model, m.d_in_proj,
+			d_inner, m.conv_dim, static_cast<int>(cfg->d_conv), conv_state, w->conv1d_weight, w->conv1d_bias, xbc, part, st);
+		if (rc) return rc;
+	}
 	else
+	{
 		rc = b200_linear(dtype, u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model,
 			m.d_in_proj, stream);
-	if (rc) return rc;
-	rc = b200_causal_conv1d_update(dtype, zx + d_inner * e, m.d_in_proj, conv_state, w->conv1d_weight, w->conv1d_bias, xbc,
-		m.conv_dim, batch, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
-	if (rc) return rc;
+		if (rc) return rc;
+		rc = b200_causal_conv1d_update(dtype, zx + d_inner * e, m.d_in_proj, conv_state, w->conv1d_weight, w->conv1d_bias, xbc,
+			m.conv_dim, batch, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+		if (rc) return rc;
+	}
+	if (fuse_gate)
+	{
+		rc = ssm_update_gated_f16(ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1, xbc + d_inner * e,
+			m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, zx, m.d_in_proj, w->norm_weight, sumsq, batch,
+			cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, 1, st);
+		if (rc) return rc;
+		return decode_out_proj_scale(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
+			sumsq, static_cast<int>(cfg->nheads), d_inner, cfg->eps, part, st);
+	}
 	rc = b200_selective_state_update(dtype, ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
 		xbc + d_inner * e, m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, batch, cfg->nheads,
 		cfg->headdim, cfg->ngroups, cfg->d_state, 1, stream);
@@ -408,9 +464,9 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	rc = b200_gated_rmsnorm(dtype, y, d_inner, zx, m.d_in_proj, w->norm_weight, y, d_inner, batch, d_inner, cfg->norm_group_size,
 		cfg->eps, stream);
 	if (rc) return rc;
-	if (dtype == B200_F16 && linear_f16_splitk_applies(batch, d_inner, cfg->d_model))
-		return linear_f16_splitk(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model, acc,
-			st);
+	if (fuse_out)
+		return decode_out_proj_scale(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
+			nullptr, 0, d_inner, cfg->eps, part, st);
 	return b200_linear(dtype, y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
 		stream);
 }

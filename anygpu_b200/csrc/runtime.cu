@@ -1,12 +1,22 @@
 // Library-wide state of the C ABI: status strings, the per-thread CUDA error record and the device error word
 // that bounded device-side waits set when they give up.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace b200 {
 
 thread_local int g_last_cuda_error = 0;
 
 __device__ uint32_t g_device_error_word = 0;
+
+bool pdl_enabled()
+{
+	static const bool on = [] {
+		const char* v = getenv("B200_NO_PDL");
+		return !(v && v[0] == '1');
+	}();
+	return on;
+}
 
 uint32_t* device_error_word()
 {

@@ -9,14 +9,20 @@ namespace b200 {
 // LPR lanes share one (b,h,p) row of N = 4*LPR states (LPR a power of two <= 32). A thread owns RPT rows, 256/LPR
 // rows apart, and issues all of their 128-bit state loads before the first use, so that enough bytes are in flight
 // per SM to cover HBM latency. B and C are read as one 8-byte (f16) or 16-byte (f32) vector per thread.
-template <typename T, int LPR, int RPT>
+// GATE: the output is additionally gated and weighted for the RMSNorm that follows, y <- round_T(y) * silu(z) * norm_w, and the
+// CTA's sum of (round_T(y) * silu(z))^2 goes to sumsq[b, h]; the consumer of y applies rsqrt(mean + eps) (a row scale commutes
+// with the projection that follows the norm).
+template <typename T, int LPR, int RPT, bool GATE = false>
 __global__ void __launch_bounds__(256) ssm_update_vec_kernel(float* __restrict__ state, const T* __restrict__ x, int64_t xs,
 	const T* __restrict__ dt, int64_t dts, const float* __restrict__ A, int a_is_log, const T* __restrict__ Bm, int64_t bs,
 	const T* __restrict__ Cm, int64_t cs, const float* __restrict__ D, const float* __restrict__ dt_bias, T* __restrict__ y,
-	int64_t ys, int H, int P, int G, int dt_softplus)
+	int64_t ys, int H, int P, int G, int dt_softplus, const T* __restrict__ z = nullptr, int64_t zs = 0,
+	const T* __restrict__ norm_w = nullptr, float* __restrict__ sumsq = nullptr)
 {
 	constexpr int N = 4 * LPR;
 	constexpr int ROWS_PER_PASS = 256 / LPR;  // rows covered by the CTA per pass
+	pdl_launch_dependents();
+	pdl_wait();  // x, dt, B, C (and z) come from the kernel before this one; no-ops for a normal launch
 	const int64_t bh = blockIdx.x;            // one CTA per (batch, head)
 	const int h = static_cast<int>(bh % H);
 	const int64_t b = bh / H;
@@ -42,6 +48,14 @@ __global__ void __launch_bounds__(256) ssm_update_vec_kernel(float* __restrict__
 	{
 		const int p = prow + i * ROWS_PER_PASS;
 		xv[i] = p < P ? ldf(x + b * xs + static_cast<int64_t>(h) * P + p) : 0.f;
+	}
+	// GATE: rows are finished by thread p (one row each, P <= 256) after the CTA barrier below
+	__shared__ float y_rows[GATE ? RPT * ROWS_PER_PASS : 1];
+	float zv = 0.f, nwv = 0.f;
+	if (GATE && static_cast<int>(threadIdx.x) < P)
+	{
+		zv = ldf(z + b * zs + static_cast<int64_t>(h) * P + threadIdx.x);
+		nwv = ldf(norm_w + static_cast<int64_t>(h) * P + threadIdx.x);
 	}
 	if (dt_bias) dtv += dt_bias[h];
 	if (dt_softplus) dtv = softplus_f32(dtv);
@@ -69,7 +83,37 @@ __global__ void __launch_bounds__(256) ssm_update_vec_kernel(float* __restrict__
 		}
 #pragma unroll
 		for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-		if (p < P && sub == 0) stf(y + b * ys + static_cast<int64_t>(h) * P + p, acc + dh * xv[i]);
+		if (p < P && sub == 0)
+		{
+			const float out = acc + dh * xv[i];
+			if (GATE)
+				y_rows[p] = out;
+			else
+				stf(y + b * ys + static_cast<int64_t>(h) * P + p, out);
+		}
+	}
+	if (GATE)
+	{
+		__shared__ float warp_sq[8];
+		__syncthreads();
+		float sq = 0.f;
+		if (static_cast<int>(threadIdx.x) < P)
+		{
+			const float out = Cvt<T>::to_f32(Cvt<T>::from_f32(y_rows[threadIdx.x]));  // y as the tensor of type T it is between the operators
+			const float g = out * silu_f32(zv);
+			sq = g * g;
+			stf(y + b * ys + static_cast<int64_t>(h) * P + threadIdx.x, g * nwv);
+		}
+		sq = warp_sum(sq);
+		if ((threadIdx.x & 31) == 0) warp_sq[threadIdx.x >> 5] = sq;
+		__syncthreads();
+		if (threadIdx.x == 0)
+		{
+			float t = 0.f;
+#pragma unroll
+			for (int i = 0; i < 8; ++i) t += warp_sq[i];
+			sumsq[bh] = t;
+		}
 	}
 }
 
@@ -105,10 +149,11 @@ __global__ void __launch_bounds__(256) ssm_update_scalar_kernel(float* __restric
 	stf(y + b * ys + static_cast<int64_t>(h) * P + p, acc);
 }
 
-template <typename T>
+template <typename T, bool GATE = false>
 static int ssm_update(float* state, const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log,
 	const void* Bm, int64_t bs, const void* Cm, int64_t cs, const float* D, const float* dt_bias, void* y, int64_t ys,
-	int64_t batch, int64_t H, int64_t P, int64_t G, int64_t N, int dt_softplus, cudaStream_t st)
+	int64_t batch, int64_t H, int64_t P, int64_t G, int64_t N, int dt_softplus, cudaStream_t st, const void* z = nullptr, int64_t zs = 0,
+	const void* norm_w = nullptr, float* sumsq = nullptr)
 {
 	const int64_t nrows = batch * H * P;
 	const T* xp = static_cast<const T*>(x);
@@ -116,6 +161,8 @@ static int ssm_update(float* state, const void* x, int64_t xs, const void* dt, i
 	const T* bp = static_cast<const T*>(Bm);
 	const T* cp = static_cast<const T*>(Cm);
 	T* yp = static_cast<T*>(y);
+	const T* zp = static_cast<const T*>(z);
+	const T* nwp = static_cast<const T*>(norm_w);
 	const int h = static_cast<int>(H), p = static_cast<int>(P), g = static_cast<int>(G);
 #define B200_SSM_LAUNCH(LPR)                                                                                       \
 	{                                                                                                              \
@@ -124,20 +171,21 @@ static int ssm_update(float* state, const void* x, int64_t xs, const void* dt, i
 		if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;                                                    \
 		const unsigned gb = static_cast<unsigned>(blocks);                                                         \
 		if (P <= RPP)                                                                                              \
-			ssm_update_vec_kernel<T, LPR, 1><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
-				yp, ys, h, p, g, dt_softplus);                                                                     \
+			launch_rc = launch_chained(GATE && pdl_enabled(), ssm_update_vec_kernel<T, LPR, 1, GATE>, dim3(gb), dim3(256), 0, st, state, xp, xs, \
+					dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, yp, ys, h, p, g, dt_softplus, zp, zs, nwp, sumsq);                                                                     \
 		else if (P <= 2 * RPP)                                                                                     \
-			ssm_update_vec_kernel<T, LPR, 2><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
-				yp, ys, h, p, g, dt_softplus);                                                                     \
+			launch_rc = launch_chained(GATE && pdl_enabled(), ssm_update_vec_kernel<T, LPR, 2, GATE>, dim3(gb), dim3(256), 0, st, state, xp, xs, \
+					dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, yp, ys, h, p, g, dt_softplus, zp, zs, nwp, sumsq);                                                                     \
 		else if (P <= 4 * RPP)                                                                                     \
-			ssm_update_vec_kernel<T, LPR, 4><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
-				yp, ys, h, p, g, dt_softplus);                                                                     \
+			launch_rc = launch_chained(GATE && pdl_enabled(), ssm_update_vec_kernel<T, LPR, 4, GATE>, dim3(gb), dim3(256), 0, st, state, xp, xs, \
+					dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, yp, ys, h, p, g, dt_softplus, zp, zs, nwp, sumsq);                                                                     \
 		else if (P <= 8 * RPP)                                                                                     \
-			ssm_update_vec_kernel<T, LPR, 8><<<gb, 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, \
-				yp, ys, h, p, g, dt_softplus);                                                                     \
+			launch_rc = launch_chained(GATE && pdl_enabled(), ssm_update_vec_kernel<T, LPR, 8, GATE>, dim3(gb), dim3(256), 0, st, state, xp, xs, \
+					dtp, dts, A, a_is_log, bp, bs, cp, cs, D, dt_bias, yp, ys, h, p, g, dt_softplus, zp, zs, nwp, sumsq);                                                                     \
 		else                                                                                                       \
 			vec_ok = false;                                                                                        \
 	}
+	cudaError_t launch_rc = cudaSuccess;
 	// B and C are read as 4-element vectors: their rows must keep 4-element alignment
 	const size_t vbytes = 4 * sizeof(T);
 	bool vec_ok = aligned16(state) && (reinterpret_cast<uintptr_t>(Bm) % vbytes) == 0 && (reinterpret_cast<uintptr_t>(Cm) % vbytes) == 0 &&
@@ -148,14 +196,31 @@ static int ssm_update(float* state, const void* x, int64_t xs, const void* dt, i
 	else if (vec_ok && N == 16) B200_SSM_LAUNCH(4)
 	if (!vec_ok)
 	{
+		if (GATE) return B200_ERR_UNSUPPORTED;  // callers check ssm_update_gated_applies first
 		const int64_t blocks = cdiv(nrows, 256);
 		if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 		ssm_update_scalar_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs,
 			cp, cs, D, dt_bias, yp, ys, nrows, h, p, g, static_cast<int>(N), dt_softplus);
 	}
 #undef B200_SSM_LAUNCH
+	B200_CUDA_TRY(launch_rc);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
+}
+
+// Gated form used by the fused decode step (f16): see the GATE note above. sumsq is [batch, H].
+bool ssm_update_gated_applies(int64_t P, int64_t N, int64_t G)
+{
+	const int lpr = static_cast<int>(N / 4);
+	return (N == 128 || N == 64 || N == 32 || N == 16) && P <= 8 * (256 / lpr) && (G * N) % 4 == 0;
+}
+
+int ssm_update_gated_f16(float* state, const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm,
+	int64_t bs, const void* Cm, int64_t cs, const float* D, const float* dt_bias, void* y, int64_t ys, const void* z, int64_t zs,
+	const void* norm_w, float* sumsq, int64_t batch, int64_t H, int64_t P, int64_t G, int64_t N, int dt_softplus, cudaStream_t st)
+{
+	return ssm_update<__half, true>(state, x, xs, dt, dts, A, a_is_log, Bm, bs, Cm, cs, D, dt_bias, y, ys, batch, H, P, G, N, dt_softplus, st,
+		z, zs, norm_w, sumsq);
 }
 
 }  // namespace b200

@@ -284,6 +284,10 @@ int tmap_2d_f16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 int tmap_3d_f16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems, uint64_t s2_elems,
 	uint32_t box0, uint32_t box1);
 
+// 128-byte-swizzled fp32 map of a 3-D tensor (box of box0 <= 32 floats x box1 rows x 1).
+int tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems, uint64_t s2_elems,
+	uint32_t box0, uint32_t box1);
+
 // Unswizzled maps used by TMA STORES of small per-warp tiles (rows of box0 elements, dense in shared memory).
 int tmap_3d_f16_linear(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems,
 	uint64_t s2_elems, uint32_t box0, uint32_t box1);

@@ -119,6 +119,15 @@ int tmap_3d_f16_linear(CUtensorMap* out, const void* base, uint64_t d0, uint64_t
 	return cached_tmap(out, base, 3, dims, strides, box, false, false);
 }
 
+int tmap_3d_f32(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_elems, uint64_t s2_elems,
+	uint32_t box0, uint32_t box1)
+{
+	const uint64_t dims[3] = { d0, d1, d2 };
+	const uint64_t strides[2] = { s1_elems, s2_elems };
+	const uint32_t box[2] = { box0, box1 };
+	return cached_tmap(out, base, 3, dims, strides, box, true, true);
+}
+
 int tmap_2d_f32_linear(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_cols,
 	uint32_t box_rows)
 {

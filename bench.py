@@ -462,7 +462,7 @@ def run_kernel(args):
         flops_alg = float(b * nchunks * (H * (2 * Q * Q * P + 4 * Q * N * P) + G * 2 * Q * Q * N))
     elif k == "decode":
         c3 = workload("cfg3")
-        wts = ops.ZambaMamba2weights.from_numpy(synth.make_weights(c3, 0), h)
+        wts = ops.ZambaMamba2weights.from_numpy(synth.make_weights(c3, 0), h, layout=ops.W_NK if args.layout == "NK" else ops.W_KN)
         mixer = ops.Mamba2Mixer(c3, wts)
         cs, ss = synth.make_decode_state(c3, 0)
         cache = ops.ZambaMambaCache(torch.from_numpy(cs).cuda().half(), torch.from_numpy(ss).cuda())
@@ -512,6 +512,7 @@ def main():
     ap.add_argument("--tp-chunk", type=int, default=4)
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
+    ap.add_argument("--layout", default="KN", choices=["KN", "NK"], help="with --kernel decode: projection weight layout")
     ap.add_argument("--graph", action="store_true", help="with --kernel decode: replay the step from a CUDA graph")
     args = ap.parse_args()
     if args.kernel:
