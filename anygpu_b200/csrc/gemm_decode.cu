@@ -389,34 +389,58 @@ __global__ void __launch_bounds__(256) streamk_reduce_conv_kernel(const float* _
 	*reinterpret_cast<Half4*>(xbc + static_cast<int64_t>(r) * conv_dim + ch) = pack4(y[0], y[1], y[2], y[3]);
 }
 
-// out_proj consumer. Row r = blockIdx.y. With sumsq != nullptr the row is multiplied by rsqrt(sum_j sumsq[r, j] / norm_dim + eps):
-// the RMSNorm scale factored out of the projection (the projection's input then carries y * silu(z) * weight un-normalised).
+// out_proj consumer: many slices per tile (K is long, N short), so the slice loads are spread over the CTA as well. One CTA
+// per (256-column tile, row): 64 column quads x 4 slice groups; group g adds slices g, g+4, ... of its quad, the four group
+// sums are combined in group order through shared memory (again a fixed order), and warp 0 finishes 8 columns per lane.
+// With sumsq != nullptr the row is multiplied by rsqrt(sum_j sumsq[r, j] / norm_dim + eps): the RMSNorm scale factored out
+// of the projection (the projection's input then carries y * silu(z) * weight un-normalised).
 __global__ void __launch_bounds__(256) streamk_reduce_scale_kernel(const float* __restrict__ part, __half* __restrict__ out, int64_t ldo,
 	int M, int N, int k_blocks, int total_units, int grid, int max_seg, const float* __restrict__ sumsq, int nsumsq, float inv_norm_dim,
 	float eps)
 {
-	__shared__ float scale_s;
+	using namespace dgemm;
+	__shared__ float4 sm[4][64];
 	pdl_launch_dependents();
 	pdl_wait();
-	const int r = blockIdx.y;
-	if (threadIdx.x < 32)
-	{
-		float v = 1.f;
-		if (sumsq)
-		{
-			v = 0.f;
-			for (int j = threadIdx.x; j < nsumsq; j += 32) v += sumsq[static_cast<int64_t>(r) * nsumsq + j];
-			v = rsqrtf(warp_sum(v) * inv_norm_dim + eps);
-		}
-		if (threadIdx.x == 0) scale_s = v;
-	}
-	const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+	const int tile = blockIdx.x, r = blockIdx.y;
+	const int quad = threadIdx.x & 63, sg = threadIdx.x >> 6;
+	const int first = cta_of_unit(static_cast<int64_t>(tile) * k_blocks, grid, total_units);
+	const int nseg = cta_of_unit(static_cast<int64_t>(tile + 1) * k_blocks - 1, grid, total_units) - first + 1;
+	const float* p = part + ((static_cast<int64_t>(tile) * max_seg) * M + r) * BN + quad * 4;
+	const int64_t seg_stride = static_cast<int64_t>(M) * BN;
 	float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-	if (col < N) a = sum_slices4(part, r, col, M, k_blocks, total_units, grid, max_seg);
+#pragma unroll 4
+	for (int s = sg; s < nseg; s += 4)
+	{
+		const float4 t = *reinterpret_cast<const float4*>(p + s * seg_stride);
+		a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+	}
+	sm[sg][quad] = a;
+	const int lane = threadIdx.x;
+	float sc = 1.f;
+	if (lane < 32 && sumsq)
+	{
+		float v = 0.f;
+		for (int j = lane; j < nsumsq; j += 32) v += sumsq[static_cast<int64_t>(r) * nsumsq + j];
+		sc = rsqrtf(warp_sum(v) * inv_norm_dim + eps);
+	}
 	__syncthreads();
-	if (col >= N) return;
-	const float sc = scale_s;
-	*reinterpret_cast<Half4*>(out + static_cast<int64_t>(r) * ldo + col) = pack4(a.x * sc, a.y * sc, a.z * sc, a.w * sc);
+	const int col = tile * BN + lane * 8;
+	if (lane >= 32 || col >= N) return;
+	float f[8];
+#pragma unroll
+	for (int hh = 0; hh < 2; ++hh)
+	{
+		float4 t = sm[0][2 * lane + hh];
+#pragma unroll
+		for (int g = 1; g < 4; ++g)
+		{
+			const float4 v = sm[g][2 * lane + hh];
+			t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+		}
+		f[4 * hh] = t.x * sc; f[4 * hh + 1] = t.y * sc; f[4 * hh + 2] = t.z * sc; f[4 * hh + 3] = t.w * sc;
+	}
+	*reinterpret_cast<Half8*>(out + static_cast<int64_t>(r) * ldo + col) = pack8(f);
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------------
@@ -527,8 +551,9 @@ int decode_out_proj_scale(const void* x, int64_t ldx, const void* w, int w_layou
 	StreamKPlan p;
 	const int rc = decode_gemm(x, ldx, w, w_layout, M, K, N, part, &p, st);
 	if (rc) return rc;
-	const dim3 g(static_cast<unsigned>(cdiv(N / 4, 256)), static_cast<unsigned>(M));
-	B200_CUDA_TRY(launch_chained(pdl_enabled(), streamk_reduce_scale_kernel, g, dim3(256), 0, st, static_cast<const float*>(part),
+	const dim3 g(static_cast<unsigned>(p.n_tiles), static_cast<unsigned>(M));
+	// normal launch: measured slower when this kernel's CTAs are resident (waiting) while the projection before it runs
+	B200_CUDA_TRY(launch_chained(false, streamk_reduce_scale_kernel, g, dim3(256), 0, st, static_cast<const float*>(part),
 		static_cast<__half*>(out), ldo, static_cast<int>(M), static_cast<int>(N), p.k_blocks, p.total, p.grid, p.max_seg, sumsq, nsumsq,
 		1.0f / static_cast<float>(norm_dim), eps));
 	return B200_OK;

@@ -38,7 +38,8 @@ int decode_in_proj_conv(const void* x, int64_t ldx, const void* w, int w_layout,
 	cudaStream_t st);
 int decode_out_proj_scale(const void* x, int64_t ldx, const void* w, int w_layout, void* out, int64_t ldo, int64_t M, int64_t K, int64_t N,
 	const float* sumsq, int nsumsq, int64_t norm_dim, float eps, float* part, cudaStream_t st);
-bool ssm_update_gated_applies(int64_t P, int64_t N, int64_t G);
+bool ssm_update_gated_applies(int64_t H, int64_t P, int64_t N, int64_t G);
+int ssm_update_gated_partials();
 int ssm_update_gated_f16(float* state, const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm,
 	int64_t bs, const void* Cm, int64_t cs, const float* D, const float* dt_bias, void* y, int64_t ys, const void* z, int64_t zs,
 	const void* norm_w, float* sumsq, int64_t batch, int64_t H, int64_t P, int64_t G, int64_t N, int dt_softplus, cudaStream_t st);
@@ -365,7 +366,7 @@ extern "C" int b200_mamba2_mixer_tp_finish(int dtype, void* out, const float* su
 		static_cast<cudaStream_t>(stream));
 }
 
-// Decode workspace: zx | xbc | y | fp32 partial tiles of the stream-K projections | per-(row, head) sums of squares.
+// Decode workspace: zx | xbc | y | fp32 partial tiles of the stream-K projections | per-(row, head, warp) sums of squares.
 struct DecodeLayout
 {
 	size_t zx, xbc, y, part, sumsq, total;
@@ -387,7 +388,7 @@ static DecodeLayout decode_layout(const b200_mamba2_config* cfg, const MixerDims
 	L.part = off;
 	off += p_in > p_out ? p_in : p_out;
 	L.sumsq = off;
-	off += align_up(batch * cfg->nheads * sizeof(float), 256);
+	off += align_up(batch * cfg->nheads * ssm_update_gated_partials() * sizeof(float), 256);  // one per warp of the recurrence kernel's CTAs
 	L.total = off;
 	return L;
 }
@@ -430,7 +431,7 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	const bool fuse_in = decode_linear_applies(dtype, batch, cfg->d_model, m.d_in_proj) && d_inner % 8 == 0 && m.conv_dim % 8 == 0;
 	const bool fuse_out = decode_linear_applies(dtype, batch, d_inner, cfg->d_model);
 	const bool whole_row_norm = cfg->norm_group_size == 0 || cfg->norm_group_size == d_inner;
-	const bool fuse_gate = fuse_out && whole_row_norm && ssm_update_gated_applies(cfg->headdim, cfg->d_state, cfg->ngroups) && GN % 8 == 0;
+	const bool fuse_gate = fuse_out && whole_row_norm && ssm_update_gated_applies(cfg->nheads, cfg->headdim, cfg->d_state, cfg->ngroups) && GN % 8 == 0;
 
 	int rc;
 	if (fuse_in)
@@ -455,7 +456,7 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 			cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, 1, st);
 		if (rc) return rc;
 		return decode_out_proj_scale(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
-			sumsq, static_cast<int>(cfg->nheads), d_inner, cfg->eps, part, st);
+			sumsq, static_cast<int>(cfg->nheads) * ssm_update_gated_partials(), d_inner, cfg->eps, part, st);
 	}
 	rc = b200_selective_state_update(dtype, ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
 		xbc + d_inner * e, m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, batch, cfg->nheads,

@@ -400,7 +400,7 @@ def run_tp(args):
 def run_kernel(args):
     """Times one operator alone with CUDA events: `--kernel NAME [--small] --steps K --warmup W`.
     conv1d_prefill / conv1d_decode: the standalone conv configuration (batch 8, 4224 channels, 4096 tokens; 256 decode steps).
-    decode: the Zamba2-2.7B-shaped decode step (batch 64). in_proj / out_proj / conv1d_tokens / ssd / gated_rmsnorm: the stages
+    decode: the Zamba2-2.7B-shaped decode step (batch 64); ssm_update: its state recurrence alone. in_proj / out_proj / conv1d_tokens / ssd / gated_rmsnorm: the stages
     of the cfg2 mixer on their in-mixer shapes. --small shrinks the token count (profiler-sized case, still larger than L2
     where the operator is bandwidth-bound)."""
     import torch
@@ -460,6 +460,16 @@ def run_kernel(args):
                                                         t[:, :, H * P + G * N:].unflatten(2, (G, N)), Q, D=D, dt_bias=dtb)
         nchunks = -(-l // Q)
         flops_alg = float(b * nchunks * (H * (2 * Q * Q * P + 4 * Q * N * P) + G * 2 * Q * Q * N))
+    elif k == "ssm_update":
+        c3 = workload("cfg3")
+        B_, H_, P_, N_, G_ = c3["batch"], c3["nheads"], c3["headdim"], c3["d_state"], c3["ngroups"]
+        state = torch.randn(B_, H_, P_, N_, device="cuda", generator=g) * 0.1
+        xs_, dts_ = rn(B_, H_, P_, std=0.5), rn(B_, H_)
+        Bs_, Cs_ = rn(B_, G_, N_, std=0.5), rn(B_, G_, N_, std=0.5)
+        A_ = -(torch.rand(H_, device="cuda", generator=g) * 15 + 1)
+        D_, dtb_ = torch.ones(H_, device="cuda"), torch.full((H_,), -3.0, device="cuda")
+        fn = lambda i: ops.tensor_mamba_selective_state_update(state, xs_, dts_, A_, Bs_, Cs_, D=D_, dt_bias=dtb_)
+        bytes_alg = 2 * state.numel() * 4
     elif k == "decode":
         c3 = workload("cfg3")
         wts = ops.ZambaMamba2weights.from_numpy(synth.make_weights(c3, 0), h, layout=ops.W_NK if args.layout == "NK" else ops.W_KN)

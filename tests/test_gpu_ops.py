@@ -269,7 +269,8 @@ def test_ssd_f16_in_place_slices(ops):
 
 # ---- decode recurrence --------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("dims", [(3, 8, 64, 1, 64), (2, 4, 64, 2, 128), (2, 8, 64, 1, 16), (1, 2, 8, 1, 24)])
+@pytest.mark.parametrize("dims", [(3, 8, 64, 1, 64), (2, 4, 64, 2, 128), (2, 8, 64, 1, 16), (1, 2, 8, 1, 24), (2, 4, 32, 1, 64),
+                                  (2, 4, 40, 2, 64), (2, 3, 16, 1, 32), (1, 2, 128, 1, 16), (2, 2, 8, 1, 64), (1, 2, 100, 1, 32)])
 @pytest.mark.parametrize("dtype", ["f16", "f32"])
 def test_selective_state_update_steps(ops, dims, dtype):
     b, H, P, G, N = dims
