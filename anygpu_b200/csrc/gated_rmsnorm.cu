@@ -191,6 +191,104 @@ __global__ void __launch_bounds__(256) row_scale_rsqrt_kernel(T* __restrict__ ou
 	stf(p, ldf(p) * rsqrtf(sumsq[r] * inv_d + eps));
 }
 
+// ---- plain RMSNorm (the input norm of the decoder layer around the mixer) ----------------------------------------------
+// y = x * rsqrt(mean(x^2) + eps) * (w + delta), tensor_rms_norm over the last axis (srcs/ops/norm_ops.hpp:134-191; delta = 1
+// for its zero_centered flag). One CTA per row, the row cached in registers between the statistic and the scaling when it fits.
+template <typename T, int THREADS, int CACHE>
+__global__ void __launch_bounds__(THREADS) rms_norm_vec_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+	T* __restrict__ y, int64_t ys, int d, float eps, float delta)
+{
+	constexpr int E = NV<T>::E;
+	__shared__ float red[THREADS / 32];
+	const int64_t row = blockIdx.x;
+	const T* xr = x + row * xs;
+	T* yr = y + row * ys;
+	const int nvec = d / E;
+	float v[CACHE][E], wv[CACHE][E];
+	float ss = 0.f;
+#pragma unroll
+	for (int it = 0; it < CACHE; ++it)
+	{
+		const int i = threadIdx.x + it * THREADS;
+		if (i < nvec)
+		{
+			NV<T>::load(xr + i * E, v[it]);
+			NV<T>::load(w + i * E, wv[it]);
+#pragma unroll
+			for (int e = 0; e < E; ++e) ss += v[it][e] * v[it][e];
+		}
+	}
+	for (int i = threadIdx.x + CACHE * THREADS; i < nvec; i += THREADS)  // rows longer than the cache: second pass below
+	{
+		float t[E];
+		NV<T>::load(xr + i * E, t);
+#pragma unroll
+		for (int e = 0; e < E; ++e) ss += t[e] * t[e];
+	}
+	const float scale = rsqrtf(block_sum<THREADS>(ss, red) / static_cast<float>(d) + eps);
+#pragma unroll
+	for (int it = 0; it < CACHE; ++it)
+	{
+		const int i = threadIdx.x + it * THREADS;
+		if (i < nvec)
+		{
+			float o[E];
+#pragma unroll
+			for (int e = 0; e < E; ++e) o[e] = v[it][e] * scale * (wv[it][e] + delta);
+			NV<T>::store(yr + i * E, o);
+		}
+	}
+	for (int i = threadIdx.x + CACHE * THREADS; i < nvec; i += THREADS)
+	{
+		float t[E], wt[E], o[E];
+		NV<T>::load(xr + i * E, t);
+		NV<T>::load(w + i * E, wt);
+#pragma unroll
+		for (int e = 0; e < E; ++e) o[e] = t[e] * scale * (wt[e] + delta);
+		NV<T>::store(yr + i * E, o);
+	}
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rms_norm_scalar_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+	T* __restrict__ y, int64_t ys, int d, float eps, float delta)
+{
+	__shared__ float red[8];
+	const int64_t row = blockIdx.x;
+	const T* xr = x + row * xs;
+	T* yr = y + row * ys;
+	float ss = 0.f;
+	for (int i = threadIdx.x; i < d; i += 256)
+	{
+		const float t = ldf(xr + i);
+		ss += t * t;
+	}
+	const float scale = rsqrtf(block_sum<256>(ss, red) / static_cast<float>(d) + eps);
+	for (int i = threadIdx.x; i < d; i += 256) stf(yr + i, ldf(xr + i) * scale * (ldf(w + i) + delta));
+}
+
+template <typename T>
+static int rms_norm(const void* xv, int64_t xs, const void* wv, void* yv, int64_t ys, int64_t rows, int64_t d, float eps, float delta,
+	cudaStream_t st)
+{
+	constexpr int E = NV<T>::E;
+	const T* x = static_cast<const T*>(xv);
+	const T* w = static_cast<const T*>(wv);
+	T* y = static_cast<T*>(yv);
+	if (rows > 0x7fffffffLL || d > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	const unsigned g = static_cast<unsigned>(rows);
+	const int dd = static_cast<int>(d);
+	const bool vec = aligned16(x) && aligned16(w) && aligned16(y) && xs % E == 0 && ys % E == 0 && d % E == 0;
+	if (!vec)
+		rms_norm_scalar_kernel<T><<<g, 256, 0, st>>>(x, xs, w, y, ys, dd, eps, delta);
+	else if (d / E <= 2 * 128)
+		rms_norm_vec_kernel<T, 128, 2><<<g, 128, 0, st>>>(x, xs, w, y, ys, dd, eps, delta);
+	else
+		rms_norm_vec_kernel<T, 256, 2><<<g, 256, 0, st>>>(x, xs, w, y, ys, dd, eps, delta);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
 template <typename T>
 static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs, const void* wv, void* yv, int64_t ys,
 	int64_t rows, int64_t d, int64_t gsize, float eps, cudaStream_t st)
@@ -265,5 +363,18 @@ extern "C" int b200_gated_rmsnorm(int dtype, const void* x, int64_t x_stride, co
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	if (dtype == B200_F16) return gated_rmsnorm<__half>(x, x_stride, z, z_stride, w, y, y_stride, rows, d, group_size, eps, st);
 	if (dtype == B200_F32) return gated_rmsnorm<float>(x, x_stride, z, z_stride, w, y, y_stride, rows, d, group_size, eps, st);
+	return B200_ERR_UNSUPPORTED;
+}
+
+extern "C" int b200_rms_norm(int dtype, const void* x, int64_t x_stride, const void* w, void* y, int64_t y_stride, int64_t rows,
+	int64_t dim, float eps, int zero_centered, void* stream)
+{
+	if (!x || !w || !y) return B200_ERR_NULL;
+	if (rows < 0 || dim <= 0 || x_stride < dim || y_stride < dim) return B200_ERR_BAD_SHAPE;
+	if (rows == 0) return B200_OK;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	const float delta = zero_centered ? 1.f : 0.f;
+	if (dtype == B200_F16) return rms_norm<__half>(x, x_stride, w, y, y_stride, rows, dim, eps, delta, st);
+	if (dtype == B200_F32) return rms_norm<float>(x, x_stride, w, y, y_stride, rows, dim, eps, delta, st);
 	return B200_ERR_UNSUPPORTED;
 }

@@ -45,7 +45,7 @@ using CfgSkinny64 = Cfg<64, 13, 1, 1, 64>;  // M <= 64: 13 x 16 KiB ring, 104 Ki
 template <int B_MN, class C>
 __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M, int N, int K, int m_tiles, int n_tiles,
-	uint32_t* err_word)
+	uint32_t* err_word, const __half* __restrict__ residual, int64_t ldr)
 {
 	using namespace gemm;
 	using namespace tc;
@@ -205,14 +205,24 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 				tmem_ld_wait();
 				const uint32_t buf = nchunk % STG_BUFS;
 				uint8_t* srow = stg + buf * STG_BYTES + lane * 128;
+				// optional residual: Y = X.W + R (R f16, row stride ldr), added in fp32 before the one rounding
+				const int rrow = m0 + q * 32 + lane;
+				const __half* rp = residual != nullptr && rrow < M ? residual + static_cast<int64_t>(rrow) * ldr + n0 + c * 64 : nullptr;
 #pragma unroll
 				for (int v = 0; v < 8; ++v)
 				{
 					const uint32_t* src = v < 4 ? r0 + v * 8 : r1 + (v - 4) * 8;
-					Half8 h;
+					float f[8];
 #pragma unroll
-					for (int e = 0; e < 4; ++e) h.h[e] = __floats2half2_rn(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
-					*reinterpret_cast<Half8*>(srow + ((v ^ (lane & 7)) << 4)) = h;
+					for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(src[e]);
+					if (rp != nullptr && n0 + c * 64 + v * 8 < N)  // N % 8 == 0
+					{
+						float rv[8];
+						unpack8(*reinterpret_cast<const Half8*>(rp + v * 8), rv);
+#pragma unroll
+						for (int e = 0; e < 8; ++e) f[e] += rv[e];
+					}
+					*reinterpret_cast<Half8*>(srow + ((v ^ (lane & 7)) << 4)) = pack8(f);
 				}
 				fence_proxy_async_smem();
 				__syncwarp();
@@ -267,7 +277,7 @@ constexpr uint32_t TMEM_COLS = 512;
 template <int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) gemm_f16_tcgen05_pair_kernel(
 	const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M,
-	int N, int K, int m_tiles /* of 256 rows */, int n_tiles, uint32_t* err_word)
+	int N, int K, int m_tiles /* of 256 rows */, int n_tiles, uint32_t* err_word, const __half* __restrict__ residual, int64_t ldr)
 {
 	using namespace gemm2;
 	using namespace tc;
@@ -427,14 +437,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) g
 				tmem_ld_wait();
 				const uint32_t buf = nchunk % STG_BUFS;
 				uint8_t* srow = stg + buf * STG_BYTES + lane * 128;
+				// optional residual: Y = X.W + R (R f16, row stride ldr), added in fp32 before the one rounding
+				const int rrow = m0 + q * 32 + lane;
+				const __half* rp = residual != nullptr && rrow < M ? residual + static_cast<int64_t>(rrow) * ldr + n0 + c * 64 : nullptr;
 #pragma unroll
 				for (int v = 0; v < 8; ++v)
 				{
 					const uint32_t* src = v < 4 ? r0 + v * 8 : r1 + (v - 4) * 8;
-					Half8 h;
+					float f[8];
 #pragma unroll
-					for (int e = 0; e < 4; ++e) h.h[e] = __floats2half2_rn(__uint_as_float(src[2 * e]), __uint_as_float(src[2 * e + 1]));
-					*reinterpret_cast<Half8*>(srow + ((v ^ (lane & 7)) << 4)) = h;
+					for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(src[e]);
+					if (rp != nullptr && n0 + c * 64 + v * 8 < N)  // N % 8 == 0
+					{
+						float rv[8];
+						unpack8(*reinterpret_cast<const Half8*>(rp + v * 8), rv);
+#pragma unroll
+						for (int e = 0; e < 8; ++e) f[e] += rv[e];
+					}
+					*reinterpret_cast<Half8*>(srow + ((v ^ (lane & 7)) << 4)) = pack8(f);
 				}
 				fence_proxy_async_smem();
 				__syncwarp();
@@ -468,7 +488,8 @@ role_done:
 }
 
 template <int B_MN>
-static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st)
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st,
+	const __half* residual, int64_t ldr)
 {
 	using namespace gemm2;
 	static bool attr_set = false;
@@ -481,13 +502,14 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
 	const int64_t pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
 	gemm_f16_tcgen05_pair_kernel<B_MN><<<static_cast<unsigned>(2 * pairs), THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles,
-		n_tiles, device_error_word());
+		n_tiles, device_error_word(), residual, ldr);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }
 
 template <int B_MN, class C>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st)
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st,
+	const __half* residual, int64_t ldr)
 {
 	using namespace gemm;
 	static bool attr_set = false;
@@ -500,17 +522,19 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
 	const int64_t slots = static_cast<int64_t>(kNumSMs) * C::MIN_CTAS;
 	const unsigned grid = static_cast<unsigned>(tiles < slots ? tiles : slots);
-	gemm_f16_tcgen05_kernel<B_MN, C><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles, n_tiles, device_error_word());
+	gemm_f16_tcgen05_kernel<B_MN, C><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles, n_tiles, device_error_word(),
+		residual, ldr);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }
 
 static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout, __half* y, int64_t ldy, int64_t M, int64_t K,
-	int64_t N, cudaStream_t st)
+	int64_t N, cudaStream_t st, const __half* residual = nullptr, int64_t ldr = 0)
 {
 	using namespace gemm;
 	if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y))
 		return B200_ERR_MISALIGNED;
+	if (residual && (ldr % 8 != 0 || !aligned16(residual))) return B200_ERR_MISALIGNED;
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 	// wide tiles once they fill most of the machine; otherwise skinny tiles, two CTAs per SM
 	const bool wide = cdiv(M, BM) * cdiv(N, 256) >= 96;
@@ -528,14 +552,24 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 		rc = tmap_2d_f16(&tmB, w, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(N), 64, BK);
 	if (rc) return rc;
 	const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
-	if (paired) return w_layout == B200_W_NK ? launch_gemm_pair<0>(tmA, tmB, tmY, m, n, k, st) : launch_gemm_pair<1>(tmA, tmB, tmY, m, n, k, st);
+	if (paired) return w_layout == B200_W_NK ? launch_gemm_pair<0>(tmA, tmB, tmY, m, n, k, st, residual, ldr) : launch_gemm_pair<1>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
 	if (w_layout == B200_W_NK)
 	{
-		if (wide) return launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st);
-		return tiny_m ? launch_gemm<0, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
+		if (wide) return launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
+		return tiny_m ? launch_gemm<0, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st, residual, ldr) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
 	}
-	if (wide) return launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st);
-	return tiny_m ? launch_gemm<1, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st);
+	if (wide) return launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
+	return tiny_m ? launch_gemm<1, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st, residual, ldr) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
+}
+
+// Y = X . W + R, f16 (R: residual stream of the layer around the projection, added in the epilogue).
+int linear_f16_residual(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+	const void* residual, int64_t ldr, cudaStream_t st)
+{
+	if (w_layout != B200_W_KN && w_layout != B200_W_NK) return B200_ERR_UNSUPPORTED;
+	if (M == 0 || N == 0) return B200_OK;
+	return gemm_f16(static_cast<const __half*>(x), ldx, static_cast<const __half*>(w), w_layout, static_cast<__half*>(y), ldy, M, K, N, st,
+		static_cast<const __half*>(residual), ldr);
 }
 
 // ---- f32 SIMT kernel --------------------------------------------------------------------------------------

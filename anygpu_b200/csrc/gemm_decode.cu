@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(256) streamk_reduce_conv_kernel(const float* _
 // of the projection (the projection's input then carries y * silu(z) * weight un-normalised).
 __global__ void __launch_bounds__(256) streamk_reduce_scale_kernel(const float* __restrict__ part, __half* __restrict__ out, int64_t ldo,
 	int M, int N, int k_blocks, int total_units, int grid, int max_seg, const float* __restrict__ sumsq, int nsumsq, float inv_norm_dim,
-	float eps)
+	float eps, const __half* __restrict__ residual, int64_t ldr)
 {
 	using namespace dgemm;
 	__shared__ float4 sm[4][64];
@@ -439,6 +439,13 @@ __global__ void __launch_bounds__(256) streamk_reduce_scale_kernel(const float* 
 			t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
 		}
 		f[4 * hh] = t.x * sc; f[4 * hh + 1] = t.y * sc; f[4 * hh + 2] = t.z * sc; f[4 * hh + 3] = t.w * sc;
+	}
+	if (residual != nullptr)  // the residual stream of the layer around the mixer, added before the one rounding
+	{
+		float rv[8];
+		unpack8(*reinterpret_cast<const Half8*>(residual + static_cast<int64_t>(r) * ldr + col), rv);
+#pragma unroll
+		for (int j = 0; j < 8; ++j) f[j] += rv[j];
 	}
 	*reinterpret_cast<Half8*>(out + static_cast<int64_t>(r) * ldo + col) = pack8(f);
 }
@@ -543,11 +550,13 @@ int decode_in_proj_conv(const void* x, int64_t ldx, const void* w, int w_layout,
 	return B200_OK;
 }
 
-// out_proj of a decode step; sumsq [M, nsumsq] (or nullptr) carries the partial sums of squares of the RMSNorm.
+// out_proj of a decode step; sumsq [M, nsumsq] (or nullptr) carries the partial sums of squares of the RMSNorm; residual
+// [M, >= N] (or nullptr) is added to the result.
 int decode_out_proj_scale(const void* x, int64_t ldx, const void* w, int w_layout, void* out, int64_t ldo, int64_t M, int64_t K, int64_t N,
-	const float* sumsq, int nsumsq, int64_t norm_dim, float eps, float* part, cudaStream_t st)
+	const float* sumsq, int nsumsq, int64_t norm_dim, float eps, float* part, cudaStream_t st, const void* residual, int64_t ldr)
 {
 	if (ldo % 8 != 0 || !aligned16(out)) return B200_ERR_MISALIGNED;
+	if (residual && (ldr % 8 != 0 || !aligned16(residual))) return B200_ERR_MISALIGNED;
 	StreamKPlan p;
 	const int rc = decode_gemm(x, ldx, w, w_layout, M, K, N, part, &p, st);
 	if (rc) return rc;
@@ -555,7 +564,7 @@ int decode_out_proj_scale(const void* x, int64_t ldx, const void* w, int w_layou
 	// normal launch: measured slower when this kernel's CTAs are resident (waiting) while the projection before it runs
 	B200_CUDA_TRY(launch_chained(false, streamk_reduce_scale_kernel, g, dim3(256), 0, st, static_cast<const float*>(part),
 		static_cast<__half*>(out), ldo, static_cast<int>(M), static_cast<int>(N), p.k_blocks, p.total, p.grid, p.max_seg, sumsq, nsumsq,
-		1.0f / static_cast<float>(norm_dim), eps));
+		1.0f / static_cast<float>(norm_dim), eps, static_cast<const __half*>(residual), ldr));
 	return B200_OK;
 }
 

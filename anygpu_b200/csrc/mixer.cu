@@ -30,6 +30,9 @@ static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
 	return true;
 }
 
+int linear_f16_residual(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+	const void* residual, int64_t ldr, cudaStream_t st);
+
 // fused decode stages (gemm_decode.cu, ssm_update.cu)
 bool decode_linear_applies(int dtype, int64_t M, int64_t K, int64_t N);
 size_t decode_linear_partial_bytes(int64_t M, int64_t K, int64_t N);
@@ -37,7 +40,7 @@ int decode_in_proj_conv(const void* x, int64_t ldx, const void* w, int w_layout,
 	int64_t conv_lo, int64_t conv_dim, int conv_width, void* conv_state, const void* conv_w, const void* conv_b, void* xbc, float* part,
 	cudaStream_t st);
 int decode_out_proj_scale(const void* x, int64_t ldx, const void* w, int w_layout, void* out, int64_t ldo, int64_t M, int64_t K, int64_t N,
-	const float* sumsq, int nsumsq, int64_t norm_dim, float eps, float* part, cudaStream_t st);
+	const float* sumsq, int nsumsq, int64_t norm_dim, float eps, float* part, cudaStream_t st, const void* residual, int64_t ldr);
 bool ssm_update_gated_applies(int64_t H, int64_t P, int64_t N, int64_t G);
 int ssm_update_gated_partials();
 int ssm_update_gated_f16(float* state, const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm,
@@ -88,6 +91,44 @@ static PrefillWs carve_prefill(void* base, const b200_mamba2_config* c, const Mi
 	return w;
 }
 
+
+// out += residual, row by row (the paths whose projection has no fused residual: fp32 tensors, unaligned shapes)
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_kernel(T* __restrict__ out, int64_t ldo, const T* __restrict__ res, int64_t ldr,
+	int64_t rows, int cols)
+{
+	const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= rows * cols) return;
+	const int64_t r = i / cols;
+	const int c = static_cast<int>(i - r * cols);
+	stf(out + r * ldo + c, ldf(out + r * ldo + c) + ldf(res + r * ldr + c));
+}
+
+static int residual_add(int dtype, void* out, int64_t ldo, const void* res, int64_t ldr, int64_t rows, int64_t cols, cudaStream_t st)
+{
+	const int64_t blocks = cdiv(rows * cols, 256);
+	if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	if (dtype == B200_F16)
+		residual_add_kernel<__half><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<__half*>(out), ldo,
+			static_cast<const __half*>(res), ldr, rows, static_cast<int>(cols));
+	else
+		residual_add_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, st>>>(static_cast<float*>(out), ldo,
+			static_cast<const float*>(res), ldr, rows, static_cast<int>(cols));
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+// out = y . W_out (+ residual): the projection that ends the mixer; the residual of the layer around it rides in the epilogue
+// of the f16 tensor-core GEMM, otherwise it is added by a second kernel.
+static int out_proj_residual(int dtype, const void* y, int64_t ldy, const void* w, int layout, void* out, int64_t ldo, int64_t T,
+	int64_t K, int64_t N, const void* residual, int64_t ldr, cudaStream_t st)
+{
+	if (residual && dtype == B200_F16 && K % 8 == 0 && N % 8 == 0 && ldr % 8 == 0 && aligned16(residual))
+		return linear_f16_residual(y, ldy, w, layout, out, ldo, T, K, N, residual, ldr, st);
+	const int rc = b200_linear(dtype, y, ldy, w, layout, out, ldo, T, K, N, st);
+	if (rc || !residual) return rc;
+	return residual_add(dtype, out, ldo, residual, ldr, T, N, st);
+}
 }  // namespace b200
 
 using namespace b200;
@@ -99,10 +140,11 @@ extern "C" size_t b200_mamba2_mixer_prefill_workspace_bytes(const b200_mamba2_co
 	return carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
 }
 
-extern "C" int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+// The prefill mixer; `residual` [T, >= d_model] (or nullptr) is added to the result (may alias `out`).
+static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u, void* out, int64_t batch, int64_t seqlen,
 	const float* initial_states, void* conv_state_out, float* ssm_state_out,
-	void* workspace, size_t workspace_bytes, void* stream)
+	void* workspace, size_t workspace_bytes, void* stream, const void* residual, int64_t ldr)
 {
 	if (!cfg || !w || !u || !out) return B200_ERR_NULL;
 	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
@@ -139,12 +181,21 @@ extern "C" int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cf
 		cfg->norm_group_size, cfg->eps, stream);
 	if (rc) return rc;
 	stage_mark(4, st);
-	rc = b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out, cfg->d_model, T, d_inner, cfg->d_model,
-		stream);
+	rc = out_proj_residual(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out, cfg->d_model, T, d_inner, cfg->d_model,
+		residual, ldr, st);
 	if (rc) return rc;
 	stage_mark(5, st);
 	if (g_timing.enabled && g_timing.calls < kTimingSlots) ++g_timing.calls;
 	return B200_OK;
+}
+
+extern "C" int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, int64_t batch, int64_t seqlen,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	return mixer_prefill_impl(dtype, cfg, w, u, out, batch, seqlen, initial_states, conv_state_out, ssm_state_out, workspace,
+		workspace_bytes, stream, nullptr, 0);
 }
 
 extern "C" int b200_stage_timing_enable(int enable)
@@ -404,9 +455,9 @@ extern "C" size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_con
 //   stream-K in_proj -> slice sum + rolling conv1d/SiLU -> recurrence + gate (+ sums of squares) -> stream-K out_proj ->
 //   slice sum + RMSNorm row scale.
 // Otherwise the operators run one by one (linear, conv update, recurrence, gated RMSNorm, linear).
-extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+static int mixer_decode_impl(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
-	void* workspace, size_t workspace_bytes, void* stream)
+	void* workspace, size_t workspace_bytes, void* stream, const void* residual, int64_t ldr)
 {
 	if (!cfg || !w || !u_t || !out_t || !conv_state || !ssm_state) return B200_ERR_NULL;
 	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
@@ -456,7 +507,7 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 			cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, 1, st);
 		if (rc) return rc;
 		return decode_out_proj_scale(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
-			sumsq, static_cast<int>(cfg->nheads) * ssm_update_gated_partials(), d_inner, cfg->eps, part, st);
+			sumsq, static_cast<int>(cfg->nheads) * ssm_update_gated_partials(), d_inner, cfg->eps, part, st, residual, ldr);
 	}
 	rc = b200_selective_state_update(dtype, ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
 		xbc + d_inner * e, m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, batch, cfg->nheads,
@@ -467,7 +518,73 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	if (rc) return rc;
 	if (fuse_out)
 		return decode_out_proj_scale(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
-			nullptr, 0, d_inner, cfg->eps, part, st);
-	return b200_linear(dtype, y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
-		stream);
+			nullptr, 0, d_inner, cfg->eps, part, st, residual, ldr);
+	return out_proj_residual(dtype, y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
+		residual, ldr, st);
+}
+
+extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	return mixer_decode_impl(dtype, cfg, w, u_t, out_t, conv_state, ssm_state, batch, workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+// ---- Zamba2 Mamba decoder layer around the mixer: out = hidden + mixer(rms_norm(hidden) * input_norm_weight) -------------
+// Workspace: the normalised hidden states [T, d_model], then the mixer's own workspace.
+extern "C" size_t b200_mamba2_decoder_prefill_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen)
+{
+	const size_t inner = b200_mamba2_mixer_prefill_workspace_bytes(cfg, dtype, batch, seqlen);
+	if (inner == 0) return 0;
+	return align_up(static_cast<size_t>(batch) * seqlen * cfg->d_model * (dtype == B200_F16 ? 2 : 4), 256) + inner;
+}
+
+extern "C" int b200_mamba2_decoder_prefill(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* input_norm_weight, float rms_eps, const void* hidden, void* out, int64_t batch, int64_t seqlen,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out, void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !input_norm_weight || !hidden || !out) return B200_ERR_NULL;
+	if (dtype != B200_F16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+	if (batch < 0 || seqlen < 0 || cfg->d_model <= 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const size_t need = b200_mamba2_decoder_prefill_workspace_bytes(cfg, dtype, batch, seqlen);
+	if (need == 0) return B200_ERR_BAD_SHAPE;
+	if (workspace_bytes < need) return B200_ERR_WORKSPACE;
+	const int64_t T = batch * seqlen;
+	const size_t normed_bytes = align_up(static_cast<size_t>(T) * cfg->d_model * (dtype == B200_F16 ? 2 : 4), 256);
+	char* normed = static_cast<char*>(workspace);
+	int rc = b200_rms_norm(dtype, hidden, cfg->d_model, input_norm_weight, normed, cfg->d_model, T, cfg->d_model, rms_eps, 0, stream);
+	if (rc) return rc;
+	return mixer_prefill_impl(dtype, cfg, w, normed, out, batch, seqlen, initial_states, conv_state_out, ssm_state_out,
+		normed + normed_bytes, workspace_bytes - normed_bytes, stream, hidden, cfg->d_model);
+}
+
+extern "C" size_t b200_mamba2_decoder_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch)
+{
+	const size_t inner = b200_mamba2_mixer_decode_workspace_bytes(cfg, dtype, batch);
+	if (inner == 0) return 0;
+	return align_up(static_cast<size_t>(batch) * cfg->d_model * (dtype == B200_F16 ? 2 : 4), 256) + inner;
+}
+
+extern "C" int b200_mamba2_decoder_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* input_norm_weight, float rms_eps, const void* hidden_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !input_norm_weight || !hidden_t || !out_t) return B200_ERR_NULL;
+	if (dtype != B200_F16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+	if (batch < 0 || cfg->d_model <= 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const size_t need = b200_mamba2_decoder_decode_workspace_bytes(cfg, dtype, batch);
+	if (need == 0) return B200_ERR_BAD_SHAPE;
+	if (workspace_bytes < need) return B200_ERR_WORKSPACE;
+	const size_t normed_bytes = align_up(static_cast<size_t>(batch) * cfg->d_model * (dtype == B200_F16 ? 2 : 4), 256);
+	char* normed = static_cast<char*>(workspace);
+	int rc = b200_rms_norm(dtype, hidden_t, cfg->d_model, input_norm_weight, normed, cfg->d_model, batch, cfg->d_model, rms_eps, 0, stream);
+	if (rc) return rc;
+	return mixer_decode_impl(dtype, cfg, w, normed, out_t, conv_state, ssm_state, batch, normed + normed_bytes,
+		workspace_bytes - normed_bytes, stream, hidden_t, cfg->d_model);
 }

@@ -106,6 +106,18 @@ def tensor_zamba_gated_rmsnorm(xt, zt, wt, gsize, eps, honor_gsize=False):
     return y.view(xt.shape) if xt.is_contiguous() else y
 
 
+def tensor_rms_norm(xt, wt, eps, zero_centered=False):
+    """tensor_rms_norm over the last axis (srcs/ops/norm_ops.hpp:134-228): x * rsqrt(mean(x^2) + eps) * (w + zero_centered)."""
+    d = xt.shape[-1]
+    x2 = xt.reshape(-1, d)
+    _rows_contig(x2)
+    assert wt.is_contiguous() and wt.numel() == d
+    y = torch.empty((x2.shape[0], d), dtype=xt.dtype, device=xt.device)
+    capi.call("b200_rms_norm", _dt(xt), _p(x2), x2.stride(0), _p(wt), _p(y), d, x2.shape[0], d, float(eps), int(zero_centered),
+              _stream())
+    return y.reshape(xt.shape)
+
+
 def _tok_stride(t, inner):
     """Element stride between tokens of a [b, l, ...] tensor whose trailing dims are dense."""
     assert t.stride(-1) == 1
@@ -254,6 +266,39 @@ class Mamba2Mixer:
         with torch.cuda.graph(graph):
             self.decode(u_t, cache, out=out)
         return graph
+
+
+class Mamba2DecoderLayer:
+    """The Zamba2 Mamba decoder layer around the mixer: out = hidden + mixer(rms_norm(hidden) * input_norm_weight).
+    One C-ABI call per prefill / decode step; the residual is added inside the last projection."""
+
+    def __init__(self, cfg, weights, input_norm_weight, rms_eps=1e-5):
+        self.mixer = Mamba2Mixer(cfg, weights)
+        self.norm_w, self.rms_eps = input_norm_weight.contiguous(), float(rms_eps)
+        self.dtype = self.mixer.dtype
+
+    def prefill(self, hidden, cache=None, initial_states=None, out=None):
+        b, l, _ = hidden.shape
+        assert hidden.is_contiguous() and hidden.dtype == self.dtype
+        m, lib = self.mixer, capi.load()
+        ws = m._ensure_ws(lib.b200_mamba2_decoder_prefill_workspace_bytes(ctypes.byref(m.c_cfg), _DT[self.dtype], b, l))
+        if out is None:
+            out = torch.empty_like(hidden)
+        capi.call("b200_mamba2_decoder_prefill", _DT[self.dtype], ctypes.byref(m.c_cfg), ctypes.byref(m.c_w), _p(self.norm_w),
+                  self.rms_eps, _p(hidden), _p(out), b, l, _p(initial_states), _p(cache.conv_state) if cache else None,
+                  _p(cache.ssm_state) if cache else None, _p(ws), ws.numel(), _stream())
+        return out
+
+    def decode(self, hidden_t, cache, out=None):
+        b = hidden_t.shape[0]
+        assert hidden_t.is_contiguous() and hidden_t.dtype == self.dtype
+        m, lib = self.mixer, capi.load()
+        ws = m._ensure_ws(lib.b200_mamba2_decoder_decode_workspace_bytes(ctypes.byref(m.c_cfg), _DT[self.dtype], b))
+        if out is None:
+            out = torch.empty_like(hidden_t)
+        capi.call("b200_mamba2_decoder_decode", _DT[self.dtype], ctypes.byref(m.c_cfg), ctypes.byref(m.c_w), _p(self.norm_w),
+                  self.rms_eps, _p(hidden_t), _p(out), _p(cache.conv_state), _p(cache.ssm_state), b, _p(ws), ws.numel(), _stream())
+        return out
 
 
 class Mamba2MixerTP:

@@ -109,6 +109,13 @@ int b200_causal_conv1d_update(int dtype, const void* x_t, int64_t x_stride, void
 int b200_gated_rmsnorm(int dtype, const void* x, int64_t x_stride, const void* z, int64_t z_stride, const void* w,
 	void* y, int64_t y_stride, int64_t rows, int64_t d, int64_t group_size, float eps, void* stream);
 
+/* ---- RMSNorm over the last axis ----------------------------------------------------------------------------
+ * tensor_rms_norm(x, -1, w, eps, zero_centered) (srcs/ops/norm_ops.hpp:134-228; CUDA launcher cu_tensor_rms_norm_f32_v1,
+ * srcs/kernels/cuda/norm_rms_f32_v1.cu:94-119, f32 only there): y = x * rsqrt(mean_row(x^2) + eps) * (w + delta), delta = 1 when
+ * zero_centered != 0. x [rows, dim] (row stride x_stride), w [dim], y [rows, dim] (row stride y_stride). */
+int b200_rms_norm(int dtype, const void* x, int64_t x_stride, const void* w, void* y, int64_t y_stride, int64_t rows, int64_t dim,
+	float eps, int zero_centered, void* stream);
+
 /* ---- SSD chunked selective scan (prefill) -------------------------------------------------------------------
  * CUDA counterpart of mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:167-215), which anyGPU
  * has only as a PyTorch script. Argument meaning follows that function:
@@ -217,6 +224,21 @@ size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, i
  * ssm_state [b,H,P,N] fp32 are advanced in place. */
 int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
+	void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- Zamba2 Mamba decoder layer: the mixer with its input norm and residual -----------------------------------
+ * out = hidden + mixer(rms_norm(hidden, input_norm_weight, rms_eps)). No counterpart in anyGPU yet; the structure (input
+ * RMSNorm, block, residual stream) is that of its hybrid block's other half, tensor_zamba_attention_decoder
+ * (srcs/models/zamba2/zamba_attn_decoder.hpp:68-118). The residual is added in the epilogue of out_proj (f16) before the
+ * single rounding of the result; `out` may alias `hidden`. Arguments as for the mixer entry points; the workspace holds the
+ * normalised hidden states followed by the mixer's workspace. */
+size_t b200_mamba2_decoder_prefill_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen);
+int b200_mamba2_decoder_prefill(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* input_norm_weight, float rms_eps, const void* hidden, void* out, int64_t batch, int64_t seqlen,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out, void* workspace, size_t workspace_bytes, void* stream);
+size_t b200_mamba2_decoder_decode_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch);
+int b200_mamba2_decoder_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* input_norm_weight, float rms_eps, const void* hidden_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
 	void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- per-stage timing of b200_mamba2_mixer_prefill -----------------------------------------------------------

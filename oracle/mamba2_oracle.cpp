@@ -190,6 +190,23 @@ void orc_causal_conv1d_update_f32(const float* x_t, float* conv_state, const flo
 	});
 }
 
+// y = x / sqrt(mean_row(x^2) + eps) * (w + delta): tensor_rms_norm<CPU> over the last axis (srcs/ops/norm_ops.hpp:134-191),
+// delta = 1 for its zero_centered flag. Sequential fp32 sum of squares; the unqualified sqrt(float) at :188 is the double
+// overload on the host, so the quotient and the product with w are formed in double and rounded once.
+void orc_rms_norm_f32(const float* x, const float* w, float* y, int64_t rows, int64_t d, float eps, int zero_centered)
+{
+	const float delta = zero_centered ? 1.f : 0.f;
+	pfor(rows, [&](int64_t r)
+	{
+		float acc = 0.f;
+		for (int64_t i = 0; i < d; ++i) acc += x[r * d + i] * x[r * d + i];
+		const float ms = acc / static_cast<float>(d);
+		for (int64_t i = 0; i < d; ++i)
+			y[r * d + i] = static_cast<float>((static_cast<double>(x[r * d + i]) / std::sqrt(static_cast<double>(ms + eps)))
+				* static_cast<double>(w[i] + delta));
+	});
+}
+
 // y = rms_norm(x * silu(z)) * w over groups of `gsize` elements of the last axis.
 // Follows tensor_zamba_gated_rmsnorm (srcs/models/zamba2/zamba_gated_rmsnorm.hpp:9-23):
 // tensor_silu (srcs/ops/math_ops.hpp:16-35), tensor_mul (srcs/ops/binary_ops.hpp:103-121),

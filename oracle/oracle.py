@@ -109,6 +109,38 @@ def gated_rmsnorm(x, z, w, eps, gsize=None):
     return y
 
 
+def rms_norm(x, w, eps, zero_centered=False):
+    x, w = _c(x), _c(w)
+    d = x.shape[-1]
+    y = np.empty_like(x)
+    lib().orc_rms_norm_f32(_p(x), _p(w), _p(y), _i64(x.size // d), _i64(d), ctypes.c_float(eps), ctypes.c_int(int(zero_centered)))
+    return y
+
+
+def _r16(a):
+    return np.asarray(a, np.float32).astype(np.float16).astype(np.float32)
+
+
+def decoder_prefill(hidden, wts, input_norm_weight, rms_eps, cfg, f16io=False):
+    """The Mamba decoder layer around the mixer: hidden + mixer(rms_norm(hidden) * w_in). With f16io every operator's output
+    tensor is rounded to binary16 (norm output, mixer stages, and the sum)."""
+    normed = rms_norm(hidden, input_norm_weight, rms_eps)
+    if f16io:
+        normed = _r16(normed)
+    res = mixer_prefill(normed, wts, cfg, f16io=f16io)
+    out = np.asarray(hidden, np.float32) + res["out"]
+    res["out"] = _r16(out) if f16io else out
+    return res
+
+
+def decoder_decode(hidden_t, wts, input_norm_weight, rms_eps, cfg, conv_state, ssm_state, f16io=False):
+    normed = rms_norm(hidden_t, input_norm_weight, rms_eps)
+    if f16io:
+        normed = _r16(normed)
+    out = np.asarray(hidden_t, np.float32) + mixer_decode(normed, wts, cfg, conv_state, ssm_state, f16io=f16io)
+    return _r16(out) if f16io else out
+
+
 def ssd_chunk_scan(x, dt, A, B, C, chunk, D=None, dt_bias=None, initial_states=None, dt_softplus=True):
     """Argument order of mamba_chunk_scan_combined_ref. Returns (y [b,l,H,P], final_states [b,H,P,N])."""
     x, dt, A, B, C, D, dt_bias, initial_states = map(_c, (x, dt, A, B, C, D, dt_bias, initial_states))
@@ -210,4 +242,13 @@ def ref_gated_rmsnorm(x, z, w, eps, gsize=0):
     y = np.empty_like(x)
     r.ref_gated_rmsnorm_f32(_p(x), _p(z), _p(w), _p(y), ctypes.c_longlong(x.size // d), ctypes.c_longlong(d),
                             ctypes.c_int(gsize or d), ctypes.c_float(eps))
+    return y
+
+
+def ref_rms_norm(x, w, eps):
+    r = ref_lib()
+    x, w = _c(x), _c(w)
+    d = x.shape[-1]
+    y = np.empty_like(x)
+    r.ref_rms_norm_f32(_p(x), _p(w), _p(y), ctypes.c_longlong(x.size // d), ctypes.c_longlong(d), ctypes.c_float(eps))
     return y

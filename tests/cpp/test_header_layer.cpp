@@ -9,6 +9,8 @@
 #include "anygpu/fused/mamba_chunk_scan.hpp"
 #include "anygpu/models/zamba2/zamba_gated_rmsnorm.hpp"
 #include "anygpu/models/zamba2/zamba_mamba2_mixer.hpp"
+#include "anygpu/models/zamba2/zamba_mamba_decoder.hpp"
+#include "anygpu/ops/norm_ops.hpp"
 #include "anygpu/ops/mm_ops.hpp"
 
 extern "C" {
@@ -16,6 +18,7 @@ void orc_linear_f32_fast(const float*, const float*, float*, int64_t, int64_t, i
 void orc_causal_conv1d_f32(const float*, const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t);
 void orc_causal_conv1d_update_f32(const float*, float*, const float*, const float*, float*, int64_t, int64_t, int64_t);
 void orc_gated_rmsnorm_f32(const float*, const float*, const float*, float*, int64_t, int64_t, int64_t, float);
+void orc_rms_norm_f32(const float*, const float*, float*, int64_t, int64_t, float, int);
 void orc_ssd_chunk_scan_f32(const float*, const float*, const float*, const float*, const float*, const float*, const float*,
 	const float*, float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int);
 void orc_mamba2_mixer_prefill_f32(const float*, const float*, const float*, const float*, const float*, const float*, const float*,
@@ -143,6 +146,24 @@ static void test_chunk_scan_f16()
 	report("tensor_mamba_chunk_scan_combined f16 (final_states)", close_enough(r.final_states.copy_to_host(), efs, 2e-2f, 2e-3f));
 }
 
+static void test_rms_norm()
+{
+	const int64 rows = 6, d = 520;
+	auto hx = crt_random_normal_tensor<float32, CPU>({ 2, 3, d }, 30);
+	auto hw = crt_random_normal_tensor<float32, CPU>({ d }, 31);
+	auto y = tensor_rms_norm(hx.copy_to_cuda(), -1, hw.copy_to_cuda(), 1e-5f).copy_to_host();
+	std::vector<float> e(static_cast<size_t>(rows * d));
+	orc_rms_norm_f32(hx.buffer(), hw.buffer(), e.data(), rows, d, 1e-5f, 0);
+	report("tensor_rms_norm f32", close_enough(y, e, 0.f, 1e-3f));
+	auto hx16 = cvt_tensor_datatype<float16, float32>(hx);
+	auto hw16 = cvt_tensor_datatype<float16, float32>(hw);
+	auto y16 = tensor_rms_norm(hx16.copy_to_cuda(), -1, hw16.copy_to_cuda(), __float2half(1e-5f), true);
+	auto fx = host_f32(hx16);
+	auto fw = host_f32(hw16);
+	orc_rms_norm_f32(fx.data(), fw.data(), e.data(), rows, d, __half2float(__float2half(1e-5f)), 1);
+	report("tensor_rms_norm f16 zero-centered", close_enough(y16.copy_to_host(), e, 2e-2f, 2e-3f));
+}
+
 static void test_mixer_f32_and_dat_files(const std::string& tmp_dir)
 {
 	// configuration-0 sizes: batch 1, seqlen 64, d_model 256, d_inner 512, 8 heads x 64, d_state 16, chunk 32
@@ -195,6 +216,31 @@ static void test_mixer_f32_and_dat_files(const std::string& tmp_dir)
 		norm_w.buffer(), w_out.buffer(), ecs.data(), efs.data(), et.data(), b, cfg.d_model, cfg.d_inner, cfg.nheads, cfg.headdim, cfg.ngroups,
 		cfg.d_state, cfg.d_conv, cfg.d_inner, cfg.eps, 0);
 	report("tensor_zamba_mamba2_mixer f32 decode", close_enough(out_t, et, 0.f, 1e-3f));
+
+	// the decoder layer around the same mixer: y = h + mixer(rms_norm(h) * w_in), prefill then one decode step
+	auto in_norm = crt_random_normal_tensor<float32, CPU>({ cfg.d_model }, 26, 0.1f);
+	for (int64 i = 0; i < cfg.d_model; ++i) in_norm.buffer()[i] += 1.0f;
+	save_tensor(in_norm, p + "in_norm.dat");
+	ZambaMambaDecoderweights<float32> dw;
+	dw.load_weights(p + "in_norm.dat", p + "in_proj.dat", p + "conv_w.dat", p + "conv_b.dat", p + "dt_bias.dat", p + "A_log.dat", p + "D.dat",
+		p + "norm.dat", p + "out_proj.dat");
+	ZambaMambaCache<float32> dcache(cfg, b);
+	auto dout = tensor_zamba_mamba_decoder(dw, dcache, u.copy_to_cuda(), cfg, 1e-5f).copy_to_host();
+	std::vector<float> normed(static_cast<size_t>(b * l * cfg.d_model)), de(normed.size());
+	orc_rms_norm_f32(u.buffer(), in_norm.buffer(), normed.data(), b * l, cfg.d_model, 1e-5f, 0);
+	orc_mamba2_mixer_prefill_f32(normed.data(), w_in.buffer(), cw2.buffer(), conv_b.buffer(), dt_bias.buffer(), A_log.buffer(), D.buffer(),
+		norm_w.buffer(), w_out.buffer(), nullptr, de.data(), nullptr, nullptr, nullptr, nullptr, efs.data(), ecs.data(), b, l, cfg.d_model,
+		cfg.d_inner, cfg.nheads, cfg.headdim, cfg.ngroups, cfg.d_state, cfg.d_conv, cfg.chunk, cfg.d_inner, cfg.eps, 0);
+	for (size_t i = 0; i < de.size(); ++i) de[i] += u.buffer()[i];
+	report("tensor_zamba_mamba_decoder f32 prefill", close_enough(dout, de, 0.f, 1e-3f));
+	auto dout_t = tensor_zamba_mamba_decoder(dw, dcache, u_t.copy_to_cuda(), cfg, 1e-5f).copy_to_host();
+	std::vector<float> normed_t(static_cast<size_t>(b * cfg.d_model));
+	orc_rms_norm_f32(u_t.buffer(), in_norm.buffer(), normed_t.data(), b, cfg.d_model, 1e-5f, 0);
+	orc_mamba2_mixer_decode_f32(normed_t.data(), w_in.buffer(), cw2.buffer(), conv_b.buffer(), dt_bias.buffer(), A_log.buffer(), D.buffer(),
+		norm_w.buffer(), w_out.buffer(), ecs.data(), efs.data(), et.data(), b, cfg.d_model, cfg.d_inner, cfg.nheads, cfg.headdim, cfg.ngroups,
+		cfg.d_state, cfg.d_conv, cfg.d_inner, cfg.eps, 0);
+	for (size_t i = 0; i < et.size(); ++i) et[i] += u_t.buffer()[i];
+	report("tensor_zamba_mamba_decoder f32 decode", close_enough(dout_t, et, 0.f, 1e-3f));
 }
 
 int main(int argc, char** argv)
@@ -209,6 +255,7 @@ int main(int argc, char** argv)
 	test_causal_conv1d_f16();
 	test_linear_f16();
 	test_gated_rmsnorm_f32();
+	test_rms_norm();
 	test_chunk_scan_f16();
 	test_mixer_f32_and_dat_files(tmp_dir);
 	CUDA_CHECK(cudaDeviceSynchronize());

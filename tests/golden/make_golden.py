@@ -97,12 +97,45 @@ def linear_case(name, seed, M, K, N):
     print(name, "max|np-ref|", np.abs(x @ w - y_ref).max())
 
 
+def rms_norm_case(name, seed, rows, d, eps):
+    r = np.random.default_rng(seed)
+    x = r.standard_normal((rows, d), np.float32) * 1.5
+    w = r.standard_normal((d,), np.float32)
+    y_ref = orc.ref_rms_norm(x, w, eps)
+    xt = torch.from_numpy(x)
+    y_torch = (xt * torch.rsqrt(xt.pow(2).mean(-1, keepdim=True) + eps) * torch.from_numpy(w)).numpy()
+    np.savez(os.path.join(OUT, name + ".npz"), x=x, w=w, eps=np.float32(eps), y_ref=y_ref, y_torch=y_torch)
+    print(name, "max|torch-ref|", np.abs(y_torch - y_ref).max())
+
+
+def decoder_cfg0():
+    """The decoder layer around the cfg0 mixer, every stage run by reference code: hidden + mixer(rms_norm(hidden) * w_in)."""
+    cfg = synth.CONFIGS["cfg0"]
+    w = synth.make_weights(cfg, seed=0)
+    hidden = synth.make_input(cfg, seed=0)
+    w_in = (1.0 + 0.1 * np.random.default_rng(99).standard_normal(cfg["d_model"])).astype(np.float32)
+    normed = orc.ref_rms_norm(hidden, w_in, 1e-5)
+    m = ref_mixer(normed, w, cfg)
+    np.savez(os.path.join(OUT, "decoder_cfg0.npz"), input_norm_weight=w_in, rms_eps=np.float32(1e-5), normed=normed,
+             out=hidden + m["out"], final_states=m["final_states"])
+    print("decoder_cfg0 max|out|", np.abs(hidden + m["out"]).max())
+
+
 def mixer_cfg0():
     """One Mamba2 mixer layer at the configuration-0 sizes, every stage run by reference code."""
     cfg = synth.CONFIGS["cfg0"]
     w = synth.make_weights(cfg, seed=0)
     u = synth.make_input(cfg, seed=0)
-    b, l = cfg["batch"], cfg["seqlen"]
+    m = ref_mixer(u, w, cfg)
+    # inputs are regenerated from the seed by the tests; keep checksums so a generator drift is caught
+    chk = np.array([np.float64(np.abs(v).sum()) for v in [u] + [w[k] for k in sorted(w)]])
+    np.savez(os.path.join(OUT, "mixer_cfg0.npz"), input_checksums=chk, **m)
+    print("mixer_cfg0 out", m["out"].shape, "max|out|", np.abs(m["out"]).max(), "max|y|", np.abs(m["y"]).max())
+
+
+def ref_mixer(u, w, cfg):
+    """The mixer composed of the reference's own functions (compiled CPU operators + its Python SSD)."""
+    b, l = u.shape[0], u.shape[1]
     d_inner, H, P, G, N = cfg["d_inner"], cfg["nheads"], cfg["headdim"], cfg["ngroups"], cfg["d_state"]
     conv_dim, d_in_proj = synth.dims(cfg)
     zx = orc.ref_linear(u.reshape(b * l, -1), w["in_proj_weight"]).reshape(b, l, d_in_proj)
@@ -119,11 +152,7 @@ def mixer_cfg0():
     g = orc.ref_gated_rmsnorm(y.reshape(b * l, d_inner), np.ascontiguousarray(z).reshape(b * l, d_inner), w["norm_weight"],
                               cfg["eps"], gsize=d_inner)
     out = orc.ref_linear(g, w["out_proj_weight"]).reshape(b, l, -1)
-    # inputs are regenerated from the seed by the tests; keep checksums so a generator drift is caught
-    chk = np.array([np.float64(np.abs(v).sum()) for v in [u] + [w[k] for k in sorted(w)]])
-    np.savez(os.path.join(OUT, "mixer_cfg0.npz"), out=out, y=y.reshape(b, l, d_inner), final_states=fs, g=g.reshape(b, l, d_inner),
-             zxbcdt=zx, input_checksums=chk)
-    print("mixer_cfg0 out", out.shape, "max|out|", np.abs(out).max(), "max|y|", np.abs(y).max())
+    return dict(out=out, y=y.reshape(b, l, d_inner), final_states=fs, g=g.reshape(b, l, d_inner), zxbcdt=zx)
 
 
 if __name__ == "__main__":
@@ -138,3 +167,5 @@ if __name__ == "__main__":
     norm_case("gated_rmsnorm", 8, 6, 512, 1e-5)
     linear_case("linear", 9, 5, 33, 21)
     mixer_cfg0()
+    rms_norm_case("rms_norm", 9, 13, 520, 1e-5)
+    decoder_cfg0()

@@ -169,3 +169,42 @@ def test_head_sharded_tp_ranks_emulated_on_one_gpu(ops, tp):
     assert_close_f16(got, want, f"tp{tp} vs oracle", max_fail_fraction=2e-4)
     assert rel_l2(got, want) < 2e-3
     assert rel_l2(got, whole) < 2e-3
+
+
+def test_decoder_layer_cfg0_fp32_matches_reference_composition(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "decoder_cfg0.npz"))
+    cfg = synth.CONFIGS["cfg0"]
+    w, hidden = synth.make_weights(cfg, 0), synth.make_input(cfg, 0)
+    layer = ops.Mamba2DecoderLayer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float32),
+                                   torch.from_numpy(g["input_norm_weight"]).cuda(), float(g["rms_eps"]))
+    cache = ops.ZambaMambaCache.zeros(cfg, cfg["batch"], torch.float32)
+    out = layer.prefill(torch.from_numpy(hidden).cuda(), cache)
+    assert_abs(host(out), g["out"], "decoder layer out (every golden stage produced by reference code)", 1e-3)
+    assert_abs(host(cache.ssm_state), g["final_states"], "final ssm state", 1e-4)
+
+
+@pytest.mark.parametrize("layout", ["KN", "NK"])
+def test_decoder_layer_f16_prefill_then_decode(ops, layout):
+    cfg = dict(SMALL, batch=3, seqlen=256)
+    w = f16w(synth.make_weights(cfg, 8))
+    w_in = synth.to_f16_values(1.0 + 0.1 * np.random.default_rng(8).standard_normal(cfg["d_model"]).astype(np.float32))
+    h = synth.to_f16_values(synth.make_input(cfg, 8, batch=3, seqlen=256 + 4))
+    wt = ops.ZambaMamba2weights.from_numpy(w, torch.float16, layout=ops.W_KN if layout == "KN" else ops.W_NK)
+    layer = ops.Mamba2DecoderLayer(cfg, wt, torch.from_numpy(w_in).cuda().half(), 1e-5)
+    cache = ops.ZambaMambaCache.zeros(cfg, 3, torch.float16)
+    hd = torch.from_numpy(h).cuda().half()
+    want = orc.decoder_prefill(h[:, :256], w, w_in, 1e-5, cfg, f16io=True)
+    out = host(layer.prefill(hd[:, :256].contiguous(), cache))
+    assert_close_f16(out, want["out"], "decoder layer prefill", max_fail_fraction=1e-4)
+    assert rel_l2(out, want["out"]) < 2e-3
+    # in place: the residual stream is overwritten by the layer's output
+    buf = hd[:, :256].contiguous()
+    layer.prefill(buf, out=buf)
+    assert torch.equal(buf.float().cpu(), torch.from_numpy(out))
+    ocs, oss = want["conv_state"].copy(), want["final_state"].copy()
+    for t in range(4):
+        ht = np.ascontiguousarray(h[:, 256 + t])
+        got = host(layer.decode(hd[:, 256 + t].contiguous(), cache))
+        wd = orc.decoder_decode(ht, w, w_in, 1e-5, cfg, ocs, oss, f16io=True)
+        assert_close_f16(got, wd, f"decoder layer decode step {t}", max_fail_fraction=2e-3)
+        assert rel_l2(got, wd) < 3e-3

@@ -291,3 +291,27 @@ def test_selective_state_update_steps(ops, dims, dtype):
     else:
         assert_abs(got, wy, "decode y", 1e-4)
     assert_abs(host(st), wst, "decode state", 1e-4)
+
+
+@pytest.mark.parametrize("shape", [(13, 520), (3, 7, 2560), (5, 36), (2, 8200), (4, 8192)])
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_rms_norm(ops, shape, dtype):
+    r = np.random.default_rng(21)
+    x = (r.standard_normal(shape) * 1.5).astype(np.float32)
+    w = (1.0 + 0.2 * r.standard_normal(shape[-1])).astype(np.float32)
+    td = torch.float16 if dtype == "f16" else torch.float32
+    if dtype == "f16":
+        x, w = f16v(x), f16v(w)
+    for zc in (False, True):
+        got = ops.tensor_rms_norm(torch.from_numpy(x).cuda().to(td), torch.from_numpy(w).cuda().to(td), 1e-5, zero_centered=zc)
+        want = orc.rms_norm(x, w, 1e-5, zero_centered=zc)
+        if dtype == "f16":
+            assert_close_f16(got.float().cpu().numpy(), want, f"rms_norm f16 zero_centered={zc}")
+        else:
+            assert_abs(got.cpu().numpy(), want, f"rms_norm f32 zero_centered={zc}", 1e-4)
+
+
+def test_rms_norm_golden_from_reference(ops, golden_dir):
+    g = np.load(os.path.join(golden_dir, "rms_norm.npz"))
+    got = ops.tensor_rms_norm(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["w"]).cuda(), float(g["eps"]))
+    assert_abs(got.cpu().numpy(), g["y_ref"], "rms_norm vs the reference CPU operator", 1e-4)

@@ -122,6 +122,25 @@ def test_mixer_decode_continues_prefill():
     assert_abs(ss, full["final_state"], "ssm_state", 2e-5)
 
 
+def test_rms_norm_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "rms_norm.npz"))
+    y = orc.rms_norm(g["x"], g["w"], float(g["eps"]))
+    assert np.array_equal(y, g["y_ref"])          # the reference's compiled tensor_rms_norm<float32, CPU>: bit-exact
+    assert_abs(y, g["y_torch"], "rms_norm vs torch", 1e-5)
+    yz = orc.rms_norm(g["x"], g["w"], float(g["eps"]), zero_centered=True)
+    assert_abs(yz, orc.rms_norm(g["x"], g["w"] + 1.0, float(g["eps"])), "zero-centered weight", 1e-5)
+
+
+def test_decoder_layer_golden(golden_dir):
+    g = np.load(os.path.join(golden_dir, "decoder_cfg0.npz"))
+    cfg = synth.CONFIGS["cfg0"]
+    w, hidden = synth.make_weights(cfg, 0), synth.make_input(cfg, 0)
+    got = orc.decoder_prefill(hidden, w, g["input_norm_weight"], float(g["rms_eps"]), cfg)
+    assert np.array_equal(orc.rms_norm(hidden, g["input_norm_weight"], float(g["rms_eps"])), g["normed"])
+    assert_abs(got["out"], g["out"], "decoder layer out", 1e-3)
+    assert_abs(got["final_state"], g["final_states"], "decoder layer final state", 1e-4)
+
+
 def test_reference_build_agrees_when_present():
     if orc.ref_lib() is None:
         pytest.skip("reference CPU operators not built in this checkout (oracle/_ref)")
@@ -135,6 +154,7 @@ def test_reference_build_agrees_when_present():
     assert np.array_equal(orc.gated_rmsnorm(a, z, nw, 1e-5), orc.ref_gated_rmsnorm(a, z, nw, 1e-5))
     m, k = r.standard_normal((6, 50), np.float32), r.standard_normal((50, 9), np.float32)
     assert np.array_equal(orc.linear(m, k), orc.ref_linear(m, k))
+    assert np.array_equal(orc.rms_norm(a, nw, 1e-5), orc.ref_rms_norm(a, nw, 1e-5))
 
 
 def test_threads_do_not_change_results():
