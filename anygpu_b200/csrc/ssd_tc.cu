@@ -208,7 +208,6 @@ __global__ void __launch_bounds__(cstate::THREADS) ssd_chunk_state_tc_kernel(con
 namespace cscan {
 constexpr int LB = 128;   // output rows (l) per CTA
 constexpr int KB = 64;    // s per K-block
-constexpr int NX = 4;     // X ring stages
 constexpr int NCW = 16;        // compute warps: 4 TMEM lane quadrants x 2 K-block parities x 2 column halves
 constexpr int THREADS = 64 + NCW * 32;  // warp 0 TMA, warp 1 MMA, warps 2-17 compute
 constexpr int S_STAGE = LB * KB * 2;  // 16 KiB
@@ -218,6 +217,13 @@ constexpr uint32_t TMEM_COLS = 512;   // CB [0,256) | Y0 Z0 [256,384) | Y1 Z1 [3
 
 constexpr int Y_STAGE = 32 * 32;      // per-warp output staging: 32 rows x 16 f16 (32 B rows, dense)
 
+// One ring of NST K-block stages, each holding the decayed-score tile S (written by the compute warps) and the X tile of the
+// same K-block (TMA). One "full" barrier (8 compute-warp arrivals + the producer's expect_tx) and one "empty" barrier (one
+// tcgen05.commit) per stage keep the MMA-issuing thread short: it is a single thread whose scalar instructions compete with
+// the compute warps of its scheduler, and its wait/issue/commit sequence per K-block was the kernel's critical path.
+// The S tiles of the ring start in the B region, which is dead once CB = C.B^T has been computed (the compute warps write
+// their first S tile only after that) and run on into the S region: NST = NS + B_BYTES / S_STAGE stages, more than the
+// K-blocks of one head, so the scores of head i+1 are produced while the tensor core still consumes those of head i.
 template <int NSTATE, int NS, int NYB>
 struct Layout
 {
@@ -228,11 +234,16 @@ struct Layout
 	static constexpr int OFF_C = 0;
 	static constexpr int OFF_B = OFF_C + C_BYTES;
 	static constexpr int OFF_S = OFF_B + B_BYTES;
+	static constexpr int NST = NS + B_BYTES / S_STAGE;
 	static constexpr int OFF_X = OFF_S + NS * S_STAGE;
-	static constexpr int OFF_P = OFF_X + NX * X_STAGE;
+	static constexpr int OFF_P = OFF_X + NST * X_STAGE;
 	static constexpr int OFF_H = OFF_P + 2 * P_BYTES;
 	static constexpr int OFF_Y = OFF_H + 2 * H_FLOATS * 4;   // [NCW compute warps][NYB buffers][Y_STAGE]
 	static constexpr int TOTAL = OFF_Y + NCW * NYB * Y_STAGE + 1024;
+	static_assert(TOTAL <= 232448, "shared memory layout exceeds the per-CTA limit");
+	// byte offsets of stage `st`: S tiles are contiguous from the start of the B region
+	static __host__ __device__ constexpr int s_off(int st) { return OFF_B + st * S_STAGE; }
+	static __host__ __device__ constexpr int x_off(int st) { return OFF_X + st * X_STAGE; }
 };
 }  // namespace cscan
 
@@ -246,8 +257,9 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 	using namespace cscan;
 	using L = Layout<NSTATE, NS, NYB>;
 	constexpr int KA = L::KA;
+	constexpr int NST = L::NST;
 	extern __shared__ uint8_t smem_raw[];
-	__shared__ uint64_t bar_in, bar_cb, s_full[NS], s_empty[NS], x_full[NX], x_empty[NX], p_full[2], p_empty[2], acc_full[2],
+	__shared__ uint64_t bar_in, bar_cb, k_full[NST], k_empty[NST], p_full[2], p_empty[2], acc_full[2],
 		acc_empty[2], h_full[2], h_empty[2];
 	__shared__ uint32_t tmem_slot;
 	__shared__ int abort_flag;
@@ -279,8 +291,7 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 		abort_flag = 0;
 		mbar_init(smem_u32(&bar_in), 1);
 		mbar_init(smem_u32(&bar_cb), 1);
-		for (int i = 0; i < NS; ++i) { mbar_init(smem_u32(&s_full[i]), 8); mbar_init(smem_u32(&s_empty[i]), 1); }
-		for (int i = 0; i < NX; ++i) { mbar_init(smem_u32(&x_full[i]), 1); mbar_init(smem_u32(&x_empty[i]), 1); }
+		for (int i = 0; i < NST; ++i) { mbar_init(smem_u32(&k_full[i]), 9); mbar_init(smem_u32(&k_empty[i]), 1); }
 		for (int i = 0; i < 2; ++i)
 		{
 			mbar_init(smem_u32(&p_full[i]), 1);
@@ -321,7 +332,8 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 					tma_load_3d(base + L::OFF_B + a * (256 * 128) + j * 8192, &tmB, in, g * NSTATE + a * 64, c * Q + j * 64,
 						static_cast<int>(b));
 			}
-			int kbc = 0;
+			int kst = 0;
+			uint32_t kphase = 0;
 			for (int i = 0; i < nheads; ++i)
 			{
 				const int h = h_begin + i;
@@ -341,16 +353,16 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 					bulk_load_1d(hb + 1024, dt + cbase, bytes, smem_u32(&h_full[buf]));
 					bulk_load_1d(hb + 2048, colf + cbase, bytes, smem_u32(&h_full[buf]));
 				}
-				for (int kb = 0; kb < nkb; ++kb, ++kbc)
+				for (int kb = 0; kb < nkb; ++kb)
 				{
-					const int st = kbc % NX;
-					if (!mbar_wait(smem_u32(&x_empty[st]), ((kbc / NX) & 1) ^ 1u, abortp))
+					if (!mbar_wait(smem_u32(&k_empty[kst]), kphase ^ 1u, abortp))
 					{
 						report_timeout(err_word, kErrProducerWait);
 						goto role_done;
 					}
-					mbar_arrive_expect_tx(smem_u32(&x_full[st]), X_STAGE);
-					tma_load_3d(base + L::OFF_X + st * X_STAGE, &tmX, smem_u32(&x_full[st]), h * 64, c * Q + kb * KB, static_cast<int>(b));
+					mbar_arrive_expect_tx(smem_u32(&k_full[kst]), X_STAGE);
+					tma_load_3d(base + L::x_off(kst), &tmX, smem_u32(&k_full[kst]), h * 64, c * Q + kb * KB, static_cast<int>(b));
+					if (++kst == NST) { kst = 0; kphase ^= 1u; }
 				}
 				if (!mbar_wait(smem_u32(&p_empty[buf]), ((i >> 1) & 1) ^ 1u, abortp))
 				{
@@ -392,7 +404,10 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 			}
 			constexpr uint32_t idesc_y = make_idesc_f16(LB, 64, 1);  // B operand (x) is MN-major
 			constexpr uint32_t idesc_z = make_idesc_f16(LB, 64, 0);
-			int kbc = 0;
+			int kst = 0;
+			uint32_t kphase = 0;
+			const uint64_t s_desc0 = make_smem_desc_sw128(base + L::s_off(0), 16, 1024);
+			const uint64_t x_desc0 = make_smem_desc_sw128(base + L::x_off(0), KB * 128, 1024);
 			for (int i = 0; i < nheads; ++i)
 			{
 				const int buf = i & 1;
@@ -404,24 +419,23 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 				tc_fence_after();
 				const uint32_t y_tmem = tmem_base + 256u + static_cast<uint32_t>(buf * 128);
 				const uint32_t z_tmem = y_tmem + 64u;
-				for (int kb = 0; kb < nkb; ++kb, ++kbc)
+				for (int kb = 0; kb < nkb; ++kb)
 				{
-					const int ss = kbc % NS, xsn = kbc % NX;
-					if (!mbar_wait(smem_u32(&s_full[ss]), (kbc / NS) & 1, abortp) ||
-						!mbar_wait(smem_u32(&x_full[xsn]), (kbc / NX) & 1, abortp))
+					if (!mbar_wait(smem_u32(&k_full[kst]), kphase, abortp))
 					{
 						report_timeout(err_word, kErrMmaWaitFull);
 						goto role_done;
 					}
 					tc_fence_after();
-					const uint64_t a_desc = make_smem_desc_sw128(base + L::OFF_S + ss * S_STAGE, 16, 1024);
-					const uint64_t b_desc = make_smem_desc_sw128(base + L::OFF_X + xsn * X_STAGE, KB * 128, 1024);
+					// descriptors address shared memory in 16-byte units: stage st is st * (stage bytes / 16) further on
+					const uint64_t a_desc = s_desc0 + static_cast<uint64_t>(kst * (S_STAGE >> 4));
+					const uint64_t b_desc = x_desc0 + static_cast<uint64_t>(kst * (X_STAGE >> 4));
 #pragma unroll
 					for (int k = 0; k < KB / 16; ++k)
 						mma_f16_ss(y_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
 							(kb | k) != 0 ? 1u : 0u);
-					mma_commit(smem_u32(&s_empty[ss]));
-					mma_commit(smem_u32(&x_empty[xsn]));
+					mma_commit(smem_u32(&k_empty[kst]));
+					if (++kst == NST) { kst = 0; kphase ^= 1u; }
 				}
 				if (!mbar_wait(smem_u32(&p_full[buf]), (i >> 1) & 1, abortp))
 				{
@@ -513,9 +527,10 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 			const float dl2 = hd[l] * kLog2e;
 			for (int kb = kpar; kb < nkb; kb += 2)
 			{
+				// stage and phase of K-block (i, kb) in the ring: this warp visits every second K-block
 				const int kbc = i * nkb + kb;
-				const int ss = kbc % NS;
-				if (!mbar_wait(smem_u32(&s_empty[ss]), ((kbc / NS) & 1) ^ 1u, abortp))
+				const int ss = kbc % NST;
+				if (!mbar_wait(smem_u32(&k_empty[ss]), ((kbc / NST) & 1) ^ 1u, abortp))
 				{
 					if (lane == 0) report_timeout(err_word, kErrScanWait);
 					goto role_done;
@@ -530,7 +545,7 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 					cb_ready = true;
 				}
 				tc_fence_after();
-				uint8_t* srow = gen + L::OFF_S + ss * S_STAGE + r * 128;
+				uint8_t* srow = gen + L::s_off(ss) + r * 128;
 				const int s_first = kb * KB;          // first column of the 64-wide K-block
 				const int s0 = s_first + chalf * 32;  // first of this warp's 32 columns
 				if (s0 > wrow0 + 31)
@@ -601,7 +616,7 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 				}
 				fence_proxy_async_smem();
 				__syncwarp();
-				if (lane == 0) mbar_arrive(smem_u32(&s_full[ss]));
+				if (lane == 0) mbar_arrive(smem_u32(&k_full[ss]));
 			}
 			// this warp no longer reads the per-head rows
 			__syncwarp();
@@ -707,18 +722,18 @@ int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs,
 	const dim3 grid(static_cast<unsigned>(base_ctas), static_cast<unsigned>(cdiv(hpg, hpc)));
 	if (d.N == 64)
 	{
-		using Lt = cscan::Layout<64, 4, 2>;
+		using Lt = cscan::Layout<64, 4, 1>;
 		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<64, 4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
-		ssd_chunk_scan_tc_kernel<64, 4, 2><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<64, 4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		ssd_chunk_scan_tc_kernel<64, 4, 1><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
 			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
 	}
 	else
 	{
-		using Lt = cscan::Layout<128, 2, 1>;
+		using Lt = cscan::Layout<128, 1, 1>;
 		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<128, 2, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
-		ssd_chunk_scan_tc_kernel<128, 2, 1><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
+		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<128, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		ssd_chunk_scan_tc_kernel<128, 1, 1><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
 			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
 	}
 	B200_LAUNCH_CHECK();
