@@ -209,7 +209,8 @@ namespace cscan {
 constexpr int LB = 128;   // output rows (l) per CTA
 constexpr int KB = 64;    // s per K-block
 constexpr int NCW = 16;        // compute warps: 4 TMEM lane quadrants x 2 K-block parities x 2 column halves
-constexpr int THREADS = 64 + NCW * 32;  // warp 0 TMA, warp 1 MMA, warps 2-17 compute
+constexpr int MMA_B_WARP = 2 + NCW;      // second MMA-issuing warp (odd heads)
+constexpr int THREADS = 96 + NCW * 32;  // warp 0 TMA, warp 1 MMA (CB, even heads), warps 2-17 compute, warp 18 MMA (odd heads)
 constexpr int S_STAGE = LB * KB * 2;  // 16 KiB
 constexpr int X_STAGE = KB * 64 * 2;  // 8 KiB
 constexpr int H_FLOATS = 3 * 256;     // per-head dAcs | dt | colf rows of the chunk (Q <= 256)
@@ -402,63 +403,81 @@ __global__ void __launch_bounds__(cscan::THREADS, 1) ssd_chunk_scan_tc_kernel(co
 				}
 				mma_commit(smem_u32(&bar_cb));
 			}
-			constexpr uint32_t idesc_y = make_idesc_f16(LB, 64, 1);  // B operand (x) is MN-major
-			constexpr uint32_t idesc_z = make_idesc_f16(LB, 64, 0);
-			int kst = 0;
-			uint32_t kphase = 0;
-			const uint64_t s_desc0 = make_smem_desc_sw128(base + L::s_off(0), 16, 1024);
-			const uint64_t x_desc0 = make_smem_desc_sw128(base + L::x_off(0), KB * 128, 1024);
-			for (int i = 0; i < nheads; ++i)
+		}
+		// falls through to the head loop below as the issuer of the even heads
+	}
+	if ((warp == 1 || warp == MMA_B_WARP) && lane == 0 && !*abortp)
+	{
+		// Two MMA-issuing threads, even heads (accumulator 0) and odd heads (accumulator 1): a head's wait / descriptor /
+		// tcgen05.mma / commit sequence is a few hundred dependent scalar instructions of ONE thread that shares its scheduler
+		// with compute warps, about as long as the compute warps need for a head's scores. The two threads' MMAs touch
+		// different accumulators and different ring stages, so they need no ordering between each other.
+		const int par = warp == 1 ? 0 : 1;
+		constexpr uint32_t idesc_y = make_idesc_f16(LB, 64, 1);  // B operand (x) is MN-major
+		constexpr uint32_t idesc_z = make_idesc_f16(LB, 64, 0);
+		const uint64_t s_desc0 = make_smem_desc_sw128(base + L::s_off(0), 16, 1024);
+		const uint64_t x_desc0 = make_smem_desc_sw128(base + L::x_off(0), KB * 128, 1024);
+		const uint32_t y_tmem = tmem_base + 256u + static_cast<uint32_t>(par * 128);
+		const uint32_t z_tmem = y_tmem + 64u;
+		bool ok = par == 0 || mbar_wait(smem_u32(&bar_in), 0, abortp);  // C tile resident (the even issuer waited already)
+		if (!ok) report_timeout(err_word, kErrMmaWaitFull);
+		tc_fence_after();
+		// ring position of K-block 0 of head `par`
+		int kst = (par * nkb) % NST;
+		uint32_t kphase = static_cast<uint32_t>((par * nkb) / NST) & 1u;
+		for (int i = par; ok && i < nheads; i += 2)
+		{
+			const uint32_t use = static_cast<uint32_t>(i >> 1) & 1u;  // parity of this accumulator's use count
+			if (!mbar_wait(smem_u32(&acc_empty[par]), use ^ 1u, abortp))
 			{
-				const int buf = i & 1;
-				if (!mbar_wait(smem_u32(&acc_empty[buf]), ((i >> 1) & 1) ^ 1u, abortp))
-				{
-					report_timeout(err_word, kErrMmaWaitTmem);
-					goto role_done;
-				}
-				tc_fence_after();
-				const uint32_t y_tmem = tmem_base + 256u + static_cast<uint32_t>(buf * 128);
-				const uint32_t z_tmem = y_tmem + 64u;
-				for (int kb = 0; kb < nkb; ++kb)
-				{
-					if (!mbar_wait(smem_u32(&k_full[kst]), kphase, abortp))
-					{
-						report_timeout(err_word, kErrMmaWaitFull);
-						goto role_done;
-					}
-					tc_fence_after();
-					// descriptors address shared memory in 16-byte units: stage st is st * (stage bytes / 16) further on
-					const uint64_t a_desc = s_desc0 + static_cast<uint64_t>(kst * (S_STAGE >> 4));
-					const uint64_t b_desc = x_desc0 + static_cast<uint64_t>(kst * (X_STAGE >> 4));
-#pragma unroll
-					for (int k = 0; k < KB / 16; ++k)
-						mma_f16_ss(y_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
-							(kb | k) != 0 ? 1u : 0u);
-					mma_commit(smem_u32(&k_empty[kst]));
-					if (++kst == NST) { kst = 0; kphase ^= 1u; }
-				}
-				if (!mbar_wait(smem_u32(&p_full[buf]), (i >> 1) & 1, abortp))
+				report_timeout(err_word, kErrMmaWaitTmem);
+				break;
+			}
+			tc_fence_after();
+			for (int kb = 0; kb < nkb; ++kb)
+			{
+				if (!mbar_wait(smem_u32(&k_full[kst]), kphase, abortp))
 				{
 					report_timeout(err_word, kErrMmaWaitFull);
-					goto role_done;
+					ok = false;
+					break;
 				}
 				tc_fence_after();
+				// descriptors address shared memory in 16-byte units: stage st is st * (stage bytes / 16) further on
+				const uint64_t a_desc = s_desc0 + static_cast<uint64_t>(kst * (S_STAGE >> 4));
+				const uint64_t b_desc = x_desc0 + static_cast<uint64_t>(kst * (X_STAGE >> 4));
 #pragma unroll
-				for (int a = 0; a < KA; ++a)
-				{
-					const uint64_t a_desc = make_smem_desc_sw128(base + L::OFF_C + a * (LB * 128), 16, 1024);
-					const uint64_t b_desc = make_smem_desc_sw128(base + L::OFF_P + buf * L::P_BYTES + a * 8192, 16, 1024);
-#pragma unroll
-					for (int k = 0; k < 4; ++k)
-						mma_f16_ss(z_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_z,
-							(a | k) != 0 ? 1u : 0u);
-				}
-				mma_commit(smem_u32(&p_empty[buf]));
-				mma_commit(smem_u32(&acc_full[buf]));
+				for (int k = 0; k < KB / 16; ++k)
+					mma_f16_ss(y_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
+						(kb | k) != 0 ? 1u : 0u);
+				mma_commit(smem_u32(&k_empty[kst]));
+				if (++kst == NST) { kst = 0; kphase ^= 1u; }
 			}
+			if (!ok) break;
+			if (!mbar_wait(smem_u32(&p_full[par]), use, abortp))
+			{
+				report_timeout(err_word, kErrMmaWaitFull);
+				break;
+			}
+			tc_fence_after();
+#pragma unroll
+			for (int a = 0; a < KA; ++a)
+			{
+				const uint64_t a_desc = make_smem_desc_sw128(base + L::OFF_C + a * (LB * 128), 16, 1024);
+				const uint64_t b_desc = make_smem_desc_sw128(base + L::OFF_P + par * L::P_BYTES + a * 8192, 16, 1024);
+#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					mma_f16_ss(z_tmem, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_z,
+						(a | k) != 0 ? 1u : 0u);
+			}
+			mma_commit(smem_u32(&p_empty[par]));
+			mma_commit(smem_u32(&acc_full[par]));
+			// skip the other issuer's head
+			kst += nkb;
+			if (kst >= NST) { kst -= NST; kphase ^= 1u; }
 		}
 	}
-	else
+	else if (warp >= 2 && warp < 2 + NCW)
 	{
 		const int q = warp & 3;           // TMEM lane quadrant
 		const int cw = warp - 2;          // compute warp index 0..15
