@@ -267,6 +267,22 @@ class Mamba2Mixer:
             self.decode(u_t, cache, out=out)
         return graph
 
+    def capture_decode_steps(self, u_steps, cache, out_steps):
+        """Records u_steps.shape[0] consecutive decode steps (inputs u_steps[t], outputs out_steps[t], both (steps, b, d_model))
+        into ONE CUDA graph: for a run of steps whose inputs are known up front (a benchmark, speculative or teacher-forced
+        decoding) the steps then follow each other without a host launch in between, and the first projection of step t+1
+        starts (programmatic dependent launch) while the last kernel of step t drains. The cache is left as it was."""
+        keep = (cache.conv_state.clone(), cache.ssm_state.clone())
+        self.decode(u_steps[0], cache, out=out_steps[0])
+        cache.conv_state.copy_(keep[0])
+        cache.ssm_state.copy_(keep[1])
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for t in range(u_steps.shape[0]):
+                self.decode(u_steps[t], cache, out=out_steps[t])
+        return graph
+
 
 class Mamba2DecoderLayer:
     """The Zamba2 Mamba decoder layer around the mixer: out = hidden + mixer(rms_norm(hidden) * input_norm_weight).

@@ -478,7 +478,13 @@ def run_kernel(args):
         cache = ops.ZambaMambaCache(torch.from_numpy(cs).cuda().half(), torch.from_numpy(ss).cuda())
         u = rn(c3["batch"], c3["d_model"])
         o = torch.empty_like(u)
-        if args.graph:
+        per_call = 1
+        if args.graph and args.graph_steps > 1:
+            per_call = args.graph_steps
+            us_, os_ = rn(per_call, c3["batch"], c3["d_model"]), torch.empty(per_call, c3["batch"], c3["d_model"], device="cuda", dtype=h)
+            graph = mixer.capture_decode_steps(us_, cache, os_)
+            fn = lambda i: graph.replay()
+        elif args.graph:
             graph = mixer.capture_decode(u, cache, o)
             fn = lambda i: graph.replay()
         else:
@@ -496,10 +502,11 @@ def run_kernel(args):
         fn(i)
         e1.record()
     torch.cuda.synchronize()
-    ms = sorted(e0.elapsed_time(e1) for e0, e1 in evs)
+    per_call = locals().get("per_call", 1)
+    ms = sorted(e0.elapsed_time(e1) / per_call for e0, e1 in evs)
     med, mn = ms[len(ms) // 2], ms[0]
     capi.check("b200_last_device_error", capi.load().b200_last_device_error(None, None))
-    out = {"kernel": k, "small": bool(args.small), "graph": bool(args.graph), "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
+    out = {"kernel": k, "small": bool(args.small), "graph": bool(args.graph), "graph_steps": args.graph_steps if args.graph else 0, "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
     if bytes_alg:
         out.update(algorithmic_bytes=bytes_alg, gbs_median=bytes_alg / (med * 1e-3) / 1e9, hbm_peak_gbs=peaks["hbm_gbs"],
                    frac_of_hbm_peak=bytes_alg / (med * 1e-3) / 1e9 / peaks["hbm_gbs"], peak_source=peaks["source"])
@@ -523,6 +530,7 @@ def main():
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
     ap.add_argument("--layout", default="KN", choices=["KN", "NK"], help="with --kernel decode: projection weight layout")
+    ap.add_argument("--graph-steps", type=int, default=1, help="with --kernel decode --graph: consecutive steps recorded into one graph")
     ap.add_argument("--graph", action="store_true", help="with --kernel decode: replay the step from a CUDA graph")
     args = ap.parse_args()
     if args.kernel:

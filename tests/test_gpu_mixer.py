@@ -130,6 +130,26 @@ def test_decode_replayed_from_a_cuda_graph_equals_eager_decode(ops):
     assert torch.equal(graph_cache.conv_state, eager_cache.conv_state)
 
 
+def test_several_decode_steps_in_one_cuda_graph_equal_eager_steps(ops):
+    cfg = dict(SMALL, batch=3)
+    w = f16w(synth.make_weights(cfg, 9))
+    cs, ss = synth.make_decode_state(cfg, 9)
+    us = torch.from_numpy(synth.make_input(cfg, 9, batch=3, seqlen=6)).cuda().half().transpose(0, 1).contiguous()  # (steps, b, d)
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16))
+    mk = lambda: ops.ZambaMambaCache(torch.from_numpy(cs).cuda().half(), torch.from_numpy(ss).cuda())
+    eager_cache, graph_cache = mk(), mk()
+    outs = torch.empty_like(us)
+    graph = mixer.capture_decode_steps(us, graph_cache, outs)
+    assert torch.equal(graph_cache.ssm_state, eager_cache.ssm_state)  # capturing does not advance the cache
+    graph.replay()
+    torch.cuda.synchronize()
+    for t in range(us.shape[0]):
+        want = mixer.decode(us[t], eager_cache)
+        assert torch.equal(outs[t], want), t
+    assert torch.equal(graph_cache.ssm_state, eager_cache.ssm_state)
+    assert torch.equal(graph_cache.conv_state, eager_cache.conv_state)
+
+
 def test_prefill_then_decode_continues_the_sequence(ops):
     cfg = dict(SMALL, batch=2, chunk=64)
     w = f16w(synth.make_weights(cfg, 4))
