@@ -144,7 +144,7 @@ extern "C" size_t b200_mamba2_mixer_prefill_workspace_bytes(const b200_mamba2_co
 static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u, void* out, int64_t batch, int64_t seqlen,
 	const float* initial_states, void* conv_state_out, float* ssm_state_out,
-	void* workspace, size_t workspace_bytes, void* stream, const void* residual, int64_t ldr)
+	void* workspace, size_t workspace_bytes, void* stream, const void* residual, int64_t ldr, const void* conv_state_in = nullptr)
 {
 	if (!cfg || !w || !u || !out) return B200_ERR_NULL;
 	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
@@ -168,12 +168,12 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 	if (rc) return rc;
 	stage_mark(1, st);
 	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
-		nullptr, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+		conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
 	if (rc) return rc;
 	stage_mark(2, st);
 	rc = b200_mamba_chunk_scan_combined(dtype, ws.xbc, m.conv_dim, ws.zxbcdt + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
 		ws.xbc + d_inner * e, m.conv_dim, ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, ws.y, d_inner,
-		ssm_state_out, batch, seqlen, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, 1, ws.ssd, ws.ssd_bytes,
+		ssm_state_out, batch, seqlen, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes,
 		stream);
 	if (rc) return rc;
 	stage_mark(3, st);
@@ -396,7 +396,7 @@ extern "C" int b200_mamba2_mixer_prefill_tp_partial(int dtype, const b200_mamba2
 	if (rc) return rc;
 	rc = b200_mamba_chunk_scan_combined(dtype, ws.xbc, m.conv_dim, ws.zxbcdt + (d_inner + m.conv_dim) * e, ws.ldz, w->A_log, 1,
 		ws.xbc + d_inner * e, m.conv_dim, ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, nullptr, ws.y, d_inner,
-		ssm_state_out, batch, seqlen, cfg_local->nheads, cfg_local->headdim, cfg_local->ngroups, cfg_local->d_state, cfg_local->chunk, 1,
+		ssm_state_out, batch, seqlen, cfg_local->nheads, cfg_local->headdim, cfg_local->ngroups, cfg_local->d_state, cfg_local->chunk, B200_DT_SOFTPLUS_EXACT,
 		ws.ssd, ws.ssd_bytes, stream);
 	if (rc) return rc;
 	rc = gated_mul_sumsq(dtype, ws.y, d_inner, ws.zxbcdt, ws.ldz, w->norm_weight, ws.y, d_inner, sumsq, T, d_inner,
@@ -528,6 +528,38 @@ extern "C" int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg
 	void* workspace, size_t workspace_bytes, void* stream)
 {
 	return mixer_decode_impl(dtype, cfg, w, u_t, out_t, conv_state, ssm_state, batch, workspace, workspace_bytes, stream, nullptr, 0);
+}
+
+// ---- prefill continuation: `seqlen` more tokens of sequences whose state so far is in the cache ---------------------------
+// Workspace: the next conv_state [b, conv_dim, d_conv-1] (written by the thread blocks that see the last tokens while others
+// still read the old one, so it cannot be produced in place), then the prefill workspace.
+extern "C" size_t b200_mamba2_mixer_prefill_continue_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch,
+	int64_t seqlen)
+{
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0 || seqlen <= 0) return 0;
+	return align_up(static_cast<size_t>(batch) * m.conv_dim * (cfg->d_conv - 1) * m.esz, 256) + carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
+}
+
+extern "C" int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, int64_t batch, int64_t seqlen, void* conv_state, float* ssm_state,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !u || !out || !conv_state || !ssm_state) return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch < 0 || seqlen < 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0 || seqlen == 0) return B200_OK;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const size_t cs_bytes = static_cast<size_t>(batch) * m.conv_dim * (cfg->d_conv - 1) * m.esz;
+	const size_t cs_pad = align_up(cs_bytes, 256);
+	if (workspace_bytes < cs_pad + carve_prefill(nullptr, cfg, m, batch, seqlen).bytes) return B200_ERR_WORKSPACE;
+	char* next_cs = static_cast<char*>(workspace);
+	const int rc = mixer_prefill_impl(dtype, cfg, w, u, out, batch, seqlen, ssm_state, next_cs, ssm_state, next_cs + cs_pad,
+		workspace_bytes - cs_pad, stream, nullptr, 0, conv_state);
+	if (rc) return rc;
+	if (cs_bytes) B200_CUDA_TRY(cudaMemcpyAsync(conv_state, next_cs, cs_bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+	return B200_OK;
 }
 
 // ---- Zamba2 Mamba decoder layer around the mixer: out = hidden + mixer(rms_norm(hidden) * input_norm_weight) -------------

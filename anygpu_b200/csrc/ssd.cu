@@ -6,9 +6,9 @@ namespace b200 {
 template <typename T>
 static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
 	const void* Cm, int64_t cs, const float* D, const float* dt_bias, const float* init, void* y, int64_t ys, float* fin,
-	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st, int dt_softplus)
 {
-	int rc = ssd_dt_cumsum<T>(static_cast<const T*>(dt), dts, A, a_is_log, dt_bias, 1, d, w, st);
+	int rc = ssd_dt_cumsum<T>(static_cast<const T*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
 	if (rc) return rc;
 	rc = ssd_chunk_state_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, d, w, st);
 	if (rc) return rc;
@@ -21,12 +21,12 @@ static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, cons
 // f16 activations on the tensor cores: the two contractions run as tcgen05 kernels.
 static int run_tc(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
 	const void* Cm, int64_t cs, const float* D, const float* dt_bias, const float* init, void* y, int64_t ys, float* fin,
-	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st, int dt_softplus)
 {
 	const __half* xh = static_cast<const __half*>(x);
 	const __half* bh = static_cast<const __half*>(Bm);
 	const __half* ch = static_cast<const __half*>(Cm);
-	int rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, 1, d, w, st);
+	int rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
 	if (rc) return rc;
 	rc = ssd_chunk_state_tc(xh, xs, bh, bs, d, w, st);
 	if (rc) return rc;
@@ -60,7 +60,8 @@ extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t 
 	if (chunk > 256) return B200_ERR_UNSUPPORTED;
 	if (x_stride < H * P || y_stride < H * P || dt_stride < H || B_stride < G * N || C_stride < G * N) return B200_ERR_BAD_SHAPE;
 	if (dtype != B200_F16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
-	if (!dt_softplus) return B200_ERR_UNSUPPORTED;  // the mixer always applies softplus (scripts/zamba2/mamba_chunk_scan_comb.py:44-45)
+	// the mixer always applies softplus (scripts/zamba2/mamba_chunk_scan_comb.py:44-45)
+	if (dt_softplus != B200_DT_SOFTPLUS && dt_softplus != B200_DT_SOFTPLUS_EXACT) return B200_ERR_UNSUPPORTED;
 	if (batch == 0 || seqlen == 0) return B200_OK;
 	if (batch * cdiv(seqlen, chunk) * H > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 	SsdDims d{ batch, seqlen, static_cast<int>(H), static_cast<int>(P), static_cast<int>(G), static_cast<int>(N),
@@ -72,10 +73,10 @@ extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t 
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	if (dtype == B200_F16 && ssd_tc_supported(d, x, x_stride, B, B_stride, C, C_stride, y, y_stride))
 		return run_tc(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y, y_stride,
-			final_states, d, w, st);
+			final_states, d, w, st, dt_softplus);
 	if (dtype == B200_F16)
 		return run_simt<__half>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
-			y_stride, final_states, d, w, st);
+			y_stride, final_states, d, w, st, dt_softplus);
 	return run_simt<float>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
-		y_stride, final_states, d, w, st);
+		y_stride, final_states, d, w, st, dt_softplus);
 }

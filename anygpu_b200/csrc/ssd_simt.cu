@@ -27,9 +27,14 @@ __global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict_
 		float v = 0.f;
 		if (h < H)
 		{
+			// positions past the end of the sequence: the reference pads dt with zeros before bias and softplus (they then decay
+			// the final state); B200_DT_SOFTPLUS_EXACT gives them dt = 0, which leaves the state alone
 			if (t < seqlen) v = ldf(dt + (b * seqlen + t) * dts + h);
-			if (dt_bias) v += dt_bias[h];
-			if (dt_softplus) v = softplus_f32(v);
+			if (t < seqlen || dt_softplus != B200_DT_SOFTPLUS_EXACT)
+			{
+				if (dt_bias) v += dt_bias[h];
+				if (dt_softplus) v = softplus_f32(v);
+			}
 		}
 		sdt[l * (kCsHeads + 1) + hh] = v;
 	}
@@ -176,7 +181,8 @@ template int ssd_chunk_state_simt<float>(const float*, int64_t, const float*, in
 constexpr int kSpBatch = 8;
 
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restrict__ states, __half* __restrict__ prev16,
-	const float* __restrict__ dacs, const float* __restrict__ init, float* __restrict__ fin, int H, int PN, int Q, int nchunks)
+	const float* __restrict__ dacs, const float* init, float* fin /* may alias init: every thread reads its slice first */, int H, int PN,
+	int Q, int nchunks)
 {
 	const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
 	if (i >= PN) return;

@@ -127,10 +127,12 @@ def _tok_stride(t, inner):
     return st
 
 
-def tensor_mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, dt_bias=None, initial_states=None, a_is_log=False):
+def tensor_mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, dt_bias=None, initial_states=None, a_is_log=False,
+                                     exact_final_state=False):
     """Argument order of mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:167-172), dt_softplus on.
     x (b,l,H,P), dt (b,l,H), A (H) fp32, B/C (b,l,G,N), D (H) fp32, dt_bias (H) fp32, initial_states (b,H,P,N) fp32.
-    Returns (y (b,l,H,P), final_states (b,H,P,N) fp32)."""
+    Returns (y (b,l,H,P), final_states (b,H,P,N) fp32). When l is not a multiple of chunk_size, final_states follows the
+    reference script (padded positions decay it) unless exact_final_state is set (state after the last real token)."""
     b, l, H, P = x.shape
     G, N = B.shape[2], B.shape[3]
     y = torch.empty((b, l, H, P), dtype=x.dtype, device=x.device)
@@ -142,7 +144,7 @@ def tensor_mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, dt_bias
         assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
     capi.call("b200_mamba_chunk_scan_combined", _dt(x), _p(x), _tok_stride(x, H * P), _p(dt), _tok_stride(dt, H), _p(A),
               int(a_is_log), _p(B), _tok_stride(B, G * N), _p(C), _tok_stride(C, G * N), _p(D), _p(dt_bias), _p(initial_states),
-              _p(y), H * P, _p(fs), b, l, H, P, G, N, chunk_size, 1, _p(ws), ws.numel(), _stream())
+              _p(y), H * P, _p(fs), b, l, H, P, G, N, chunk_size, 2 if exact_final_state else 1, _p(ws), ws.numel(), _stream())
     return y, fs
 
 
@@ -228,6 +230,19 @@ class Mamba2Mixer:
         capi.call("b200_mamba2_mixer_prefill", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w), _p(u), _p(out),
                   b, l, _p(initial_states), _p(cache.conv_state) if cache else None, _p(cache.ssm_state) if cache else None,
                   _p(ws), ws.numel(), _stream())
+        return out
+
+    def prefill_continue(self, u, cache, out=None):
+        """`u` (b,l,d_model) are the next l tokens of sequences whose state so far is in `cache` (zeros for new sequences);
+        the cache is advanced in place. Feeding a prompt piece by piece equals one prefill over the whole prompt."""
+        b, l, _ = u.shape
+        assert u.is_contiguous() and u.dtype == self.dtype
+        lib = capi.load()
+        ws = self._ensure_ws(lib.b200_mamba2_mixer_prefill_continue_workspace_bytes(ctypes.byref(self.c_cfg), _DT[self.dtype], b, l))
+        if out is None:
+            out = torch.empty_like(u)
+        capi.call("b200_mamba2_mixer_prefill_continue", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w), _p(u),
+                  _p(out), b, l, _p(cache.conv_state), _p(cache.ssm_state), _p(ws), ws.numel(), _stream())
         return out
 
     def prefill_host(self, u_host, out_host):

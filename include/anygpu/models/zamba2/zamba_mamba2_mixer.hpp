@@ -120,3 +120,23 @@ inline Tensor<dtype, CUDA> tensor_zamba_mamba2_mixer(const ZambaMamba2weights<dt
 	}
 	return out;
 }
+
+// The next tokens (batch, seq_len, d_model) of sequences whose state so far is in `cache` (a freshly constructed cache for new
+// sequences): chunked prefill of long prompts. Any split of a prompt into pieces gives the outputs and the cache of one call.
+template <typename dtype>
+inline Tensor<dtype, CUDA> tensor_zamba_mamba2_mixer_continue(const ZambaMamba2weights<dtype>& weights, ZambaMambaCache<dtype>& cache,
+	const Tensor<dtype, CUDA>& hidden_states, const ZambaMamba2Config& config)
+{
+	ACASSERT(hidden_states.dim == 3, "hidden_states is (batch, seq_len, d_model)");
+	ACASSERT(hidden_states.shape[2] == config.d_model, "hidden size does not match the config");
+	const b200_mamba2_config cfg = config.c_struct();
+	const b200_mamba2_weights w = weights.c_struct();
+	const int dt = b200_dtype_of<dtype>();
+	Tensor<dtype, CUDA> out(hidden_states.dim, hidden_states.shape);
+	const int64 batch = hidden_states.shape[0], seqlen = hidden_states.shape[1];
+	const size_t ws_bytes = b200_mamba2_mixer_prefill_continue_workspace_bytes(&cfg, dt, batch, seqlen);
+	void* ws = b200_workspace(ws_bytes);
+	b200_check(b200_mamba2_mixer_prefill_continue(dt, &cfg, &w, hidden_states.buffer(), out.buffer(), batch, seqlen,
+		cache.conv_state.buffer(), cache.ssm_state.buffer(), ws, ws_bytes, nullptr), "tensor_zamba_mamba2_mixer_continue");
+	return out;
+}

@@ -122,8 +122,13 @@ int b200_rms_norm(int dtype, const void* x, int64_t x_stride, const void* w, voi
  *   x [b,l,H,P] (token stride x_stride), dt [b,l,H] (dt_stride), A [H] fp32 (or A_log when a_is_log != 0: A = -exp(A_log)),
  *   B, C [b,l,G,N] (B_stride, C_stride), D [H] fp32 or null, dt_bias [H] fp32 or null,
  *   initial_states [b,H,P,N] fp32 or null  ->  y [b,l,H,P] (y_stride), final_states [b,H,P,N] fp32 (or null).
- * chunk <= 256. seqlen need not be a multiple of chunk (y is exact; final_states then follows the script's
- * pad-before-softplus behaviour). */
+ * chunk <= 256. seqlen need not be a multiple of chunk: y is exact either way; final_states follows dt_softplus:
+ *   B200_DT_SOFTPLUS (1)        the script's behaviour: it pads dt with zeros BEFORE bias and softplus (:38-45), so the padded
+ *                               tail of the last chunk decays final_states by exp(A * softplus(dt_bias)) per padded position;
+ *   B200_DT_SOFTPLUS_EXACT (2)  padded positions carry dt = 0: final_states is the state after the last real token (what a
+ *                               decode step or a further prefill piece must start from). The mixer entry points use this. */
+#define B200_DT_SOFTPLUS 1
+#define B200_DT_SOFTPLUS_EXACT 2
 size_t b200_mamba_chunk_scan_combined_workspace_bytes(int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G,
 	int64_t N, int64_t chunk);
 int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
@@ -224,6 +229,17 @@ size_t b200_mamba2_mixer_decode_workspace_bytes(const b200_mamba2_config* cfg, i
  * ssm_state [b,H,P,N] fp32 are advanced in place. */
 int b200_mamba2_mixer_decode(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_t, void* out_t, void* conv_state, float* ssm_state, int64_t batch,
+	void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- prefill continuation (chunked prefill) -----------------------------------------------------------------
+ * `seqlen` more tokens for `batch` sequences whose state after the tokens seen so far is in conv_state [b, conv_dim, d_conv-1]
+ * (dtype) and ssm_state [b,H,P,N] fp32 (zeros for a fresh sequence); both are advanced in place. A long prompt fed in pieces of
+ * any length gives the same states and outputs as one call over the whole prompt (initial_states of
+ * mamba_chunk_scan_combined_ref, scripts/zamba2/mamba_chunk_scan_comb.py:93-95,196-197, plus the conv1d history), and a decode
+ * step may follow any piece. No counterpart in anyGPU. */
+size_t b200_mamba2_mixer_prefill_continue_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen);
+int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, int64_t batch, int64_t seqlen, void* conv_state, float* ssm_state,
 	void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---- Zamba2 Mamba decoder layer: the mixer with its input norm and residual -----------------------------------

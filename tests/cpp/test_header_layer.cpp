@@ -217,6 +217,21 @@ static void test_mixer_f32_and_dat_files(const std::string& tmp_dir)
 		cfg.d_state, cfg.d_conv, cfg.d_inner, cfg.eps, 0);
 	report("tensor_zamba_mamba2_mixer f32 decode", close_enough(out_t, et, 0.f, 1e-3f));
 
+	// the same prompt in two pieces (40 + 24 tokens; 40 is not a multiple of the chunk) from a fresh cache
+	{
+		ZambaMambaCache<float32> pc(cfg, b);
+		// batch 1: a token range of u is a contiguous block
+		auto piece = [&](int64 t0, int64 t1) {
+			std::vector<float32> h(u.buffer() + t0 * cfg.d_model, u.buffer() + t1 * cfg.d_model);
+			return Tensor<float32, CPU>(std::vector<int64>{ b, t1 - t0, cfg.d_model }, h).copy_to_cuda();
+		};
+		auto o1 = tensor_zamba_mamba2_mixer_continue(weights, pc, piece(0, 40), cfg).copy_to_host();
+		auto o2 = tensor_zamba_mamba2_mixer_continue(weights, pc, piece(40, l), cfg).copy_to_host();
+		const std::vector<float> e1(e.begin(), e.begin() + 40 * cfg.d_model), e2(e.begin() + 40 * cfg.d_model, e.end());
+		report("tensor_zamba_mamba2_mixer_continue f32, first piece of the prompt", close_enough(o1, e1, 0.f, 1e-3f));
+		report("tensor_zamba_mamba2_mixer_continue f32, second piece of the prompt", close_enough(o2, e2, 0.f, 1e-3f));
+	}
+
 	// the decoder layer around the same mixer: y = h + mixer(rms_norm(h) * w_in), prefill then one decode step
 	auto in_norm = crt_random_normal_tensor<float32, CPU>({ cfg.d_model }, 26, 0.1f);
 	for (int64 i = 0; i < cfg.d_model; ++i) in_norm.buffer()[i] += 1.0f;

@@ -228,3 +228,31 @@ def test_decoder_layer_f16_prefill_then_decode(ops, layout):
         wd = orc.decoder_decode(ht, w, w_in, 1e-5, cfg, ocs, oss, f16io=True)
         assert_close_f16(got, wd, f"decoder layer decode step {t}", max_fail_fraction=2e-3)
         assert rel_l2(got, wd) < 3e-3
+
+
+@pytest.mark.parametrize("pieces", [(512,), (256, 256), (100, 7, 300, 105), (1, 511)])
+def test_prefill_in_pieces_equals_one_prefill(ops, pieces):
+    """Chunked prefill: any split of the prompt gives the same outputs and states (piece lengths need not be multiples of
+    the scan chunk); a decode step continues from the cache afterwards."""
+    cfg = dict(SMALL, batch=2, seqlen=512, chunk=128)
+    w = f16w(synth.make_weights(cfg, 10))
+    u = synth.to_f16_values(synth.make_input(cfg, 10, batch=2, seqlen=513))
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16))
+    ud = torch.from_numpy(u).cuda().half()
+    whole_cache = ops.ZambaMambaCache.zeros(cfg, 2, torch.float16)
+    whole = mixer.prefill(ud[:, :512].contiguous(), whole_cache)
+    cache = ops.ZambaMambaCache.zeros(cfg, 2, torch.float16)
+    outs, t0 = [], 0
+    for n in pieces:
+        outs.append(mixer.prefill_continue(ud[:, t0:t0 + n].contiguous(), cache))
+        t0 += n
+    got = torch.cat(outs, dim=1)
+    want = orc.mixer_prefill(u[:, :512], w, dict(cfg, chunk=8), f16io=True)  # 512 = 64 chunks of 8: no padding in the oracle
+    assert_close_f16(host(got), want["out"], f"pieces {pieces} vs oracle", max_fail_fraction=1e-3)
+    assert rel_l2(host(got), want["out"]) < 2e-3
+    assert rel_l2(host(got), host(whole)) < 2e-3
+    assert torch.equal(cache.conv_state, whole_cache.conv_state)  # the last three inputs, whatever the split
+    assert_close_f16(host(cache.ssm_state), want["final_state"], "ssm state after the pieces", max_fail_fraction=1e-4)
+    d1 = mixer.decode(ud[:, 512].contiguous(), cache)
+    d2 = mixer.decode(ud[:, 512].contiguous(), whole_cache)
+    assert rel_l2(host(d1), host(d2)) < 3e-3

@@ -315,3 +315,37 @@ def test_rms_norm_golden_from_reference(ops, golden_dir):
     g = np.load(os.path.join(golden_dir, "rms_norm.npz"))
     got = ops.tensor_rms_norm(torch.from_numpy(g["x"]).cuda(), torch.from_numpy(g["w"]).cuda(), float(g["eps"]))
     assert_abs(got.cpu().numpy(), g["y_ref"], "rms_norm vs the reference CPU operator", 1e-4)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_ssd_ragged_length_final_state_modes(ops, dtype):
+    """seqlen % chunk != 0: y is exact in both modes; final_states follows the reference script (padded tail decays it) by
+    default and is the state after the last real token with exact_final_state."""
+    b, l, H, P, G, N, Q = 2, 300, 4, 64, 1, 64, 128
+    r = np.random.default_rng(31)
+    x = (r.standard_normal((b, l, H, P)) * 0.5).astype(np.float32)
+    dt = r.standard_normal((b, l, H)).astype(np.float32)
+    Bm = (r.standard_normal((b, l, G, N)) * 0.5).astype(np.float32)
+    Cm = (r.standard_normal((b, l, G, N)) * 0.5).astype(np.float32)
+    A = -(r.uniform(1, 16, H)).astype(np.float32)
+    D, dtb = np.ones(H, np.float32), np.full(H, -2.0, np.float32)
+    td = torch.float16 if dtype == "f16" else torch.float32
+    if dtype == "f16":
+        x, dt, Bm, Cm = f16v(x), f16v(dt), f16v(Bm), f16v(Cm)
+    dev = lambda a, t=td: torch.from_numpy(a).cuda().to(t)
+    args = (dev(x), dev(dt), dev(A, torch.float32), dev(Bm), dev(Cm), Q)
+    kw = dict(D=dev(D, torch.float32), dt_bias=dev(dtb, torch.float32))
+    y1, fs_ref_mode = ops.tensor_mamba_chunk_scan_combined(*args, **kw)
+    y2, fs_exact = ops.tensor_mamba_chunk_scan_combined(*args, exact_final_state=True, **kw)
+    assert torch.equal(y1, y2)
+    wy, wfs_script = orc.ssd_chunk_scan(x, dt, A, Bm, Cm, Q, D=D, dt_bias=dtb)         # restates the script, padding included
+    _, wfs_true = orc.ssd_recurrence(x, dt, A, Bm, Cm, D=D, dt_bias=dtb)                # token-by-token recurrence
+    assert np.abs(wfs_script - wfs_true).max() > 1e-3                                   # the two really differ on this input
+    if dtype == "f16":
+        assert_close_f16(y1.float().cpu().numpy(), wy, "ragged y")
+        assert_close_f16(fs_ref_mode.cpu().numpy(), wfs_script, "final state, script mode")
+        assert_close_f16(fs_exact.cpu().numpy(), wfs_true, "final state, exact mode")
+    else:
+        assert_abs(y1.cpu().numpy(), wy, "ragged y", 1e-3)
+        assert_abs(fs_ref_mode.cpu().numpy(), wfs_script, "final state, script mode", 1e-4)
+        assert_abs(fs_exact.cpu().numpy(), wfs_true, "final state, exact mode", 1e-4)
