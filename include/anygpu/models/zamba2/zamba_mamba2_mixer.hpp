@@ -7,6 +7,7 @@
 
 #include "../../b200_call.hpp"
 #include "../../io/dat_file.hpp"
+#include "../../io/safetensors_file.hpp"
 
 struct ZambaMamba2Config
 {
@@ -49,6 +50,23 @@ struct ZambaMamba2weights
 		D = load_tensor<float32>(D_path).copy_to_cuda();
 		norm_weight = to_device(load_tensor<float32>(norm_weight_path));
 		out_proj_weight = to_device(transposed(load_tensor<float32>(out_proj_path)));
+	}
+
+	// The same tensors straight from a .safetensors checkpoint: `prefix` + {in_proj.weight, conv1d.weight, conv1d.bias, dt_bias,
+	// A_log, D, norm.weight, out_proj.weight}, e.g. prefix "model.layers.3.mamba." (stored F32, F16 or BF16).
+	void load_safetensors(const std::string& path, const std::string& prefix)
+	{
+		auto get = [&](const char* leaf) { return sft_read_tensor_f32(path, prefix + leaf); };
+		in_proj_weight = to_device(transposed(get("in_proj.weight")));
+		auto cw = get("conv1d.weight");
+		if (cw.dim == 3) cw = tensor_view(cw, { cw.shape[0], cw.shape[2] });
+		conv1d_weight = to_device(cw);
+		conv1d_bias = to_device(get("conv1d.bias"));
+		dt_bias = get("dt_bias").copy_to_cuda();
+		A_log = get("A_log").copy_to_cuda();
+		D = get("D").copy_to_cuda();
+		norm_weight = to_device(get("norm.weight"));
+		out_proj_weight = to_device(transposed(get("out_proj.weight")));
 	}
 
 	b200_mamba2_weights c_struct() const

@@ -19,5 +19,19 @@ def build():
     return OUT
 
 
+SFT_OUT = os.path.join(HERE, "_build", "sft_dump")
+
+
+def build_sft_dump():
+    """Host-only program around the safetensors reader (compiled with nvcc for the CUDA headers tensor.hpp includes)."""
+    os.makedirs(os.path.dirname(SFT_OUT), exist_ok=True)
+    cmd = [os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc"), "-std=c++17", "-O1", "-x", "cu", "-DAC_WITH_ASSERT",
+           "-gencode", "arch=compute_100a,code=sm_100a", "-I", os.path.join(ROOT, "include"), os.path.join(HERE, "sft_dump.cpp"),
+           "-o", SFT_OUT]
+    subprocess.check_call(cmd)
+    return SFT_OUT
+
+
 if __name__ == "__main__":
     print(build())
+    print(build_sft_dump())

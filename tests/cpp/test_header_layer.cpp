@@ -4,6 +4,8 @@
 // Links libanygpu_b200.so (the product) and liboracle.so (test infrastructure, the checker).
 #include <cmath>
 #include <cstdio>
+#include <cstring>
+#include <fstream>
 
 #include "anygpu/fused/causal_conv1d.hpp"
 #include "anygpu/fused/mamba_chunk_scan.hpp"
@@ -216,6 +218,56 @@ static void test_mixer_f32_and_dat_files(const std::string& tmp_dir)
 		norm_w.buffer(), w_out.buffer(), ecs.data(), efs.data(), et.data(), b, cfg.d_model, cfg.d_inner, cfg.nheads, cfg.headdim, cfg.ngroups,
 		cfg.d_state, cfg.d_conv, cfg.d_inner, cfg.eps, 0);
 	report("tensor_zamba_mamba2_mixer f32 decode", close_enough(out_t, et, 0.f, 1e-3f));
+
+	// the same weights from a .safetensors file (F32 and BF16 entries, a __metadata__ object in the header)
+	{
+		struct Entry { std::string name; const Tensor<float32, CPU>* t; bool bf16; };
+		const std::vector<Entry> entries = {
+			{ "model.layers.0.mamba.in_proj.weight", &w_in_t, false }, { "model.layers.0.mamba.conv1d.weight", &conv_w, false },
+			{ "model.layers.0.mamba.conv1d.bias", &conv_b, false }, { "model.layers.0.mamba.dt_bias", &dt_bias, false },
+			{ "model.layers.0.mamba.A_log", &A_log, false }, { "model.layers.0.mamba.D", &D, true },
+			{ "model.layers.0.mamba.norm.weight", &norm_w, true }, { "model.layers.0.mamba.out_proj.weight", &w_out_t, false } };
+		std::string header = "{\"__metadata__\": {\"format\": \"pt\", \"note\": \"{braces} in a string\"}";
+		std::vector<char> data;
+		for (const auto& en : entries)
+		{
+			const size_t n = static_cast<size_t>(en.t->numel());
+			const size_t begin = data.size();
+			if (en.bf16)  // D and the norm weight are all ones: exact in bfloat16
+				for (size_t i = 0; i < n; ++i)
+				{
+					uint32_t u;
+					std::memcpy(&u, &en.t->buffer()[i], 4);
+					const uint16_t b16 = static_cast<uint16_t>(u >> 16);
+					data.insert(data.end(), reinterpret_cast<const char*>(&b16), reinterpret_cast<const char*>(&b16) + 2);
+				}
+			else
+				data.insert(data.end(), reinterpret_cast<const char*>(en.t->buffer()), reinterpret_cast<const char*>(en.t->buffer()) + n * 4);
+			header += ", \"" + en.name + "\": {\"dtype\": \"" + (en.bf16 ? "BF16" : "F32") + "\", \"shape\": [";
+			for (int64 k = 0; k < en.t->dim; ++k) header += (k ? ", " : "") + std::to_string(en.t->shape[k]);
+			header += "], \"data_offsets\": [" + std::to_string(begin) + ", " + std::to_string(data.size()) + "]}";
+		}
+		header += "}";
+		while (header.size() % 8) header.push_back(' ');
+		{
+			std::ofstream f(p + "mixer.safetensors", std::ios::binary);
+			const unsigned long long hs = header.size();
+			f.write(reinterpret_cast<const char*>(&hs), 8);
+			f.write(header.data(), static_cast<std::streamsize>(header.size()));
+			f.write(data.data(), static_cast<std::streamsize>(data.size()));
+		}
+		const auto infos = sft_read_tensorinfos(p + "mixer.safetensors");
+		report("safetensors header: 8 tensors, metadata skipped", infos.size() == 8 && infos[1].shape.size() == 3 && infos[5].dtype == "BF16");
+		ZambaMamba2weights<float32> sw;
+		sw.load_safetensors(p + "mixer.safetensors", "model.layers.0.mamba.");
+		auto same = [](const auto& a, const auto& b) {
+			auto ha = a.copy_to_host(), hb = b.copy_to_host();
+			return ha.numel() == hb.numel() && std::memcmp(ha.buffer(), hb.buffer(), sizeof(*ha.buffer()) * static_cast<size_t>(ha.numel())) == 0;
+		};
+		report("load_safetensors equals load_weights", same(sw.in_proj_weight, weights.in_proj_weight) && same(sw.conv1d_weight, weights.conv1d_weight) &&
+			same(sw.conv1d_bias, weights.conv1d_bias) && same(sw.dt_bias, weights.dt_bias) && same(sw.A_log, weights.A_log) && same(sw.D, weights.D) &&
+			same(sw.norm_weight, weights.norm_weight) && same(sw.out_proj_weight, weights.out_proj_weight));
+	}
 
 	// the same prompt in two pieces (40 + 24 tokens; 40 is not a multiple of the chunk) from a fresh cache
 	{
