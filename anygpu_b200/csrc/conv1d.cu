@@ -3,7 +3,7 @@
 // accesses; the (width-1)-element halo comes from the neighbouring lane by warp shuffle (or a cached re-read at
 // warp boundaries). fp32 accumulation in the tap order of anyGPU's CPU operator
 // (srcs/fused/causal_conv1d.hpp:55-84): taps oldest-first, bias last, then x / (1 + exp(-x)).
-#include "common.cuh"
+#include "conv_dt_bodies.cuh"
 
 namespace b200 {
 
@@ -132,92 +132,7 @@ __global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x
 	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
 	int seqlen, int dims, unsigned cvec /* ceil(dims / V) */, unsigned nwork /* cvec * token blocks */)
 {
-	const unsigned wid = blockIdx.x * blockDim.x + threadIdx.x;
-	if (wid >= nwork) return;
-	const unsigned tb = wid / cvec;
-	const int c0 = static_cast<int>(wid - tb * cvec) * V;
-	const int64_t b = blockIdx.y;
-	const int t0 = static_cast<int>(tb) * TL;
-	const T* xb = x + b * seqlen * xs + c0;
-	T* yb = y + b * seqlen * ys + c0;
-
-	// rows t0-(W-1) .. t0+TL-1, all requested before the first use
-	Pack<T, V> raw[TL + W - 1];
-#pragma unroll
-	for (int i = 0; i < TL + W - 1; ++i)
-	{
-		const int t = t0 - (W - 1) + i;
-		if (t >= 0 && t < seqlen) raw[i].load(xb + static_cast<int64_t>(t) * xs);
-	}
-
-	float wt[W][V], bs[V];
-#pragma unroll
-	for (int c = 0; c < V; ++c)
-	{
-		bs[c] = ldf(bias + c0 + c);
-#pragma unroll
-		for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + static_cast<int64_t>(c0 + c) * W + k);
-	}
-
-	float f[TL + W - 1][V];
-#pragma unroll
-	for (int i = 0; i < TL + W - 1; ++i)
-	{
-		const int t = t0 - (W - 1) + i;
-		if (t >= 0)
-		{
-			if (t < seqlen) raw[i].unpack(f[i]);
-			else
-			{
-#pragma unroll
-				for (int c = 0; c < V; ++c) f[i][c] = 0.f;
-			}
-		}
-		else
-		{
-			// before the sequence: initial conv_state [b, dims, W-1] (oldest first) or zeros
-#pragma unroll
-			for (int c = 0; c < V; ++c) f[i][c] = init ? ldf(init + (b * dims + c0 + c) * (W - 1) + (t + (W - 1))) : 0.f;
-		}
-	}
-
-#pragma unroll
-	for (int i = 0; i < TL; ++i)
-	{
-		if (t0 + i < seqlen)
-		{
-			float out[V];
-#pragma unroll
-			for (int c = 0; c < V; ++c)
-			{
-				float acc = 0.f;
-#pragma unroll
-				for (int k = 0; k < W; ++k) acc += wt[k][c] * f[i + k][c];
-				acc += bs[c];
-				out[c] = silu_f32(acc);
-			}
-			Pack<T, V> o;
-			o.pack(out);
-			o.store(yb + static_cast<int64_t>(t0 + i) * ys);
-		}
-	}
-
-	// the thread that consumed the last token holds the next conv_state: the W-1 inputs ending at token seqlen-1
-	if (fin != nullptr && t0 < seqlen && t0 + TL >= seqlen)
-	{
-		const int last = seqlen - 1 - t0;  // index of the last valid token inside this block, 0 <= last < TL
-#pragma unroll
-		for (int i = 0; i < TL; ++i)
-		{
-			if (i == last)
-			{
-#pragma unroll
-				for (int k = 0; k < W - 1; ++k)
-#pragma unroll
-					for (int c = 0; c < V; ++c) stf(fin + (b * dims + c0 + c) * (W - 1) + k, f[i + 1 + k][c]);
-			}
-		}
-	}
+	conv1d_tok_body<T, V, W, TL>(x, xs, w, bias, y, ys, init, fin, seqlen, dims, cvec, nwork, blockIdx.x, blockIdx.y);
 }
 
 // ---- decode: one token, rolling state ----------------------------------------------------------------------

@@ -1,0 +1,182 @@
+// Bodies of the token-major conv1d kernel and of the scan's dt stage as device functions: each is a kernel of its own
+// (conv1d.cu, ssd_simt.cu) and both run side by side in ONE launch in the prefill mixer (conv_dt_fused.cu), where the dt stage
+// (15 us of launch and ramp for a few MB) would otherwise sit between two bandwidth-bound kernels.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+// One thread owns V consecutive channels and TL consecutive tokens of block (block_x, block_y = batch index).
+template <typename T, int V, int W, int TL>
+__device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
+	int seqlen, int dims, unsigned cvec /* ceil(dims / V) */, unsigned nwork /* cvec * token blocks */, unsigned block_x, unsigned block_y)
+{
+	const unsigned wid = block_x * blockDim.x + threadIdx.x;
+	if (wid >= nwork) return;
+	const unsigned tb = wid / cvec;
+	const int c0 = static_cast<int>(wid - tb * cvec) * V;
+	const int64_t b = block_y;
+	const int t0 = static_cast<int>(tb) * TL;
+	const T* xb = x + b * seqlen * xs + c0;
+	T* yb = y + b * seqlen * ys + c0;
+
+	// rows t0-(W-1) .. t0+TL-1, all requested before the first use
+	Pack<T, V> raw[TL + W - 1];
+#pragma unroll
+	for (int i = 0; i < TL + W - 1; ++i)
+	{
+		const int t = t0 - (W - 1) + i;
+		if (t >= 0 && t < seqlen) raw[i].load(xb + static_cast<int64_t>(t) * xs);
+	}
+
+	float wt[W][V], bs[V];
+#pragma unroll
+	for (int c = 0; c < V; ++c)
+	{
+		bs[c] = ldf(bias + c0 + c);
+#pragma unroll
+		for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + static_cast<int64_t>(c0 + c) * W + k);
+	}
+
+	float f[TL + W - 1][V];
+#pragma unroll
+	for (int i = 0; i < TL + W - 1; ++i)
+	{
+		const int t = t0 - (W - 1) + i;
+		if (t >= 0)
+		{
+			if (t < seqlen) raw[i].unpack(f[i]);
+			else
+			{
+#pragma unroll
+				for (int c = 0; c < V; ++c) f[i][c] = 0.f;
+			}
+		}
+		else
+		{
+			// before the sequence: initial conv_state [b, dims, W-1] (oldest first) or zeros
+#pragma unroll
+			for (int c = 0; c < V; ++c) f[i][c] = init ? ldf(init + (b * dims + c0 + c) * (W - 1) + (t + (W - 1))) : 0.f;
+		}
+	}
+
+#pragma unroll
+	for (int i = 0; i < TL; ++i)
+	{
+		if (t0 + i < seqlen)
+		{
+			float out[V];
+#pragma unroll
+			for (int c = 0; c < V; ++c)
+			{
+				float acc = 0.f;
+#pragma unroll
+				for (int k = 0; k < W; ++k) acc += wt[k][c] * f[i + k][c];
+				acc += bs[c];
+				out[c] = silu_f32(acc);
+			}
+			Pack<T, V> o;
+			o.pack(out);
+			o.store(yb + static_cast<int64_t>(t0 + i) * ys);
+		}
+	}
+
+	// the thread that consumed the last token holds the next conv_state: the W-1 inputs ending at token seqlen-1
+	if (fin != nullptr && t0 < seqlen && t0 + TL >= seqlen)
+	{
+		const int last = seqlen - 1 - t0;  // index of the last valid token inside this block, 0 <= last < TL
+#pragma unroll
+		for (int i = 0; i < TL; ++i)
+		{
+			if (i == last)
+			{
+#pragma unroll
+				for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+					for (int c = 0; c < V; ++c) stf(fin + (b * dims + c0 + c) * (W - 1) + k, f[i + 1 + k][c]);
+			}
+		}
+	}
+}
+
+// dt = softplus(dt_raw + bias); dAcs = cumsum_l(dt * A) within each chunk; colf = column factor of the rank-1 decay.
+// Block (block_x = batch * nchunks + chunk, block_y = group of kCsHeads heads); sdt: [Q][kCsHeads + 1] floats of shared memory.
+constexpr int kCsHeads = 8;
+
+template <typename T>
+__device__ __forceinline__ void ssd_dt_cumsum_body(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
+	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
+	float* __restrict__ dt_out, float* __restrict__ dacs_out, float* __restrict__ colf_out, float* sdt, unsigned block_x, unsigned block_y)
+{
+	const int64_t b = block_x / nchunks;
+	const int c = static_cast<int>(block_x % nchunks);
+	const int h0 = block_y * kCsHeads;
+	for (int idx = threadIdx.x; idx < Q * kCsHeads; idx += blockDim.x)
+	{
+		const int l = idx / kCsHeads, hh = idx % kCsHeads;
+		const int h = h0 + hh;
+		const int64_t t = static_cast<int64_t>(c) * Q + l;
+		float v = 0.f;
+		if (h < H)
+		{
+			// positions past the end of the sequence: the reference pads dt with zeros before bias and softplus (they then decay
+			// the final state); B200_DT_SOFTPLUS_EXACT gives them dt = 0, which leaves the state alone
+			if (t < seqlen) v = ldf(dt + (b * seqlen + t) * dts + h);
+			if (t < seqlen || dt_softplus != B200_DT_SOFTPLUS_EXACT)
+			{
+				if (dt_bias) v += dt_bias[h];
+				if (dt_softplus) v = softplus_f32(v);
+			}
+		}
+		sdt[l * (kCsHeads + 1) + hh] = v;
+	}
+	__syncthreads();
+	const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+	const int ep = (Q + 31) / 32;  // consecutive positions per lane (<= 8)
+	for (int hh = wid; hh < kCsHeads; hh += blockDim.x / 32)
+	{
+		const int h = h0 + hh;
+		if (h >= H) break;
+		const float a = a_is_log ? -expf(A[h]) : A[h];
+		float loc[8];
+		float run = 0.f;
+#pragma unroll
+		for (int i = 0; i < 8; ++i)
+		{
+			const int l = lane * ep + i;
+			float v = 0.f;
+			if (i < ep && l < Q) v = sdt[l * (kCsHeads + 1) + hh] * a;
+			run += v;
+			loc[i] = run;
+		}
+		// exclusive prefix of lane totals
+		float incl = run;
+#pragma unroll
+		for (int o = 1; o < 32; o <<= 1)
+		{
+			const float n = __shfl_up_sync(0xffffffffu, incl, o);
+			if (lane >= o) incl += n;
+		}
+		const float excl = incl - run;
+		// dAcs at the end of this lane's 64-position block (Q % 64 == 0: ep divides 64, a block is 64/ep consecutive lanes)
+		const bool blocks64 = (Q % 64) == 0 && (64 % ep) == 0;
+		const float blk_end = blocks64 ? __shfl_sync(0xffffffffu, excl + run, lane | (64 / ep - 1)) : 0.f;
+		const int64_t base = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+#pragma unroll
+		for (int i = 0; i < 8; ++i)
+		{
+			const int l = lane * ep + i;
+			if (i < ep && l < Q)
+			{
+				const float dv = sdt[l * (kCsHeads + 1) + hh];
+				dacs_out[base + l] = excl + loc[i];
+				dt_out[base + l] = dv;
+				if (blocks64) colf_out[base + l] = __expf(blk_end - (excl + loc[i])) * dv;
+			}
+		}
+	}
+}
+
+}  // namespace b200

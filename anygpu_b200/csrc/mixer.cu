@@ -30,6 +30,21 @@ static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
 	return true;
 }
 
+// conv1d + the scan's dt stage in one launch (conv_dt_fused.cu), and the scan without / with chosen stages (ssd.cu)
+constexpr int kSsdStageScan = 2;
+bool conv_dt_fused_applies(int dtype, const void* x, int64_t xs, const void* y, int64_t ys, int64_t batch, int64_t seqlen, int64_t dims,
+	int width);
+int conv1d_tokens_with_scan_dt(int dtype, const void* x, int64_t xs, const void* w, const void* bias, void* y, int64_t ys,
+	const void* init, void* fin, int64_t batch, int64_t seqlen, int64_t dims, int width, const void* dt, int64_t dts, const float* A,
+	int a_is_log, const float* dt_bias, int dt_softplus, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, void* ssd_workspace,
+	size_t ssd_workspace_bytes, cudaStream_t st);
+int ssd_combined_stages(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
+	const float* D, const float* dt_bias, const float* initial_states,
+	void* y, int64_t y_stride, float* final_states,
+	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
+	void* workspace, size_t workspace_bytes, void* stream, int stages);
+
 int linear_f16_residual(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
 	const void* residual, int64_t ldr, cudaStream_t st);
 
@@ -167,14 +182,22 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 		m.d_in_proj, stream);
 	if (rc) return rc;
 	stage_mark(1, st);
-	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
-		conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+	const char* dtp = ws.zxbcdt + (d_inner + m.conv_dim) * e;
+	const bool dt_in_conv = conv_dt_fused_applies(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, ws.xbc, m.conv_dim, batch, seqlen, m.conv_dim,
+		static_cast<int>(cfg->d_conv)) && cfg->chunk <= 256 && batch * cdiv(seqlen, cfg->chunk) * cfg->nheads <= 0x7fffffffLL;
+	if (dt_in_conv)
+		rc = conv1d_tokens_with_scan_dt(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
+			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), dtp, m.d_in_proj, w->A_log, 1, w->dt_bias,
+			B200_DT_SOFTPLUS_EXACT, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, ws.ssd, ws.ssd_bytes, st);
+	else
+		rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
+			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
 	if (rc) return rc;
 	stage_mark(2, st);
-	rc = b200_mamba_chunk_scan_combined(dtype, ws.xbc, m.conv_dim, ws.zxbcdt + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
-		ws.xbc + d_inner * e, m.conv_dim, ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, ws.y, d_inner,
-		ssm_state_out, batch, seqlen, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes,
-		stream);
+	rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
+		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, ws.y, d_inner, ssm_state_out, batch, seqlen, cfg->nheads,
+		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream,
+		dt_in_conv ? kSsdStageScan : 3);
 	if (rc) return rc;
 	stage_mark(3, st);
 	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,

@@ -3,13 +3,18 @@
 
 namespace b200 {
 
+// The scan in two parts: kSsdStageDt (softplus, in-chunk cumulative sums: needs dt only; the prefill mixer runs it inside its
+// conv1d launch) and kSsdStageScan (chunk states, state passing, chunk scan: needs x, B, C and the first part's results).
+constexpr int kSsdStageDt = 1, kSsdStageScan = 2;
+
 template <typename T>
 static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
 	const void* Cm, int64_t cs, const float* D, const float* dt_bias, const float* init, void* y, int64_t ys, float* fin,
-	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st, int dt_softplus)
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st, int dt_softplus, int stages)
 {
-	int rc = ssd_dt_cumsum<T>(static_cast<const T*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
-	if (rc) return rc;
+	int rc = B200_OK;
+	if (stages & kSsdStageDt) rc = ssd_dt_cumsum<T>(static_cast<const T*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
+	if (rc || !(stages & kSsdStageScan)) return rc;
 	rc = ssd_chunk_state_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, d, w, st);
 	if (rc) return rc;
 	rc = ssd_state_passing(init, fin, false, d, w, st);
@@ -21,13 +26,14 @@ static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, cons
 // f16 activations on the tensor cores: the two contractions run as tcgen05 kernels.
 static int run_tc(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
 	const void* Cm, int64_t cs, const float* D, const float* dt_bias, const float* init, void* y, int64_t ys, float* fin,
-	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st, int dt_softplus)
+	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st, int dt_softplus, int stages)
 {
 	const __half* xh = static_cast<const __half*>(x);
 	const __half* bh = static_cast<const __half*>(Bm);
 	const __half* ch = static_cast<const __half*>(Cm);
-	int rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
-	if (rc) return rc;
+	int rc = B200_OK;
+	if (stages & kSsdStageDt) rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
+	if (rc || !(stages & kSsdStageScan)) return rc;
 	rc = ssd_chunk_state_tc(xh, xs, bh, bs, d, w, st);
 	if (rc) return rc;
 	rc = ssd_state_passing(init, fin, true, d, w, st);
@@ -48,12 +54,13 @@ extern "C" size_t b200_mamba_chunk_scan_combined_workspace_bytes(int64_t batch, 
 	return ssd_carve(nullptr, d).bytes;
 }
 
-extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+namespace b200 {
+int ssd_combined_stages(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
 	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
 	const float* D, const float* dt_bias, const float* initial_states,
 	void* y, int64_t y_stride, float* final_states,
 	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
-	void* workspace, size_t workspace_bytes, void* stream)
+	void* workspace, size_t workspace_bytes, void* stream, int stages)
 {
 	if (!x || !dt || !A || !B || !C || !y) return B200_ERR_NULL;
 	if (batch < 0 || seqlen < 0 || H <= 0 || P <= 0 || G <= 0 || N <= 0 || chunk <= 0 || H % G != 0) return B200_ERR_BAD_SHAPE;
@@ -73,10 +80,23 @@ extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t 
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	if (dtype == B200_F16 && ssd_tc_supported(d, x, x_stride, B, B_stride, C, C_stride, y, y_stride))
 		return run_tc(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y, y_stride,
-			final_states, d, w, st, dt_softplus);
+			final_states, d, w, st, dt_softplus, stages);
 	if (dtype == B200_F16)
 		return run_simt<__half>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
-			y_stride, final_states, d, w, st, dt_softplus);
+			y_stride, final_states, d, w, st, dt_softplus, stages);
 	return run_simt<float>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
-		y_stride, final_states, d, w, st, dt_softplus);
+		y_stride, final_states, d, w, st, dt_softplus, stages);
+}
+}  // namespace b200
+
+extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
+	const float* A, int a_is_log, const void* B, int64_t B_stride, const void* C, int64_t C_stride,
+	const float* D, const float* dt_bias, const float* initial_states,
+	void* y, int64_t y_stride, float* final_states,
+	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	return ssd_combined_stages(dtype, x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
+		y_stride, final_states, batch, seqlen, H, P, G, N, chunk, dt_softplus, workspace, workspace_bytes, stream,
+		kSsdStageDt | kSsdStageScan);
 }

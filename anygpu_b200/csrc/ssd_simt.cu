@@ -2,87 +2,21 @@
 // the two contraction stages. The SIMT contractions serve Tensor<float32> callers (fp32 end to end, like the
 // reference's CPU path); f16 callers take the tensor-core stages in ssd_tc.cu.
 #include "ssd_common.cuh"
+#include "conv_dt_bodies.cuh"
 
 namespace b200 {
 
 // ---- stage 1: dt = softplus(dt_raw + bias); dAcs = cumsum_l(dt * A) within each chunk -------------------------
 // grid (b*nchunks, ceil(H/8)), 256 threads. Positions past seqlen hold dt_raw = 0 BEFORE bias and softplus,
 // exactly as the reference pads (scripts/zamba2/mamba_chunk_scan_comb.py:38-45).
-constexpr int kCsHeads = 8;
-
 template <typename T>
 __global__ void __launch_bounds__(256) ssd_dt_cumsum_kernel(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
 	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
 	float* __restrict__ dt_out, float* __restrict__ dacs_out, float* __restrict__ colf_out)
 {
 	extern __shared__ float sdt[];  // [Q][kCsHeads + 1]
-	const int64_t b = blockIdx.x / nchunks;
-	const int c = static_cast<int>(blockIdx.x % nchunks);
-	const int h0 = blockIdx.y * kCsHeads;
-	for (int idx = threadIdx.x; idx < Q * kCsHeads; idx += blockDim.x)
-	{
-		const int l = idx / kCsHeads, hh = idx % kCsHeads;
-		const int h = h0 + hh;
-		const int64_t t = static_cast<int64_t>(c) * Q + l;
-		float v = 0.f;
-		if (h < H)
-		{
-			// positions past the end of the sequence: the reference pads dt with zeros before bias and softplus (they then decay
-			// the final state); B200_DT_SOFTPLUS_EXACT gives them dt = 0, which leaves the state alone
-			if (t < seqlen) v = ldf(dt + (b * seqlen + t) * dts + h);
-			if (t < seqlen || dt_softplus != B200_DT_SOFTPLUS_EXACT)
-			{
-				if (dt_bias) v += dt_bias[h];
-				if (dt_softplus) v = softplus_f32(v);
-			}
-		}
-		sdt[l * (kCsHeads + 1) + hh] = v;
-	}
-	__syncthreads();
-	const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-	const int ep = (Q + 31) / 32;  // consecutive positions per lane (<= 8)
-	for (int hh = wid; hh < kCsHeads; hh += blockDim.x / 32)
-	{
-		const int h = h0 + hh;
-		if (h >= H) break;
-		const float a = a_is_log ? -expf(A[h]) : A[h];
-		float loc[8];
-		float run = 0.f;
-#pragma unroll
-		for (int i = 0; i < 8; ++i)
-		{
-			const int l = lane * ep + i;
-			float v = 0.f;
-			if (i < ep && l < Q) v = sdt[l * (kCsHeads + 1) + hh] * a;
-			run += v;
-			loc[i] = run;
-		}
-		// exclusive prefix of lane totals
-		float incl = run;
-#pragma unroll
-		for (int o = 1; o < 32; o <<= 1)
-		{
-			const float n = __shfl_up_sync(0xffffffffu, incl, o);
-			if (lane >= o) incl += n;
-		}
-		const float excl = incl - run;
-		// dAcs at the end of this lane's 64-position block (Q % 64 == 0: ep divides 64, a block is 64/ep consecutive lanes)
-		const bool blocks64 = (Q % 64) == 0 && (64 % ep) == 0;
-		const float blk_end = blocks64 ? __shfl_sync(0xffffffffu, excl + run, lane | (64 / ep - 1)) : 0.f;
-		const int64_t base = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
-#pragma unroll
-		for (int i = 0; i < 8; ++i)
-		{
-			const int l = lane * ep + i;
-			if (i < ep && l < Q)
-			{
-				const float dv = sdt[l * (kCsHeads + 1) + hh];
-				dacs_out[base + l] = excl + loc[i];
-				dt_out[base + l] = dv;
-				if (blocks64) colf_out[base + l] = __expf(blk_end - (excl + loc[i])) * dv;
-			}
-		}
-	}
+	ssd_dt_cumsum_body<T>(dt, dts, A, a_is_log, dt_bias, dt_softplus, seqlen, H, Q, nchunks, dt_out, dacs_out, colf_out, sdt, blockIdx.x,
+		blockIdx.y);
 }
 
 template <typename T>
