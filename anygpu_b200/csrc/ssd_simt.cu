@@ -145,7 +145,8 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restric
 		{
 			if (c0 + j < nchunks)
 			{
-				*reinterpret_cast<float4*>(sp + (c0 + j) * cstride) = s;
+				// the state before chunk c replaces the chunk's own state: in fp32 for the SIMT scan, as f16 for the tensor-core scan
+				if (pp == nullptr) *reinterpret_cast<float4*>(sp + (c0 + j) * cstride) = s;
 				if (pp)
 				{
 					__half2* q = reinterpret_cast<__half2*>(pp + (c0 + j) * cstride);
