@@ -144,6 +144,23 @@ def cpu_reference_throughput(name, tokens_per_worker, workers, steps, warmup):
     return workers * tokens_per_worker * steps / dt, dt / steps, kind
 
 
+def reference_cuda_kernels():
+    """The reference's own CUDA kernels recompiled for sm_100a (oracle/_ref/ref_cuda_bench, built by `make -C oracle ref_cuda`
+    where the reference checkout is present), timed on this GPU at the cfg2 projection shapes and the conv configuration: a second
+    baseline beside the CPU one. Runs as a child process (the reference's launchers exit on any CUDA error). None when not built."""
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "oracle", "_ref", "ref_cuda_bench")
+    if not os.path.exists(exe):
+        return None
+    out = {}
+    for what in ("mm", "conv"):
+        try:
+            r = subprocess.run([exe, what, "3"], capture_output=True, text=True, timeout=180)
+            out[what] = json.loads(r.stdout.strip().splitlines()[-1]) if r.returncode == 0 and r.stdout.strip() else {"failed": r.returncode}
+        except Exception as ex:  # noqa: BLE001 - a baseline that cannot run is reported, not fatal
+            out[what] = {"failed": str(ex)[:100]}
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -297,13 +314,16 @@ def run_gpu(args):
         dt = time.perf_counter() - t0
         cpu = {"value": cpu_tokens / dt, "unit": UNIT, "cores": 1, "kind": kind,
                "sample": f"{cpu_tokens} tokens of one sequence through the whole mixer, single thread (the reference is single-threaded), {dt:.1f} s"}
+        ref_cuda = reference_cuda_kernels()
+        if ref_cuda:
+            cpu["reference_cuda_kernels"] = ref_cuda
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic", "config": _config_dict(args.workload, cfg, world), "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
                     "ms_per_step": e2e_ms / args.steps},
-            "gpu_launches": 8 * args.steps, "roofline": roofline, "whole_step": whole, "cpu_baseline": cpu}
+            "gpu_launches": 7 * args.steps, "roofline": roofline, "whole_step": whole, "cpu_baseline": cpu}
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

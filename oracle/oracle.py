@@ -19,10 +19,12 @@ _i64 = ctypes.c_int64
 
 
 def build(with_ref=True):
-    """Compile liboracle.so (always) and _ref/libanygpu_ref.so (only where the anyGPU checkout exists)."""
+    """Compile liboracle.so (always) and, only where the anyGPU checkout exists, _ref/libanygpu_ref.so (its CPU operators) and
+    _ref/ref_cuda_bench (a timing program around its CUDA kernels)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
     if with_ref and os.path.exists("/root/reference/srcs/core/core.cpp"):
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref_cuda"])
 
 
 def lib():
