@@ -70,6 +70,12 @@ SIGNATURES = {
     "b200_mamba2_mixer_prefill_continue_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
     "b200_mamba2_mixer_prefill_continue": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _i64,
                                                   _i64, _vp, _vp, _vp, _sz, _vp]),
+    "b200_mamba2_mixer_prefill_sp_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
+    "b200_mamba2_mixer_prefill_sp_begin": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _i64, _i64,
+                                                  _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200_ssm_segment_prefix": (_int, [_vp, _vp, _int, _i64, _i64, _i64, _i64, _vp, _vp]),
+    "b200_mamba2_mixer_prefill_sp_finish": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _i64, _i64,
+                                                   _vp, _vp, _vp, _sz, _vp]),
     "b200_rms_norm": (_int, [_int, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _f32, _int, _vp]),
     "b200_mamba2_decoder_prefill_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
     "b200_mamba2_decoder_prefill": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _f32, _vp, _vp,

@@ -31,7 +31,7 @@ static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
 }
 
 // conv1d + the scan's dt stage in one launch (conv_dt_fused.cu), and the scan without / with chosen stages (ssd.cu)
-constexpr int kSsdStageScan = 2;
+constexpr int kSsdStageDt = 1, kSsdStageStates = 2, kSsdStagePass = 4, kSsdStageSummary = 8;
 bool conv_dt_fused_applies(int dtype, const void* x, int64_t xs, const void* y, int64_t ys, int64_t batch, int64_t seqlen, int64_t dims,
 	int width);
 int conv1d_tokens_with_scan_dt(int dtype, const void* x, int64_t xs, const void* w, const void* bias, void* y, int64_t ys,
@@ -44,6 +44,11 @@ int ssd_combined_stages(int dtype, const void* x, int64_t x_stride, const void* 
 	void* y, int64_t y_stride, float* final_states,
 	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
 	void* workspace, size_t workspace_bytes, void* stream, int stages);
+
+int ssd_segment_logdecay_of(float* out, int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk,
+	void* workspace, cudaStream_t st);
+int ssd_segment_prefix(const float* seg_states, const float* seg_logdecay, int nseg, int64_t batch, int64_t H, int64_t P, int64_t N,
+	float* state_in, cudaStream_t st);
 
 int linear_f16_residual(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
 	const void* residual, int64_t ldr, cudaStream_t st);
@@ -197,7 +202,7 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 	rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
 		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, ws.y, d_inner, ssm_state_out, batch, seqlen, cfg->nheads,
 		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream,
-		dt_in_conv ? kSsdStageScan : 3);
+		(dt_in_conv ? 0 : kSsdStageDt) | kSsdStageStates | kSsdStagePass);
 	if (rc) return rc;
 	stage_mark(3, st);
 	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,
@@ -583,6 +588,124 @@ extern "C" int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_c
 	if (rc) return rc;
 	if (cs_bytes) B200_CUDA_TRY(cudaMemcpyAsync(conv_state, next_cs, cs_bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
 	return B200_OK;
+}
+
+// ---- sequence-parallel prefill: one sequence split into segments, one segment per GPU ----------------------------------------
+// Everything but the scan's state is local to a segment once the d_conv-1 tokens before it are known (they are re-projected
+// here: cheaper than shipping conv inputs). The state is linear in what enters the segment: begin() runs in_proj, conv1d and the
+// per-chunk states and reports the segment's outgoing state for a ZERO incoming state plus the log of its total decay;
+// after the ranks have exchanged those two small tensors, b200_ssm_segment_prefix folds them into the true incoming state
+// and finish() runs the state passing, the chunk scan, the gated norm and out_proj. The library does not communicate.
+// Workspace: projected halo [b*(d_conv-1), d_in_proj] | halo conv_state [b, conv_dim, d_conv-1] | halo conv output (unused) | the prefill workspace, which
+// must be handed unchanged from begin() to finish().
+namespace b200 {
+struct SpWs
+{
+	char* halo_zx;
+	char* halo_cs;
+	char* halo_y;
+	char* inner;
+	size_t inner_bytes, bytes;
+};
+static SpWs carve_sp(void* base, const b200_mamba2_config* c, const MixerDims& m, int64_t batch, int64_t seglen)
+{
+	SpWs w;
+	char* p = static_cast<char*>(base);
+	size_t off = 0;
+	const int64_t hw = c->d_conv - 1;
+	w.halo_zx = p + off; off += align_up(static_cast<size_t>(batch) * hw * m.d_in_proj * m.esz, 256);
+	w.halo_cs = p + off; off += align_up(static_cast<size_t>(batch) * m.conv_dim * hw * m.esz, 256);
+	w.halo_y = p + off; off += align_up(static_cast<size_t>(batch) * m.conv_dim * hw * m.esz, 256);
+	w.inner = p + off;
+	w.inner_bytes = carve_prefill(nullptr, c, m, batch, seglen).bytes;
+	w.bytes = off + w.inner_bytes;
+	return w;
+}
+}  // namespace b200
+
+extern "C" size_t b200_mamba2_mixer_prefill_sp_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seglen)
+{
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0 || seglen <= 0) return 0;
+	return carve_sp(nullptr, cfg, m, batch, seglen).bytes;
+}
+
+extern "C" int b200_mamba2_mixer_prefill_sp_begin(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_seg, const void* u_halo, int64_t batch, int64_t seglen, float* seg_state, float* seg_logdecay, void* conv_state_out,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !u_seg || !seg_state || !seg_logdecay) return B200_ERR_NULL;
+	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log) return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0 || seglen <= 0) return B200_ERR_BAD_SHAPE;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const SpWs sp = carve_sp(workspace, cfg, m, batch, seglen);
+	if (workspace_bytes < sp.bytes) return B200_ERR_WORKSPACE;
+	const PrefillWs ws = carve_prefill(sp.inner, cfg, m, batch, seglen);
+	const int64_t T = batch * seglen, d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state, hw = cfg->d_conv - 1;
+	const size_t e = m.esz;
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	int rc;
+	const void* conv_in = nullptr;
+	if (u_halo != nullptr && hw > 0)
+	{
+		// the conv inputs of the d_conv-1 tokens before the segment: project them and let the conv kernel lay them out as a state
+		rc = b200_linear(dtype, u_halo, cfg->d_model, w->in_proj_weight, w->in_proj_layout, sp.halo_zx, m.d_in_proj, batch * hw, cfg->d_model,
+			m.d_in_proj, stream);
+		if (rc) return rc;
+		rc = b200_causal_conv1d_tokens(dtype, sp.halo_zx + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, sp.halo_y /* unused */,
+			m.conv_dim, nullptr, sp.halo_cs, batch, hw, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+		if (rc) return rc;
+		conv_in = sp.halo_cs;
+	}
+	rc = b200_linear(dtype, u_seg, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model, m.d_in_proj,
+		stream);
+	if (rc) return rc;
+	const char* dtp = ws.zxbcdt + (d_inner + m.conv_dim) * e;
+	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim, conv_in,
+		conv_state_out, batch, seglen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
+	if (rc) return rc;
+	rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
+		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, nullptr, ws.y, d_inner, seg_state, batch, seglen, cfg->nheads, cfg->headdim,
+		cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream,
+		kSsdStageDt | kSsdStageStates | kSsdStageSummary);
+	if (rc) return rc;
+	return ssd_segment_logdecay_of(seg_logdecay, batch, seglen, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, ws.ssd, st);
+}
+
+extern "C" int b200_ssm_segment_prefix(const float* seg_states, const float* seg_logdecay, int nseg, int64_t batch, int64_t H, int64_t P,
+	int64_t N, float* state_in, void* stream)
+{
+	if (!state_in || (nseg > 0 && (!seg_states || !seg_logdecay))) return B200_ERR_NULL;
+	if (nseg < 0 || batch < 0 || H <= 0 || P <= 0 || N <= 0) return B200_ERR_BAD_SHAPE;
+	if (batch == 0) return B200_OK;
+	return ssd_segment_prefix(seg_states, seg_logdecay, nseg, batch, H, P, N, state_in, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_mamba2_mixer_prefill_sp_finish(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w, void* out_seg,
+	int64_t batch, int64_t seglen, const float* state_in, float* ssm_state_out, void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !out_seg) return B200_ERR_NULL;
+	if (!w->A_log || !w->D || !w->dt_bias || !w->norm_weight || !w->out_proj_weight) return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || batch <= 0 || seglen <= 0) return B200_ERR_BAD_SHAPE;
+	if (!workspace) return B200_ERR_WORKSPACE;
+	if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+	const SpWs sp = carve_sp(workspace, cfg, m, batch, seglen);
+	if (workspace_bytes < sp.bytes) return B200_ERR_WORKSPACE;
+	const PrefillWs ws = carve_prefill(sp.inner, cfg, m, batch, seglen);
+	const int64_t T = batch * seglen, d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
+	const size_t e = m.esz;
+	const char* dtp = ws.zxbcdt + (d_inner + m.conv_dim) * e;
+	int rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
+		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, state_in, ws.y, d_inner, ssm_state_out, batch, seglen, cfg->nheads,
+		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream, kSsdStagePass);
+	if (rc) return rc;
+	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner, cfg->norm_group_size,
+		cfg->eps, stream);
+	if (rc) return rc;
+	return b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out_seg, cfg->d_model, T, d_inner, cfg->d_model, stream);
 }
 
 // ---- Zamba2 Mamba decoder layer around the mixer: out = hidden + mixer(rms_norm(hidden) * input_norm_weight) -------------

@@ -3,9 +3,11 @@
 
 namespace b200 {
 
-// The scan in two parts: kSsdStageDt (softplus, in-chunk cumulative sums: needs dt only; the prefill mixer runs it inside its
-// conv1d launch) and kSsdStageScan (chunk states, state passing, chunk scan: needs x, B, C and the first part's results).
-constexpr int kSsdStageDt = 1, kSsdStageScan = 2;
+// The scan in parts. kSsdStageDt: softplus and in-chunk cumulative sums (needs dt only; the prefill mixer runs it inside its
+// conv1d launch). kSsdStageStates: per-chunk states from x and B. kSsdStageSummary: the segment's state for a zero incoming
+// state (written to `fin`) without touching the chunk states: what a GPU that holds one segment of a sequence sends on.
+// kSsdStagePass: state passing from `init` and the chunk scan. A plain call runs Dt | States | Pass.
+constexpr int kSsdStageDt = 1, kSsdStageStates = 2, kSsdStagePass = 4, kSsdStageSummary = 8;
 
 template <typename T>
 static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, const float* A, int a_is_log, const void* Bm, int64_t bs,
@@ -14,9 +16,11 @@ static int run_simt(const void* x, int64_t xs, const void* dt, int64_t dts, cons
 {
 	int rc = B200_OK;
 	if (stages & kSsdStageDt) rc = ssd_dt_cumsum<T>(static_cast<const T*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
-	if (rc || !(stages & kSsdStageScan)) return rc;
-	rc = ssd_chunk_state_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, d, w, st);
 	if (rc) return rc;
+	if (stages & kSsdStageStates) rc = ssd_chunk_state_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, d, w, st);
+	if (rc) return rc;
+	if (stages & kSsdStageSummary) rc = ssd_state_passing(nullptr, fin, false, d, w, st, false);
+	if (rc || !(stages & kSsdStagePass)) return rc;
 	rc = ssd_state_passing(init, fin, false, d, w, st);
 	if (rc) return rc;
 	return ssd_chunk_scan_simt<T>(static_cast<const T*>(x), xs, static_cast<const T*>(Bm), bs, static_cast<const T*>(Cm), cs, D,
@@ -33,9 +37,11 @@ static int run_tc(const void* x, int64_t xs, const void* dt, int64_t dts, const 
 	const __half* ch = static_cast<const __half*>(Cm);
 	int rc = B200_OK;
 	if (stages & kSsdStageDt) rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
-	if (rc || !(stages & kSsdStageScan)) return rc;
-	rc = ssd_chunk_state_tc(xh, xs, bh, bs, d, w, st);
 	if (rc) return rc;
+	if (stages & kSsdStageStates) rc = ssd_chunk_state_tc(xh, xs, bh, bs, d, w, st);
+	if (rc) return rc;
+	if (stages & kSsdStageSummary) rc = ssd_state_passing(nullptr, fin, true, d, w, st, false);
+	if (rc || !(stages & kSsdStagePass)) return rc;
 	rc = ssd_state_passing(init, fin, true, d, w, st);
 	if (rc) return rc;
 	return ssd_chunk_scan_tc(xh, xs, bh, bs, ch, cs, D, static_cast<__half*>(y), ys, d, w, st);
@@ -87,6 +93,14 @@ int ssd_combined_stages(int dtype, const void* x, int64_t x_stride, const void* 
 	return run_simt<float>(x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
 		y_stride, final_states, d, w, st, dt_softplus, stages);
 }
+
+int ssd_segment_logdecay_of(float* out, int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk,
+	void* workspace, cudaStream_t st)
+{
+	const SsdDims d{ batch, seqlen, static_cast<int>(H), static_cast<int>(P), static_cast<int>(G), static_cast<int>(N),
+		static_cast<int>(chunk), static_cast<int>(cdiv(seqlen, chunk)) };
+	return ssd_segment_logdecay(out, d, ssd_carve(workspace, d), st);
+}
 }  // namespace b200
 
 extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t x_stride, const void* dt, int64_t dt_stride,
@@ -98,5 +112,5 @@ extern "C" int b200_mamba_chunk_scan_combined(int dtype, const void* x, int64_t 
 {
 	return ssd_combined_stages(dtype, x, x_stride, dt, dt_stride, A, a_is_log, B, B_stride, C, C_stride, D, dt_bias, initial_states, y,
 		y_stride, final_states, batch, seqlen, H, P, G, N, chunk, dt_softplus, workspace, workspace_bytes, stream,
-		kSsdStageDt | kSsdStageScan);
+		kSsdStageDt | kSsdStageStates | kSsdStagePass);
 }

@@ -60,7 +60,9 @@ int ssd_chunk_state_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const 
 
 // write_prev16: also store the f16 copy of the state before each chunk (needed by the tensor-core chunk scan).
 int ssd_state_passing(const float* initial_states, float* final_states, bool write_prev16, const SsdDims& d, const SsdWorkspace& w,
-	cudaStream_t st);
+	cudaStream_t st, bool write_prev = true);
+// log of the total decay of the segment per (batch, head), from the dt stage's results
+int ssd_segment_logdecay(float* out, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
 
 // Tensor-core stages (f16 activations; shapes accepted by ssd_tc_supported).
 bool ssd_tc_supported(const SsdDims& d, const void* x, int64_t xs, const void* Bm, int64_t bs, const void* Cm, int64_t cs, const void* y,

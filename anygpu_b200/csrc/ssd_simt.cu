@@ -116,7 +116,7 @@ constexpr int kSpBatch = 8;
 
 __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restrict__ states, __half* __restrict__ prev16,
 	const float* __restrict__ dacs, const float* init, float* fin /* may alias init: every thread reads its slice first */, int H, int PN,
-	int Q, int nchunks)
+	int Q, int nchunks, int write_prev /* 0: only `fin` is produced, the chunk states stay as they are */)
 {
 	const int i = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
 	if (i >= PN) return;
@@ -146,8 +146,8 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restric
 			if (c0 + j < nchunks)
 			{
 				// the state before chunk c replaces the chunk's own state: in fp32 for the SIMT scan, as f16 for the tensor-core scan
-				if (pp == nullptr) *reinterpret_cast<float4*>(sp + (c0 + j) * cstride) = s;
-				if (pp)
+				if (write_prev && pp == nullptr) *reinterpret_cast<float4*>(sp + (c0 + j) * cstride) = s;
+				if (write_prev && pp)
 				{
 					__half2* q = reinterpret_cast<__half2*>(pp + (c0 + j) * cstride);
 					q[0] = __floats2half2_rn(s.x, s.y);
@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(256) ssd_state_passing_kernel(float* __restric
 }
 
 int ssd_state_passing(const float* initial_states, float* final_states, bool write_prev16, const SsdDims& d, const SsdWorkspace& w,
-	cudaStream_t st)
+	cudaStream_t st, bool write_prev)
 {
 	const int PN = d.P * d.N;
 	if (PN % 4 != 0 || (initial_states && !aligned16(initial_states)) || (final_states && !aligned16(final_states)))
@@ -173,9 +173,43 @@ int ssd_state_passing(const float* initial_states, float* final_states, bool wri
 	const dim3 g(static_cast<unsigned>(cdiv(PN / 4, 256)), static_cast<unsigned>(d.H), static_cast<unsigned>(d.batch));
 	if (g.z > 65535u || g.y > 65535u) return B200_ERR_UNSUPPORTED;
 	ssd_state_passing_kernel<<<g, 256, 0, st>>>(w.states, write_prev16 ? w.prev16 : nullptr, w.dacs, initial_states, final_states, d.H,
-		PN, d.Q, d.nchunks);
+		PN, d.Q, d.nchunks, write_prev ? 1 : 0);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
+}
+
+// Sum over the chunks of a segment of the per-chunk total of dt*A, per (batch, head): the log of the factor by which the segment
+// decays a state that enters it (used when a sequence is split over GPUs).
+__global__ void __launch_bounds__(256) ssd_segment_logdecay_kernel(const float* __restrict__ dacs, float* __restrict__ out, int64_t bh,
+	int Q, int nchunks)
+{
+	const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= bh) return;
+	const float* p = dacs + i * static_cast<int64_t>(nchunks) * Q + (Q - 1);
+	float s = 0.f;
+	for (int c = 0; c < nchunks; ++c) s += p[static_cast<int64_t>(c) * Q];
+	out[i] = s;
+}
+
+int ssd_segment_logdecay(float* out, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	const int64_t bh = d.batch * d.H;
+	ssd_segment_logdecay_kernel<<<static_cast<unsigned>(cdiv(bh, 256)), 256, 0, st>>>(w.dacs, out, bh, d.Q, d.nchunks);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+// state_in = state entering segment `nseg` of a sequence split into segments: h <- exp(logdecay_q) * h + seg_state_q for
+// q = 0 .. nseg-1, from the per-segment results of zero-state passes (seg_states [nseg, b*H*P*N], seg_logdecay [nseg, b*H]).
+__global__ void __launch_bounds__(256) ssd_segment_prefix_kernel(const float* __restrict__ seg_states, const float* __restrict__ seg_logdecay,
+	int nseg, int64_t total, int64_t bh, int PN, float* __restrict__ state_in)
+{
+	const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+	if (i >= total) return;
+	const int64_t ibh = i / PN;
+	float h = 0.f;
+	for (int q = 0; q < nseg; ++q) h = h * __expf(seg_logdecay[q * bh + ibh]) + seg_states[q * total + i];
+	state_in[i] = h;
 }
 
 // ---- stage 4 (SIMT): chunk scan -----------------------------------------------------------------------------
@@ -343,5 +377,16 @@ int ssd_chunk_scan_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const T
 }
 template int ssd_chunk_scan_simt<__half>(const __half*, int64_t, const __half*, int64_t, const __half*, int64_t, const float*, __half*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
 template int ssd_chunk_scan_simt<float>(const float*, int64_t, const float*, int64_t, const float*, int64_t, const float*, float*, int64_t, const SsdDims&, const SsdWorkspace&, cudaStream_t);
+
+int ssd_segment_prefix(const float* seg_states, const float* seg_logdecay, int nseg, int64_t batch, int64_t H, int64_t P, int64_t N,
+	float* state_in, cudaStream_t st)
+{
+	const int64_t total = batch * H * P * N;
+	if (P * N > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
+	ssd_segment_prefix_kernel<<<static_cast<unsigned>(cdiv(total, 256)), 256, 0, st>>>(seg_states, seg_logdecay, nseg, total, batch * H,
+		static_cast<int>(P * N), state_in);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
 
 }  // namespace b200

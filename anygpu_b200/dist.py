@@ -34,3 +34,12 @@ def sum_over_ranks(value, device="cpu"):
 def job_throughput(units_this_rank, seconds_this_rank, device="cpu"):
     """Whole-job throughput: units processed by all ranks divided by the slowest rank's time."""
     return sum_over_ranks(units_this_rank, device) / max_over_ranks(seconds_this_rank, device)
+
+
+def sp_segments(seqlen, world, align=1):
+    """Consecutive token ranges [start, end) of a sequence split over `world` ranks for sequence-parallel prefill: as even as
+    possible, every boundary but the last a multiple of `align` (segments need not be multiples of the scan chunk, but aligned
+    ones avoid a padded chunk at every boundary). Ranks past the end of a short sequence get empty ranges."""
+    per = -(-seqlen // world)
+    per = -(-per // align) * align
+    return [(min(r * per, seqlen), min((r + 1) * per, seqlen)) for r in range(world)]

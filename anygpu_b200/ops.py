@@ -332,6 +332,53 @@ class Mamba2DecoderLayer:
         return out
 
 
+class Mamba2MixerSP:
+    """One rank of a sequence-parallel prefill: the rank holds one segment of every sequence. `begin` -> exchange (the caller
+    all-gathers the two small tensors it returns) -> `prefix` -> `finish`."""
+
+    def __init__(self, cfg, weights):
+        self.cfg, self.w = cfg, weights
+        self.c_cfg, self.c_w = make_config(cfg), weights.c_struct()
+        self.dtype, self.device = weights.in_proj_weight.dtype, weights.in_proj_weight.device
+        self._ws = None
+        self._shape = None
+
+    def begin(self, u_seg, u_halo=None, cache=None):
+        """u_seg (b, seglen, d_model); u_halo (b, d_conv-1, d_model): the tokens just before the segment (None for the first
+        segment). Returns (seg_state (b,H,P,N) fp32, seg_logdecay (b,H) fp32); cache.conv_state receives the segment's last
+        conv inputs when a cache is given."""
+        b, l, _ = u_seg.shape
+        assert u_seg.is_contiguous() and u_seg.dtype == self.dtype and (u_halo is None or u_halo.is_contiguous())
+        lib = capi.load()
+        nbytes = lib.b200_mamba2_mixer_prefill_sp_workspace_bytes(ctypes.byref(self.c_cfg), _DT[self.dtype], b, l)
+        if self._ws is None or self._ws.numel() < nbytes:
+            self._ws = _workspace(nbytes, self.device)
+        self._shape = (b, l)
+        c = self.cfg
+        seg_state = torch.empty((b, c["nheads"], c["headdim"], c["d_state"]), dtype=torch.float32, device=self.device)
+        seg_logdecay = torch.empty((b, c["nheads"]), dtype=torch.float32, device=self.device)
+        capi.call("b200_mamba2_mixer_prefill_sp_begin", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w), _p(u_seg),
+                  _p(u_halo), b, l, _p(seg_state), _p(seg_logdecay), _p(cache.conv_state) if cache else None, _p(self._ws),
+                  self._ws.numel(), _stream())
+        return seg_state, seg_logdecay
+
+    def prefix(self, seg_states, seg_logdecay, rank):
+        """State entering segment `rank` from the gathered per-segment results (R,b,H,P,N) and (R,b,H)."""
+        R, b, H, P, N = seg_states.shape
+        assert seg_states.is_contiguous() and seg_logdecay.is_contiguous() and seg_states.dtype == torch.float32
+        state_in = torch.empty((b, H, P, N), dtype=torch.float32, device=seg_states.device)
+        capi.call("b200_ssm_segment_prefix", _p(seg_states), _p(seg_logdecay), int(rank), b, H, P, N, _p(state_in), _stream())
+        return state_in
+
+    def finish(self, state_in, out=None, cache=None):
+        b, l = self._shape
+        if out is None:
+            out = torch.empty((b, l, self.cfg["d_model"]), dtype=self.dtype, device=self.device)
+        capi.call("b200_mamba2_mixer_prefill_sp_finish", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w), _p(out), b, l,
+                  _p(state_in), _p(cache.ssm_state) if cache else None, _p(self._ws), self._ws.numel(), _stream())
+        return out
+
+
 class Mamba2MixerTP:
     """One rank of the head-sharded (tensor-parallel) prefill mixer. `cfg_local` / `weights` are the rank's local sizes and
     slices (anygpu_b200.synth.tp_local_config / shard_weights_tp). `partial` runs everything up to the rank's out_proj addend;

@@ -333,6 +333,77 @@ def run_gpu(args):
 # head-sharded tensor parallelism (cfg4): every rank holds the whole batch and 1/N of the heads
 # ---------------------------------------------------------------------------------------------------------------
 
+def run_sp(args):
+    """`--mode sp` under torchrun with N ranks: ONE long sequence per batch entry (cfg2 layer sizes, `--sp-seqlen` tokens) split
+    into N consecutive segments. Per step: local in_proj / conv1d / chunk states -> all-gather of the zero-state segment states
+    [b,H,P,N] and log-decays [b,H] (NCCL) -> incoming state -> state passing, chunk scan, gated norm, out_proj. Strong scaling:
+    the sequence is fixed."""
+    import torch
+    import torch.distributed as dist
+    from anygpu_b200 import capi, ops
+    from anygpu_b200 import dist as bdist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = capi.load()
+    cfg = dict(synth.CONFIGS["cfg2"], batch=args.sp_batch, seqlen=args.sp_seqlen)
+    b, l = cfg["batch"], cfg["seqlen"]
+    wts = ops.ZambaMamba2weights.from_numpy(synth.make_weights(cfg, 0), torch.float16)
+    lo, hi = bdist.sp_segments(l, world, align=cfg["chunk"])[rank]
+    g = torch.Generator(device="cuda").manual_seed(0)  # same sequence on every rank; each uses its segment (+ 3 halo tokens)
+    u = torch.randn(b, l, cfg["d_model"], device="cuda", generator=g).half()
+    u_seg = u[:, lo:hi].contiguous()
+    halo = u[:, lo - 3:lo].contiguous() if rank > 0 else None
+    del u
+    mixer = ops.Mamba2MixerSP(cfg, wts)
+    out = torch.empty_like(u_seg)
+    H, P, N = cfg["nheads"], cfg["headdim"], cfg["d_state"]
+    states = torch.empty((world, b, H, P, N), dtype=torch.float32, device="cuda")
+    decays = torch.empty((world, b, H), dtype=torch.float32, device="cuda")
+
+    def step():
+        s_, d_ = mixer.begin(u_seg, halo)
+        if world > 1:
+            dist.all_gather_into_tensor(states, s_)
+            dist.all_gather_into_tensor(decays, d_)
+        else:
+            states[0].copy_(s_)
+            decays[0].copy_(d_)
+        mixer.finish(mixer.prefix(states, decays, rank), out=out)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms = bdist.max_over_ranks(e0.elapsed_time(e1), device="cuda")
+    capi.check("b200_last_device_error", lib.b200_last_device_error(None, None))
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": b * l * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                          "config": {"workload": f"cfg2 layer sizes, batch {b} x ONE sequence of {l} tokens split into {world} segments",
+                                     "global_batch": b, "seq_len": l,
+                                     "parallelism": f"sp{world}: sequence-parallel, NCCL all-gather of segment states "
+                                                    f"({b * H * P * N * 4 / 1e6:.1f} MB per rank) and log-decays"}}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_tp(args):
     """`--mode tp` under torchrun with N ranks: the Zamba2-7B-shaped layer with nheads/N heads per rank. Per chunk of sequences:
     local mixer up to the out_proj addend -> NCCL all-reduce (sum) of the addends and of the per-token sums of squares ->
@@ -544,7 +615,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="dp", choices=["dp", "tp"], help="dp: batch-sharded (default); tp: head-sharded cfg4 layer")
+    ap.add_argument("--mode", default="dp", choices=["dp", "tp", "sp"],
+                    help="dp: batch-sharded (default); tp: head-sharded cfg4 layer; sp: one long sequence split over the ranks")
+    ap.add_argument("--sp-seqlen", type=int, default=32768)
+    ap.add_argument("--sp-batch", type=int, default=1)
     ap.add_argument("--tp-batch", type=int, default=32)
     ap.add_argument("--tp-chunk", type=int, default=4)
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
@@ -557,6 +631,8 @@ def main():
         return run_kernel(args)
     if args.mode == "tp" and args.impl == "b200":
         return run_tp(args)
+    if args.mode == "sp" and args.impl == "b200":
+        return run_sp(args)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     if args.impl == "reference":
         run_reference(args)

@@ -242,6 +242,24 @@ int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_config* cfg,
 	const void* u, void* out, int64_t batch, int64_t seqlen, void* conv_state, float* ssm_state,
 	void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- sequence-parallel prefill: a long sequence split into consecutive segments, one per GPU ---------------------
+ * No counterpart in anyGPU. The caller owns the communication; per segment (rank) r of R:
+ *   1. _sp_begin(u_seg, u_halo = the d_conv-1 tokens before the segment, NULL for r = 0)   -> seg_state [b,H,P,N] fp32: the state the
+ *      segment hands on for a ZERO incoming state; seg_logdecay [b,H] fp32: log of the factor by which it decays an incoming state
+ *   2. all-gather seg_state and seg_logdecay over the ranks (two small tensors)
+ *   3. b200_ssm_segment_prefix(gathered, nseg = r) -> state_in [b,H,P,N]: h <- exp(logdecay_q) h + seg_state_q for q < r
+ *   4. _sp_finish(state_in)  -> out_seg [b, seglen, d_model]; ssm_state_out (optional) is the true state after the segment
+ * The workspace of _sp_begin must reach _sp_finish unchanged. Segment lengths are free (they need not be multiples of the
+ * chunk). The concatenated out_seg equal b200_mamba2_mixer_prefill over the whole sequence. */
+size_t b200_mamba2_mixer_prefill_sp_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seglen);
+int b200_mamba2_mixer_prefill_sp_begin(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_seg, const void* u_halo, int64_t batch, int64_t seglen, float* seg_state, float* seg_logdecay, void* conv_state_out,
+	void* workspace, size_t workspace_bytes, void* stream);
+int b200_ssm_segment_prefix(const float* seg_states, const float* seg_logdecay, int nseg, int64_t batch, int64_t H, int64_t P,
+	int64_t N, float* state_in, void* stream);
+int b200_mamba2_mixer_prefill_sp_finish(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w, void* out_seg,
+	int64_t batch, int64_t seglen, const float* state_in, float* ssm_state_out, void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- Zamba2 Mamba decoder layer: the mixer with its input norm and residual -----------------------------------
  * out = hidden + mixer(rms_norm(hidden, input_norm_weight, rms_eps)). No counterpart in anyGPU yet; the structure (input
  * RMSNorm, block, residual stream) is that of its hybrid block's other half, tensor_zamba_attention_decoder

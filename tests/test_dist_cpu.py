@@ -59,3 +59,13 @@ def test_shard_bounds_properties():
 def test_single_process_is_identity():
     assert bdist.max_over_ranks(3.25) == 3.25
     assert bdist.job_throughput(10, 2.0) == 5.0
+
+
+def test_sequence_parallel_segment_bounds():
+    from anygpu_b200.dist import sp_segments
+    assert sp_segments(4096, 4) == [(0, 1024), (1024, 2048), (2048, 3072), (3072, 4096)]
+    assert sp_segments(1000, 4, align=256) == [(0, 256), (256, 512), (512, 768), (768, 1000)]
+    assert sp_segments(300, 4, align=256) == [(0, 256), (256, 300), (300, 300), (300, 300)]
+    for seqlen, world, align in [(777, 3, 1), (4097, 8, 256), (5, 8, 1)]:
+        segs = sp_segments(seqlen, world, align)
+        assert segs[0][0] == 0 and segs[-1][1] == seqlen and all(a[1] == b[0] for a, b in zip(segs, segs[1:]))

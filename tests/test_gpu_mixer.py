@@ -256,3 +256,44 @@ def test_prefill_in_pieces_equals_one_prefill(ops, pieces):
     d1 = mixer.decode(ud[:, 512].contiguous(), cache)
     d2 = mixer.decode(ud[:, 512].contiguous(), whole_cache)
     assert rel_l2(host(d1), host(d2)) < 3e-3
+
+
+@pytest.mark.parametrize("bounds", [[0, 128, 256, 384, 512], [0, 100, 101, 300, 512], [0, 512]])
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_sequence_parallel_segments_emulated_on_one_gpu(ops, bounds, dtype):
+    """Sequence parallelism without a second GPU: the segments run one after the other on this device, the gathered
+    per-segment states are what the all-gather would deliver. Outputs and final states must equal one prefill of the whole
+    sequence (any segment lengths, aligned to the chunk or not)."""
+    cfg = dict(SMALL, batch=2, seqlen=512, chunk=128)
+    td = torch.float16 if dtype == "f16" else torch.float32
+    w = synth.make_weights(cfg, 11)
+    u = synth.make_input(cfg, 11)
+    if dtype == "f16":
+        w, u = f16w(w), synth.to_f16_values(u)
+    wt = ops.ZambaMamba2weights.from_numpy(w, td)
+    ud = torch.from_numpy(u).cuda().to(td)
+    whole_cache = ops.ZambaMambaCache.zeros(cfg, 2, td)
+    whole = ops.Mamba2Mixer(cfg, wt).prefill(ud, whole_cache)
+    R = len(bounds) - 1
+    ranks = [ops.Mamba2MixerSP(cfg, wt) for _ in range(R)]
+    caches = [ops.ZambaMambaCache.zeros(cfg, 2, td) for _ in range(R)]
+    states, decays = [], []
+    for r in range(R):
+        lo, hi = bounds[r], bounds[r + 1]
+        halo = ud[:, lo - 3:lo].contiguous() if r > 0 else None
+        s_, d_ = ranks[r].begin(ud[:, lo:hi].contiguous(), halo, caches[r])
+        states.append(s_)
+        decays.append(d_)
+    gs, gd = torch.stack(states).contiguous(), torch.stack(decays).contiguous()  # what the all-gather delivers
+    outs = [ranks[r].finish(ranks[r].prefix(gs, gd, r), cache=caches[r]) for r in range(R)]
+    got = torch.cat(outs, dim=1)
+    if dtype == "f16":
+        want = orc.mixer_prefill(u, w, dict(cfg, chunk=8), f16io=True)
+        assert_close_f16(host(got), want["out"], "segments vs oracle", max_fail_fraction=1e-3)
+        assert rel_l2(host(got), host(whole)) < 2e-3
+        assert_close_f16(host(caches[-1].ssm_state), want["final_state"], "final state on the last rank", max_fail_fraction=1e-4)
+    else:
+        want = orc.mixer_prefill(u, w, dict(cfg, chunk=8))
+        assert_abs(host(got), want["out"], "segments vs oracle", 1e-3)
+        assert_abs(host(caches[-1].ssm_state), want["final_state"], "final state on the last rank", 1e-4)
+    assert torch.equal(caches[-1].conv_state, whole_cache.conv_state)
