@@ -286,7 +286,7 @@ def run_gpu(args):
     per_stage = [stage_ms[j] / max(calls.value, 1) for j in range(5)]
     flops_in = 2.0 * tokens * cfg["d_model"] * d_in_proj
     dom = int(np.argmax(per_stage))
-    roofline = {"kernel": "gemm_f16_tcgen05_kernel (in_proj)", "bound": "tensor",
+    roofline = {"kernel": "gemm_f16_tcgen05_pair_kernel (in_proj)", "bound": "tensor",
                 "achieved": flops_in / (per_stage[0] * 1e-3) / 1e12 if per_stage[0] > 0 else None,
                 "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
                 # DRAM bytes per launch: the ncu capture of the M=2048 case (profiles/gemm_f16_tcgen05_in_proj_small.md) read exactly
