@@ -289,7 +289,7 @@ def run_gpu(args):
     roofline = {"kernel": "gemm_f16_tcgen05_pair_kernel (in_proj)", "bound": "tensor",
                 "achieved": flops_in / (per_stage[0] * 1e-3) / 1e12 if per_stage[0] > 0 else None,
                 "peak": peaks["tflops_sustained"], "unit": "TFLOP/s",
-                # DRAM bytes per launch: the ncu capture of the M=2048 case (profiles/gemm_f16_tcgen05_in_proj_small.md) read exactly
+                # DRAM bytes per launch: the ncu capture of the M=2048 case read exactly
                 # the operand bytes once (X + W); scaled to this launch that is X + W read and Y written = the algorithmic bytes
                 "traffic": float(tokens * cfg["d_model"] * 2 + cfg["d_model"] * d_in_proj * 2 + tokens * d_in_proj * 2),
                 "traffic_note": "scaled from the ncu capture of the M=2048 case: operands read once from DRAM, output written once",

@@ -1,6 +1,6 @@
 """Generates the golden vectors under tests/golden/ from the anyGPU reference itself.
 
-Run once in a container that has the anyGPU checkout (default /root/reference, or $ANYGPU_REF):
+Run once in a container that has the anyGPU checkout (its location: $ANYGPU_REF, see REF below):
 
     python tests/golden/make_golden.py
 
