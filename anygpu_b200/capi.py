@@ -70,6 +70,9 @@ SIGNATURES = {
     "b200_mamba2_mixer_prefill_continue_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
     "b200_mamba2_mixer_prefill_continue": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _i64,
                                                   _i64, _vp, _vp, _vp, _sz, _vp]),
+    "b200_mamba2_mixer_prefill_varlen_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64]),
+    "b200_mamba2_mixer_prefill_varlen": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp,
+                                                ctypes.POINTER(ctypes.c_int64), _i64, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200_mamba2_mixer_prefill_sp_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
     "b200_mamba2_mixer_prefill_sp_begin": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _i64, _i64,
                                                   _vp, _vp, _vp, _vp, _sz, _vp]),

@@ -160,6 +160,33 @@ extern "C" size_t b200_mamba2_mixer_prefill_workspace_bytes(const b200_mamba2_co
 	return carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
 }
 
+// The stages between the two projections for `batch` sequences of `seqlen` tokens whose projected rows start at `zxbcdt`:
+// conv1d + SiLU over the xBC columns (with the scan's dt stage in the same launch where that applies), then the chunked scan.
+static int mixer_conv_ssd(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w, const MixerDims& m, const char* zxbcdt,
+	char* xbc, char* y, char* ssd, size_t ssd_bytes, int64_t batch, int64_t seqlen, const float* initial_states, const void* conv_state_in,
+	void* conv_state_out, float* ssm_state_out, cudaStream_t st, bool mark)
+{
+	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
+	const size_t e = m.esz;
+	const char* dtp = zxbcdt + (d_inner + m.conv_dim) * e;
+	const bool dt_in_conv = conv_dt_fused_applies(dtype, zxbcdt + d_inner * e, m.d_in_proj, xbc, m.conv_dim, batch, seqlen, m.conv_dim,
+		static_cast<int>(cfg->d_conv)) && cfg->chunk <= 256 && batch * cdiv(seqlen, cfg->chunk) * cfg->nheads <= 0x7fffffffLL;
+	int rc;
+	if (dt_in_conv)
+		rc = conv1d_tokens_with_scan_dt(dtype, zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, xbc, m.conv_dim,
+			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), dtp, m.d_in_proj, w->A_log, 1, w->dt_bias,
+			B200_DT_SOFTPLUS_EXACT, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, ssd, ssd_bytes, st);
+	else
+		rc = b200_causal_conv1d_tokens(dtype, zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, xbc, m.conv_dim,
+			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), st);
+	if (rc) return rc;
+	if (mark) stage_mark(2, st);
+	return ssd_combined_stages(dtype, xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, xbc + d_inner * e, m.conv_dim,
+		xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, y, d_inner, ssm_state_out, batch, seqlen, cfg->nheads,
+		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ssd, ssd_bytes, st,
+		(dt_in_conv ? 0 : kSsdStageDt) | kSsdStageStates | kSsdStagePass);
+}
+
 // The prefill mixer; `residual` [T, >= d_model] (or nullptr) is added to the result (may alias `out`).
 static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u, void* out, int64_t batch, int64_t seqlen,
@@ -179,30 +206,15 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 	if (workspace_bytes < ws.bytes) return B200_ERR_WORKSPACE;
 
 	const int64_t T = batch * seqlen;
-	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
-	const size_t e = m.esz;
+	const int64_t d_inner = cfg->d_inner;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	stage_mark(0, st);
 	int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model,
 		m.d_in_proj, stream);
 	if (rc) return rc;
 	stage_mark(1, st);
-	const char* dtp = ws.zxbcdt + (d_inner + m.conv_dim) * e;
-	const bool dt_in_conv = conv_dt_fused_applies(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, ws.xbc, m.conv_dim, batch, seqlen, m.conv_dim,
-		static_cast<int>(cfg->d_conv)) && cfg->chunk <= 256 && batch * cdiv(seqlen, cfg->chunk) * cfg->nheads <= 0x7fffffffLL;
-	if (dt_in_conv)
-		rc = conv1d_tokens_with_scan_dt(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
-			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), dtp, m.d_in_proj, w->A_log, 1, w->dt_bias,
-			B200_DT_SOFTPLUS_EXACT, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, ws.ssd, ws.ssd_bytes, st);
-	else
-		rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim,
-			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
-	if (rc) return rc;
-	stage_mark(2, st);
-	rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
-		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, ws.y, d_inner, ssm_state_out, batch, seqlen, cfg->nheads,
-		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream,
-		(dt_in_conv ? 0 : kSsdStageDt) | kSsdStageStates | kSsdStagePass);
+	rc = mixer_conv_ssd(dtype, cfg, w, m, ws.zxbcdt, ws.xbc, ws.y, ws.ssd, ws.ssd_bytes, batch, seqlen, initial_states, conv_state_in,
+		conv_state_out, ssm_state_out, st, true);
 	if (rc) return rc;
 	stage_mark(3, st);
 	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,
@@ -588,6 +600,77 @@ extern "C" int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_c
 	if (rc) return rc;
 	if (cs_bytes) B200_CUDA_TRY(cudaMemcpyAsync(conv_state, next_cs, cs_bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
 	return B200_OK;
+}
+
+// ---- packed variable-length batches ------------------------------------------------------------------------------------------
+// `nseq` sequences of different lengths stored back to back on the token axis: rows cu_seqlens[s] .. cu_seqlens[s+1]-1 of
+// u / out belong to sequence s (cu_seqlens is a HOST array of nseq+1 non-decreasing offsets starting at 0, the convention of
+// the `cu_seqlens` argument that scripts/zamba2/mamba_chunk_scan_comb.py:164-166 leaves unsupported). Both projections and the
+// gated norm run once over all tokens; the conv1d and the scan, the two stages that look across tokens, run per sequence on
+// its rows, so no padding is computed and nothing leaks across a boundary. An empty sequence leaves its initial state (or
+// zeros) as its final state.
+extern "C" size_t b200_mamba2_mixer_prefill_varlen_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t total_tokens)
+{
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || total_tokens <= 0) return 0;
+	return carve_prefill(nullptr, cfg, m, 1, total_tokens).bytes;
+}
+
+extern "C" int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, const int64_t* cu_seqlens, int64_t nseq,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	if (!cfg || !w || !cu_seqlens) return B200_ERR_NULL;
+	if (!w->in_proj_weight || !w->conv1d_weight || !w->conv1d_bias || !w->dt_bias || !w->A_log || !w->D || !w->norm_weight ||
+		!w->out_proj_weight)
+		return B200_ERR_NULL;
+	MixerDims m;
+	if (!dims_ok(cfg, dtype, &m) || nseq < 0 || cu_seqlens[0] != 0) return B200_ERR_BAD_SHAPE;
+	for (int64_t s = 0; s < nseq; ++s)
+		if (cu_seqlens[s + 1] < cu_seqlens[s]) return B200_ERR_BAD_SHAPE;
+	const int64_t T = cu_seqlens[nseq];
+	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	const size_t e = m.esz;
+	const int64_t d_inner = cfg->d_inner;
+	const size_t state_elems = static_cast<size_t>(cfg->nheads) * cfg->headdim * cfg->d_state;
+	const size_t cs_bytes = static_cast<size_t>(m.conv_dim) * (cfg->d_conv - 1) * e;
+	PrefillWs ws{};
+	if (T > 0)
+	{
+		if (!u || !out) return B200_ERR_NULL;
+		if (!workspace) return B200_ERR_WORKSPACE;
+		if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
+		ws = carve_prefill(workspace, cfg, m, 1, T);
+		if (workspace_bytes < ws.bytes) return B200_ERR_WORKSPACE;
+		const int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model,
+			m.d_in_proj, stream);
+		if (rc) return rc;
+	}
+	for (int64_t s = 0; s < nseq; ++s)
+	{
+		const int64_t t0 = cu_seqlens[s], len = cu_seqlens[s + 1] - t0;
+		const float* init = initial_states ? initial_states + s * state_elems : nullptr;
+		float* fin = ssm_state_out ? ssm_state_out + s * state_elems : nullptr;
+		char* cs = conv_state_out ? static_cast<char*>(conv_state_out) + s * cs_bytes : nullptr;
+		if (len == 0)
+		{
+			if (fin && init && fin != init)
+				B200_CUDA_TRY(cudaMemcpyAsync(fin, init, state_elems * sizeof(float), cudaMemcpyDeviceToDevice, st));
+			else if (fin && !init)
+				B200_CUDA_TRY(cudaMemsetAsync(fin, 0, state_elems * sizeof(float), st));
+			if (cs && cs_bytes) B200_CUDA_TRY(cudaMemsetAsync(cs, 0, cs_bytes, st));
+			continue;
+		}
+		const int rc = mixer_conv_ssd(dtype, cfg, w, m, ws.zxbcdt + t0 * m.d_in_proj * e, ws.xbc + t0 * m.conv_dim * e,
+			ws.y + t0 * d_inner * e, ws.ssd, ws.ssd_bytes, 1, len, init, nullptr, cs, fin, st, false);
+		if (rc) return rc;
+	}
+	if (T == 0) return B200_OK;
+	int rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,
+		cfg->norm_group_size, cfg->eps, stream);
+	if (rc) return rc;
+	return b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out, cfg->d_model, T, d_inner, cfg->d_model, stream);
 }
 
 // ---- sequence-parallel prefill: one sequence split into segments, one segment per GPU ----------------------------------------

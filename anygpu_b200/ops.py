@@ -245,6 +245,24 @@ class Mamba2Mixer:
                   _p(out), b, l, _p(cache.conv_state), _p(cache.ssm_state), _p(ws), ws.numel(), _stream())
         return out
 
+    def prefill_varlen(self, u, cu_seqlens, initial_states=None, cache=None, out=None):
+        """Packed batch: `u` (total_tokens, d_model) holds len(cu_seqlens)-1 sequences back to back, sequence s in rows
+        cu_seqlens[s]:cu_seqlens[s+1] (host integers). `cache`, if given, has one entry per sequence and receives the final
+        states. Each sequence gets what prefill() gives for it alone."""
+        cu = [int(v) for v in cu_seqlens]
+        nseq = len(cu) - 1
+        total = cu[-1]
+        assert u.is_contiguous() and u.dtype == self.dtype and u.shape[0] == total
+        lib = capi.load()
+        ws = self._ensure_ws(max(1, lib.b200_mamba2_mixer_prefill_varlen_workspace_bytes(ctypes.byref(self.c_cfg), _DT[self.dtype], total)))
+        if out is None:
+            out = torch.empty_like(u)
+        cu_arr = (ctypes.c_int64 * (nseq + 1))(*cu)
+        capi.call("b200_mamba2_mixer_prefill_varlen", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w), _p(u), _p(out),
+                  cu_arr, nseq, _p(initial_states), _p(cache.conv_state) if cache else None, _p(cache.ssm_state) if cache else None,
+                  _p(ws), ws.numel(), _stream())
+        return out
+
     def prefill_host(self, u_host, out_host):
         """Same with HOST (pinned) tensors: H2D copy, mixer, D2H copy, all inside the one C-ABI call."""
         b, l, _ = u_host.shape

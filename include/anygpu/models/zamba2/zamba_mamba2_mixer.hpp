@@ -158,3 +158,28 @@ inline Tensor<dtype, CUDA> tensor_zamba_mamba2_mixer_continue(const ZambaMamba2w
 		cache.conv_state.buffer(), cache.ssm_state.buffer(), ws, ws_bytes, nullptr), "tensor_zamba_mamba2_mixer_continue");
 	return out;
 }
+
+// A packed batch: hidden_states (total_tokens, d_model) holds cu_seqlens.size()-1 sequences back to back, sequence s in rows
+// cu_seqlens[s] .. cu_seqlens[s+1]-1. `cache` (one entry per sequence) receives the final states. Every sequence gets what
+// tensor_zamba_mamba2_mixer gives for it alone.
+template <typename dtype>
+inline Tensor<dtype, CUDA> tensor_zamba_mamba2_mixer_varlen(const ZambaMamba2weights<dtype>& weights, ZambaMambaCache<dtype>& cache,
+	const Tensor<dtype, CUDA>& hidden_states, const std::vector<int64>& cu_seqlens, const ZambaMamba2Config& config)
+{
+	ACASSERT(hidden_states.dim == 2, "hidden_states is (total_tokens, d_model)");
+	ACASSERT(hidden_states.shape[1] == config.d_model, "hidden size does not match the config");
+	ACASSERT(!cu_seqlens.empty() && cu_seqlens.back() == hidden_states.shape[0], "cu_seqlens must end at the token count");
+	const int64 nseq = static_cast<int64>(cu_seqlens.size()) - 1;
+	ACASSERT(cache.conv_state.shape[0] == nseq && cache.ssm_state.shape[0] == nseq, "one cache entry per sequence");
+	const b200_mamba2_config cfg = config.c_struct();
+	const b200_mamba2_weights w = weights.c_struct();
+	const int dt = b200_dtype_of<dtype>();
+	Tensor<dtype, CUDA> out(hidden_states.dim, hidden_states.shape);
+	const size_t ws_bytes = b200_mamba2_mixer_prefill_varlen_workspace_bytes(&cfg, dt, hidden_states.shape[0]);
+	void* ws = b200_workspace(ws_bytes);
+	static_assert(sizeof(int64) == sizeof(int64_t), "cu_seqlens is passed as int64_t");
+	b200_check(b200_mamba2_mixer_prefill_varlen(dt, &cfg, &w, hidden_states.buffer(), out.buffer(),
+		reinterpret_cast<const int64_t*>(cu_seqlens.data()), nseq, nullptr, cache.conv_state.buffer(), cache.ssm_state.buffer(), ws, ws_bytes,
+		nullptr), "tensor_zamba_mamba2_mixer_varlen");
+	return out;
+}

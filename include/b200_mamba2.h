@@ -242,6 +242,18 @@ int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_config* cfg,
 	const void* u, void* out, int64_t batch, int64_t seqlen, void* conv_state, float* ssm_state,
 	void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- packed variable-length batches ---------------------------------------------------------------------------
+ * `nseq` sequences of different lengths stored back to back on the token axis: rows cu_seqlens[s] .. cu_seqlens[s+1]-1 of u and
+ * out [total_tokens, d_model] belong to sequence s. cu_seqlens is a HOST array of nseq+1 non-decreasing offsets that starts at 0
+ * (the `cu_seqlens` convention that scripts/zamba2/mamba_chunk_scan_comb.py:164-166 leaves unsupported). initial_states
+ * [nseq,H,P,N] fp32 or NULL; conv_state_out [nseq, conv_dim, d_conv-1] (dtype) and ssm_state_out [nseq,H,P,N] fp32 or NULL. Every
+ * sequence gets exactly what b200_mamba2_mixer_prefill gives for it alone; an empty sequence hands on its initial state. */
+size_t b200_mamba2_mixer_prefill_varlen_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t total_tokens);
+int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u, void* out, const int64_t* cu_seqlens, int64_t nseq,
+	const float* initial_states, void* conv_state_out, float* ssm_state_out,
+	void* workspace, size_t workspace_bytes, void* stream);
+
 /* ---- sequence-parallel prefill: a long sequence split into consecutive segments, one per GPU ---------------------
  * No counterpart in anyGPU. The caller owns the communication; per segment (rank) r of R:
  *   1. _sp_begin(u_seg, u_halo = the d_conv-1 tokens before the segment, NULL for r = 0)   -> seg_state [b,H,P,N] fp32: the state the

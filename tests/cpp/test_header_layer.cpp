@@ -282,6 +282,18 @@ static void test_mixer_f32_and_dat_files(const std::string& tmp_dir)
 		const std::vector<float> e1(e.begin(), e.begin() + 40 * cfg.d_model), e2(e.begin() + 40 * cfg.d_model, e.end());
 		report("tensor_zamba_mamba2_mixer_continue f32, first piece of the prompt", close_enough(o1, e1, 0.f, 1e-3f));
 		report("tensor_zamba_mamba2_mixer_continue f32, second piece of the prompt", close_enough(o2, e2, 0.f, 1e-3f));
+
+		// a packed batch of two sequences: the prompt and its first 40 tokens (causal: the same first 40 outputs)
+		std::vector<float32> packed(u.buffer(), u.buffer() + l * cfg.d_model);
+		packed.insert(packed.end(), u.buffer(), u.buffer() + 40 * cfg.d_model);
+		ZambaMambaCache<float32> vc(cfg, 2);
+		auto vo = tensor_zamba_mamba2_mixer_varlen(weights, vc, Tensor<float32, CPU>(std::vector<int64>{ l + 40, cfg.d_model }, packed).copy_to_cuda(),
+			std::vector<int64>{ 0, l, l + 40 }, cfg).copy_to_host();
+		const Tensor<float32, CPU> v1(std::vector<int64>{ l, cfg.d_model }, std::vector<float32>(vo.buffer(), vo.buffer() + l * cfg.d_model));
+		const Tensor<float32, CPU> v2(std::vector<int64>{ 40, cfg.d_model },
+			std::vector<float32>(vo.buffer() + l * cfg.d_model, vo.buffer() + (l + 40) * cfg.d_model));
+		report("tensor_zamba_mamba2_mixer_varlen f32, first sequence", close_enough(v1, e, 0.f, 1e-3f));
+		report("tensor_zamba_mamba2_mixer_varlen f32, second sequence", close_enough(v2, e1, 0.f, 1e-3f));
 	}
 
 	// the decoder layer around the same mixer: y = h + mixer(rms_norm(h) * w_in), prefill then one decode step

@@ -70,3 +70,16 @@ def test_workspace_queries():
     assert lib.b200_mamba2_mixer_prefill(capi.F16, ctypes.byref(cfg), ctypes.byref(w), ctypes.c_void_p(256), ctypes.c_void_p(256),
                                          1, 8, None, None, None, None, 0, None) == -7  # null weights
     assert lib.b200_mamba2_mixer_decode_workspace_bytes(ctypes.byref(cfg), capi.F16, 64) > 0
+    # packed variable-length batches: the workspace is that of one sequence of all the tokens; offsets are validated on the host
+    assert lib.b200_mamba2_mixer_prefill_varlen_workspace_bytes(ctypes.byref(cfg), capi.F16, T) == \
+        lib.b200_mamba2_mixer_prefill_workspace_bytes(ctypes.byref(cfg), capi.F16, 1, T)
+    full = capi.Mamba2Weights(*([ctypes.c_void_p(256)] * 8))
+    one = ctypes.c_void_p(256)
+    cu = lambda *v: (ctypes.c_int64 * len(v))(*v)  # noqa: E731
+    call = lambda c, n: lib.b200_mamba2_mixer_prefill_varlen(capi.F16, ctypes.byref(cfg), ctypes.byref(full), one, one, c, n,  # noqa: E731
+                                                             None, None, None, None, 0, None)
+    assert call(None, 1) == -7
+    assert call(cu(1, 5), 1) == -1  # does not start at 0
+    assert call(cu(0, 5, 3), 2) == -1  # decreasing
+    assert call(cu(0, 0, 0), 2) == 0  # only empty sequences, no states wanted: nothing to do
+    assert call(cu(0, 5), 1) == -3  # tokens but no workspace

@@ -258,6 +258,48 @@ def test_prefill_in_pieces_equals_one_prefill(ops, pieces):
     assert rel_l2(host(d1), host(d2)) < 3e-3
 
 
+@pytest.mark.parametrize("lens", [[512, 100, 0, 1, 257, 3], [128, 128], [0], [700]])
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_packed_variable_length_batch_equals_separate_prefills(ops, lens, dtype):
+    """cu_seqlens batches: every sequence of the packed call gets the outputs and final states of a prefill of that sequence
+    alone (bit for bit: same kernels on the same rows), nothing leaks across a boundary, an empty sequence hands on its
+    initial state; one sequence is also checked against the oracle."""
+    cfg = dict(SMALL, batch=1, seqlen=max(max(lens), 1), chunk=128)
+    td = torch.float16 if dtype == "f16" else torch.float32
+    w = synth.make_weights(cfg, 12)
+    total = sum(lens)
+    u = synth.make_input(cfg, 12, batch=1, seqlen=max(total, 1))[0, :total]
+    if dtype == "f16":
+        w, u = f16w(w), synth.to_f16_values(u)
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, td))
+    ud = torch.from_numpy(np.ascontiguousarray(u)).cuda().to(td)
+    nseq = len(lens)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    H, P, N = cfg["nheads"], cfg["headdim"], cfg["d_state"]
+    init = (torch.randn(nseq, H, P, N, device="cuda", generator=torch.Generator("cuda").manual_seed(3)) * 0.1).contiguous()
+    cache = ops.ZambaMambaCache.zeros(cfg, nseq, td)
+    cache.conv_state.fill_(7.0)  # must be overwritten for every sequence
+    got = mixer.prefill_varlen(ud, cu, initial_states=init, cache=cache)
+    assert got.shape == ud.shape
+    for s, n in enumerate(lens):
+        one = ops.ZambaMambaCache.zeros(cfg, 1, td)
+        if n == 0:
+            assert torch.equal(cache.ssm_state[s], init[s])
+            assert torch.count_nonzero(cache.conv_state[s]) == 0
+            continue
+        alone = mixer.prefill(ud[cu[s]:cu[s + 1]].unsqueeze(0).contiguous(), one, initial_states=init[s:s + 1].contiguous())
+        assert torch.equal(got[cu[s]:cu[s + 1]], alone[0]), f"sequence {s} of lengths {lens}"
+        assert torch.equal(cache.ssm_state[s], one.ssm_state[0])
+        assert torch.equal(cache.conv_state[s], one.conv_state[0])
+    s = int(np.argmax(lens))
+    if lens[s] > 0 and lens[s] % 4 == 0:
+        want = orc.mixer_prefill(u[None, cu[s]:cu[s + 1]], w, dict(cfg, chunk=4), f16io=dtype == "f16",
+                                 initial_states=host(init[s:s + 1]))
+        if dtype == "f16":
+            assert_close_f16(host(got[cu[s]:cu[s + 1]])[None], want["out"], "packed sequence vs oracle", max_fail_fraction=1e-3)
+        assert rel_l2(host(got[cu[s]:cu[s + 1]])[None], want["out"]) < (2e-3 if dtype == "f16" else 1e-4)
+
+
 @pytest.mark.parametrize("bounds", [[0, 128, 256, 384, 512], [0, 100, 101, 300, 512], [0, 512]])
 @pytest.mark.parametrize("dtype", ["f16", "f32"])
 def test_sequence_parallel_segments_emulated_on_one_gpu(ops, bounds, dtype):
