@@ -81,7 +81,15 @@ template <typename T> __device__ __forceinline__ void stf(T* p, float v) { *p = 
 // silu(x) = x / (1 + exp(-x)), the form anyGPU uses (srcs/kernels/cuda/math_ops.cu:3-34).
 // The quotient uses the fast reciprocal path (2 ulp): an IEEE division here makes the conv and norm kernels
 // instruction-bound instead of HBM-bound.
-__device__ __forceinline__ float silu_f32(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
+__device__ __forceinline__ float silu_f32(float v)
+{
+	// ex2 / rcp in their flush-to-zero forms: the default forms wrap each MUFU in range checks and rescaling for denormals,
+	// which nothing here can tell apart from zero (v < -87 gives -0 instead of a denormal)
+	float e, r;
+	asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(v * -1.4426950408889634f));
+	asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+	return v * r;
+}
 
 // torch softplus (beta 1, threshold 20), as F.softplus in scripts/zamba2/mamba_chunk_scan_comb.py:45.
 __device__ __forceinline__ float softplus_f32(float v) { return v > 20.f ? v : log1pf(expf(v)); }
