@@ -7,37 +7,49 @@
 
 namespace b200 {
 
-// One thread owns V consecutive channels and TL consecutive tokens of block (block_x, block_y = batch index).
-template <typename T, int V, int W, int TL>
-__device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
-	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
-	int seqlen, int dims, unsigned cvec /* ceil(dims / V) */, unsigned nwork /* cvec * token blocks */, unsigned block_x, unsigned block_y)
+// The work of one thread of the token-major conv1d: V consecutive channels x TL consecutive tokens starting at (t0, c0).
+// INTERIOR: the W-1 tokens before t0 and all TL tokens lie inside the sequence (all but the first and last token block): no
+// per-row bounds tests, no initial state, unconditional stores.
+template <typename T, int V, int W, int TL, bool INTERIOR>
+__device__ __forceinline__ void conv1d_tok_thread(const T* __restrict__ xb, int64_t xs, const T* __restrict__ w, const T* __restrict__ bias,
+	T* __restrict__ yb, int64_t ys, const T* __restrict__ init, T* __restrict__ fin, int seqlen, int dims, int64_t b, int c0, int t0)
 {
-	const unsigned wid = block_x * blockDim.x + threadIdx.x;
-	if (wid >= nwork) return;
-	const unsigned tb = wid / cvec;
-	const int c0 = static_cast<int>(wid - tb * cvec) * V;
-	const int64_t b = block_y;
-	const int t0 = static_cast<int>(tb) * TL;
-	const T* xb = x + b * seqlen * xs + c0;
-	T* yb = y + b * seqlen * ys + c0;
-
 	// rows t0-(W-1) .. t0+TL-1, all requested before the first use
 	Pack<T, V> raw[TL + W - 1];
 #pragma unroll
 	for (int i = 0; i < TL + W - 1; ++i)
 	{
 		const int t = t0 - (W - 1) + i;
-		if (t >= 0 && t < seqlen) raw[i].load(xb + static_cast<int64_t>(t) * xs);
+		if (INTERIOR || (t >= 0 && t < seqlen)) raw[i].load(xb + static_cast<int64_t>(t) * xs);
 	}
 
+	// weights of V channels x W taps are contiguous: vector loads where the row of a channel quad is 16-byte aligned
 	float wt[W][V], bs[V];
-#pragma unroll
-	for (int c = 0; c < V; ++c)
+	if constexpr (W == 4 && V == 4)
 	{
-		bs[c] = ldf(bias + c0 + c);
+		Pack<T, 4> wv[4], bv;
 #pragma unroll
-		for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + static_cast<int64_t>(c0 + c) * W + k);
+		for (int c = 0; c < 4; ++c) wv[c].load(w + static_cast<int64_t>(c0 + c) * 4);
+		bv.load(bias + c0);
+		bv.unpack(bs);
+#pragma unroll
+		for (int c = 0; c < 4; ++c)
+		{
+			float t4[4];
+			wv[c].unpack(t4);
+#pragma unroll
+			for (int k = 0; k < 4; ++k) wt[k][c] = t4[k];
+		}
+	}
+	else
+	{
+#pragma unroll
+		for (int c = 0; c < V; ++c)
+		{
+			bs[c] = ldf(bias + c0 + c);
+#pragma unroll
+			for (int k = 0; k < W; ++k) wt[k][c] = ldf(w + static_cast<int64_t>(c0 + c) * W + k);
+		}
 	}
 
 	float f[TL + W - 1][V];
@@ -45,9 +57,9 @@ __device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t
 	for (int i = 0; i < TL + W - 1; ++i)
 	{
 		const int t = t0 - (W - 1) + i;
-		if (t >= 0)
+		if (INTERIOR || t >= 0)
 		{
-			if (t < seqlen) raw[i].unpack(f[i]);
+			if (INTERIOR || t < seqlen) raw[i].unpack(f[i]);
 			else
 			{
 #pragma unroll
@@ -65,13 +77,13 @@ __device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t
 #pragma unroll
 	for (int i = 0; i < TL; ++i)
 	{
-		if (t0 + i < seqlen)
+		if (INTERIOR || t0 + i < seqlen)
 		{
 			float out[V];
 #pragma unroll
 			for (int c = 0; c < V; ++c)
 			{
-				float acc = 0.f;
+				float acc = 0.f;  // taps first, bias last: the order of the reference operator
 #pragma unroll
 				for (int k = 0; k < W; ++k) acc += wt[k][c] * f[i + k][c];
 				acc += bs[c];
@@ -84,7 +96,7 @@ __device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t
 	}
 
 	// the thread that consumed the last token holds the next conv_state: the W-1 inputs ending at token seqlen-1
-	if (fin != nullptr && t0 < seqlen && t0 + TL >= seqlen)
+	if (fin != nullptr && t0 + TL >= seqlen)
 	{
 		const int last = seqlen - 1 - t0;  // index of the last valid token inside this block, 0 <= last < TL
 #pragma unroll
@@ -99,6 +111,26 @@ __device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t
 			}
 		}
 	}
+}
+
+// One thread owns V consecutive channels and TL consecutive tokens of block (block_x, block_y = batch index).
+template <typename T, int V, int W, int TL>
+__device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
+	int seqlen, int dims, unsigned cvec /* ceil(dims / V) */, unsigned nwork /* cvec * token blocks */, unsigned block_x, unsigned block_y)
+{
+	const unsigned wid = block_x * blockDim.x + threadIdx.x;
+	if (wid >= nwork) return;
+	const unsigned tb = wid / cvec;
+	const int c0 = static_cast<int>(wid - tb * cvec) * V;
+	const int64_t b = block_y;
+	const int t0 = static_cast<int>(tb) * TL;
+	const T* xb = x + b * seqlen * xs + c0;
+	T* yb = y + b * seqlen * ys + c0;
+	if (t0 >= W - 1 && t0 + TL < seqlen)  // strictly inside: the block with the last token also writes the next conv_state
+		conv1d_tok_thread<T, V, W, TL, true>(xb, xs, w, bias, yb, ys, init, nullptr, seqlen, dims, b, c0, t0);
+	else
+		conv1d_tok_thread<T, V, W, TL, false>(xb, xs, w, bias, yb, ys, init, fin, seqlen, dims, b, c0, t0);
 }
 
 // dt = softplus(dt_raw + bias); dAcs = cumsum_l(dt * A) within each chunk; colf = column factor of the rank-1 decay.
