@@ -60,6 +60,19 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T
 	float ss = 0.f;
 	if constexpr (CACHED)
 	{
+		// every 16-byte vector of x and z this thread will touch is requested before the first one is used: one memory round
+		// trip per row instead of one per vector
+		Pack<T, E> rx[kNormCache], rz[kNormCache];
+#pragma unroll
+		for (int it = 0; it < kNormCache; ++it)
+		{
+			const int i = threadIdx.x + it * kNormThreads;
+			if (i < nvec)
+			{
+				rx[it].load_pinned(xr + i * E);
+				rz[it].load_pinned(zr + i * E);
+			}
+		}
 #pragma unroll
 		for (int it = 0; it < kNormCache; ++it)
 		{
@@ -67,8 +80,8 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T
 			if (i < nvec)
 			{
 				float xv[E], zv[E];
-				NV<T>::load(xr + i * E, xv);
-				NV<T>::load(zr + i * E, zv);
+				rx[it].unpack(xv);
+				rz[it].unpack(zv);
 #pragma unroll
 				for (int e = 0; e < E; ++e)
 				{
