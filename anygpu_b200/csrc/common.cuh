@@ -147,12 +147,15 @@ struct Pack
 	using B = typename BitsOf<V * sizeof(T)>::type;
 	B bits;
 	__device__ __forceinline__ void load(const T* p) { bits = *reinterpret_cast<const B*>(p); }
-	// 16-byte load that stays where it is written (the compiler may otherwise move a load down to its first use and
+	// 8- or 16-byte load that stays where it is written (the compiler may otherwise move a load down to its first use and
 	// serialise what was meant to be a batch of independent requests)
 	__device__ __forceinline__ void load_pinned(const T* p)
 	{
-		static_assert(V * sizeof(T) == 16, "load_pinned moves 16 bytes");
-		asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(bits.x), "=r"(bits.y), "=r"(bits.z), "=r"(bits.w) : "l"(p) : "memory");
+		static_assert(V * sizeof(T) == 16 || V * sizeof(T) == 8, "load_pinned moves 8 or 16 bytes");
+		if constexpr (V * sizeof(T) == 16)
+			asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(bits.x), "=r"(bits.y), "=r"(bits.z), "=r"(bits.w) : "l"(p) : "memory");
+		else
+			asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits.x), "=r"(bits.y) : "l"(p) : "memory");
 	}
 	__device__ __forceinline__ void store(T* p) const { *reinterpret_cast<B*>(p) = bits; }
 	// f16 pairs go through the packed half2 conversions (a scalar f16 -> f32 conversion issues on the slow XU pipe)

@@ -219,13 +219,20 @@ __global__ void __launch_bounds__(THREADS) rms_norm_vec_kernel(const T* __restri
 	const int nvec = d / E;
 	float v[CACHE][E], wv[CACHE][E];
 	float ss = 0.f;
+	Pack<T, E> rx[CACHE];  // all cached vectors of the row are requested before the first is used
+#pragma unroll
+	for (int it = 0; it < CACHE; ++it)
+	{
+		const int i = threadIdx.x + it * THREADS;
+		if (i < nvec) rx[it].load_pinned(xr + i * E);
+	}
 #pragma unroll
 	for (int it = 0; it < CACHE; ++it)
 	{
 		const int i = threadIdx.x + it * THREADS;
 		if (i < nvec)
 		{
-			NV<T>::load(xr + i * E, v[it]);
+			rx[it].unpack(v[it]);
 			NV<T>::load(w + i * E, wv[it]);
 #pragma unroll
 			for (int e = 0; e < E; ++e) ss += v[it][e] * v[it][e];
