@@ -103,6 +103,78 @@ __global__ void __launch_bounds__(256) conv1d_seq_vec_kernel(const T* __restrict
 	for (int i = 0; i < NV; ++i) Vec16<T>::store(y + base + i * E, out + i * E);
 }
 
+// Width 4, long rows: one CTA per row, a thread owns NVI 16-byte vectors that lie blockDim.x vectors apart, so that every
+// load and store instruction of a warp covers 512 contiguous bytes and all NVI loads of a thread are in flight together. The
+// three elements before a vector come from the neighbouring lane by shuffle; lane 0 of a warp reads the 4 elements in front of its
+// vector instead (vector 0 of a row sees the zero padding). The per-thread overhead (weights, addressing) is paid once per
+// NVI * E outputs.
+template <typename T, int NVI>
+__global__ void __launch_bounds__(256) conv1d_seq_w4_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+	T* __restrict__ y, int vec_per_row /* S / E, a multiple of blockDim.x * NVI */, unsigned dims)
+{
+	constexpr int E = Vec16<T>::E;
+	constexpr int HV = 4;  // elements fetched in front of a vector by lane 0 (8 or 16 bytes, aligned like the vector); 3 are used
+	const unsigned row = blockIdx.y + blockIdx.z * 65535u;
+	const int lane = threadIdx.x & 31;
+	const int64_t rbase = static_cast<int64_t>(row) * (static_cast<int64_t>(vec_per_row) * E);
+	const int v0 = blockIdx.x * (blockDim.x * NVI) + threadIdx.x;
+
+	Pack<T, E> raw[NVI];
+	Pack<T, HV> head[NVI];
+#pragma unroll
+	for (int i = 0; i < NVI; ++i) raw[i].load_pinned(x + rbase + static_cast<int64_t>(v0 + i * static_cast<int>(blockDim.x)) * E);
+	if (lane == 0)
+	{
+#pragma unroll
+		for (int i = 0; i < NVI; ++i)
+		{
+			const int v = v0 + i * static_cast<int>(blockDim.x);
+			if (v > 0) head[i].load_pinned(x + rbase + static_cast<int64_t>(v) * E - HV);
+		}
+	}
+	const unsigned d = row % dims;
+	Pack<T, 4> wp;
+	wp.load(w + static_cast<int64_t>(d) * 4);
+	float wt[4];
+	wp.unpack(wt);
+	const float bs = ldf(bias + d);
+
+#pragma unroll
+	for (int i = 0; i < NVI; ++i)
+	{
+		const int v = v0 + i * static_cast<int>(blockDim.x);
+		float f[E + 3];
+		raw[i].unpack(f + 3);
+		float h0 = __shfl_up_sync(0xffffffffu, f[E], 1);
+		float h1 = __shfl_up_sync(0xffffffffu, f[E + 1], 1);
+		float h2 = __shfl_up_sync(0xffffffffu, f[E + 2], 1);
+		if (lane == 0)
+		{
+			h0 = h1 = h2 = 0.f;  // zero left padding in front of the row
+			if (v > 0)
+			{
+				float hf[HV];
+				head[i].unpack(hf);
+				h0 = hf[HV - 3]; h1 = hf[HV - 2]; h2 = hf[HV - 1];
+			}
+		}
+		f[0] = h0; f[1] = h1; f[2] = h2;
+		float out[E];
+#pragma unroll
+		for (int e = 0; e < E; ++e)
+		{
+			float acc = 0.f;  // taps oldest first, bias last
+#pragma unroll
+			for (int k = 0; k < 4; ++k) acc += wt[k] * f[e + k];
+			acc += bs;
+			out[e] = silu_f32(acc);
+		}
+		Pack<T, E> o;
+		o.pack(out);
+		o.store(y + rbase + static_cast<int64_t>(v) * E);
+	}
+}
+
 // Any shape: one thread per output element.
 template <typename T>
 __global__ void __launch_bounds__(256) conv1d_seq_scalar_kernel(const T* __restrict__ x, const T* __restrict__ w,
@@ -201,6 +273,32 @@ static int conv1d_seq(const void* xv, const void* wv, const void* bv, void* yv, 
 	constexpr int E = Vec16<T>::E;
 	const bool al = aligned16(x) && aligned16(y);
 	const bool grid_ok = rows <= 65535 || rows % 65535 == 0;
+	if (al && grid_ok && W == 4 && S % E == 0 && (reinterpret_cast<uintptr_t>(w) % (4 * sizeof(T))) == 0 &&
+		dims <= 0x7fffffffLL)
+	{
+		// threads x vectors per thread that tile the row exactly; prefer 4 vectors per thread
+		const int64_t vpr = S / E;
+		int threads = 0, nvi = 0;
+		for (int t : { 128, 256, 64, 32 })
+		{
+			if (vpr % (t * 4) == 0) { threads = t; nvi = 4; break; }
+		}
+		if (!threads)
+			for (int t : { 256, 128, 64, 32 })
+			{
+				if (vpr % (t * 2) == 0) { threads = t; nvi = 2; break; }
+			}
+		if (threads)
+		{
+			unsigned gy = static_cast<unsigned>(rows), gz = 1;
+			if (rows > 65535) { gy = 65535u; gz = static_cast<unsigned>(rows / 65535); }
+			const dim3 g(static_cast<unsigned>(vpr / (threads * nvi)), gy, gz);
+			if (nvi == 4) conv1d_seq_w4_kernel<T, 4><<<g, threads, 0, st>>>(x, w, bias, y, static_cast<int>(vpr), static_cast<unsigned>(dims));
+			else conv1d_seq_w4_kernel<T, 2><<<g, threads, 0, st>>>(x, w, bias, y, static_cast<int>(vpr), static_cast<unsigned>(dims));
+			B200_LAUNCH_CHECK();
+			return B200_OK;
+		}
+	}
 	if (al && grid_ok && S % (2 * E) == 0) return launch_seq_vec<T, 2>(x, w, bias, y, rows, S, dims, W, st);
 	if (al && grid_ok && S % E == 0) return launch_seq_vec<T, 1>(x, w, bias, y, rows, S, dims, W, st);
 	const int64_t total = rows * S;
