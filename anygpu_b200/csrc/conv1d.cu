@@ -230,6 +230,54 @@ __global__ void __launch_bounds__(256) conv1d_update_kernel(const T* __restrict_
 	if (SW > 0) stf(st + SW - 1, xv);
 }
 
+// Width 4, 4 channels per thread: their 12 state values, 16 taps, 4 biases and 4 inputs are each contiguous, so the step is
+// 9 vector loads and 4 vector stores per thread instead of 24 scalar accesses per channel; grid (channel quads, batch).
+template <typename T>
+__global__ void __launch_bounds__(128) conv1d_update_w4_kernel(const T* __restrict__ xt, int64_t xs, T* __restrict__ state,
+	const T* __restrict__ w, const T* __restrict__ bias, T* __restrict__ yt, int64_t ys, int dims)
+{
+	const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+	if (d >= dims) return;
+	const int64_t b = blockIdx.y;
+	T* st = state + (b * dims + d) * 3;
+	Pack<T, 4> sv[3], wv[4], bv, xv;
+#pragma unroll
+	for (int i = 0; i < 3; ++i) sv[i].load(st + i * 4);
+	xv.load(xt + b * xs + d);
+#pragma unroll
+	for (int c = 0; c < 4; ++c) wv[c].load(w + static_cast<int64_t>(d + c) * 4);
+	bv.load(bias + d);
+	float s[12], x[4], bs[4], y[4];
+#pragma unroll
+	for (int i = 0; i < 3; ++i) sv[i].unpack(s + i * 4);  // channel-major: s[c * 3 + k]
+	xv.unpack(x);
+	bv.unpack(bs);
+#pragma unroll
+	for (int c = 0; c < 4; ++c)
+	{
+		float wt[4];
+		wv[c].unpack(wt);
+		float acc = 0.f;  // taps oldest first, bias last
+#pragma unroll
+		for (int k = 0; k < 3; ++k) acc += wt[k] * s[c * 3 + k];
+		acc += wt[3] * x[c];
+		acc += bs[c];
+		y[c] = silu_f32(acc);
+		s[c * 3] = s[c * 3 + 1];
+		s[c * 3 + 1] = s[c * 3 + 2];
+		s[c * 3 + 2] = x[c];
+	}
+	Pack<T, 4> o;
+	o.pack(y);
+	o.store(yt + b * ys + d);
+#pragma unroll
+	for (int i = 0; i < 3; ++i)
+	{
+		sv[i].pack(s + i * 4);
+		sv[i].store(st + i * 4);
+	}
+}
+
 // ---- host launchers ----------------------------------------------------------------------------------------
 
 template <typename T, int NV>
@@ -393,6 +441,21 @@ extern "C" int b200_causal_conv1d_update(int dtype, const void* x_t, int64_t x_s
 	if (batch < 0 || dims <= 0 || width < 1 || width > kMaxWidth || x_stride < dims || y_stride < dims) return B200_ERR_BAD_SHAPE;
 	if (batch == 0) return B200_OK;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
+	const size_t vb = 4 * (dtype == B200_F16 ? 2 : 4);  // bytes of a 4-element vector
+	auto al = [vb](const void* p) { return (reinterpret_cast<uintptr_t>(p) % vb) == 0; };
+	if (width == 4 && dims % 4 == 0 && x_stride % 4 == 0 && y_stride % 4 == 0 && batch <= 65535 && dims <= 0x7fffffffLL && al(x_t) &&
+		al(conv_state) && al(w) && al(bias) && al(y_t) && (dtype == B200_F16 || dtype == B200_F32))
+	{
+		const dim3 g(static_cast<unsigned>(cdiv(dims / 4, 128)), static_cast<unsigned>(batch));
+		if (dtype == B200_F16)
+			conv1d_update_w4_kernel<__half><<<g, 128, 0, st>>>(static_cast<const __half*>(x_t), x_stride, static_cast<__half*>(conv_state),
+				static_cast<const __half*>(w), static_cast<const __half*>(bias), static_cast<__half*>(y_t), y_stride, static_cast<int>(dims));
+		else
+			conv1d_update_w4_kernel<float><<<g, 128, 0, st>>>(static_cast<const float*>(x_t), x_stride, static_cast<float*>(conv_state),
+				static_cast<const float*>(w), static_cast<const float*>(bias), static_cast<float*>(y_t), y_stride, static_cast<int>(dims));
+		B200_LAUNCH_CHECK();
+		return B200_OK;
+	}
 	const unsigned blocks = static_cast<unsigned>(cdiv(batch * dims, 256));
 	if (dtype == B200_F16)
 		conv1d_update_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(x_t), x_stride,

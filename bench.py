@@ -520,6 +520,18 @@ def run_kernel(args):
         w, bs = rn(C_, 4, std=0.5), rn(C_, std=0.1)
         state, xt = rn(B_, C_, 3), rn(B_, C_)
         fn = lambda i: ops.tensor_causal_conv1d_update(xt, state, w, bs)
+        if args.graph:
+            # the configuration's 256 consecutive single-token steps as one CUDA graph: per-step device time without the host's
+            # launch path (ctypes + launch, ~20 us per call) in between
+            per_call = 256
+            xts = rn(per_call, B_, C_)
+            fn(0)
+            torch.cuda.synchronize()
+            gobj = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gobj):
+                for t in range(per_call):
+                    ops.tensor_causal_conv1d_update(xts[t], state, w, bs)
+            fn = lambda i: gobj.replay()
         bytes_alg = B_ * C_ * 2 * (3 + 3 + 1 + 1) + C_ * 5 * 2
     elif k == "conv1d_tokens":
         zx = [rn(b, l, d_in_proj) for _ in range(nbuf)]
@@ -597,7 +609,7 @@ def run_kernel(args):
     ms = sorted(e0.elapsed_time(e1) / per_call for e0, e1 in evs)
     med, mn = ms[len(ms) // 2], ms[0]
     capi.check("b200_last_device_error", capi.load().b200_last_device_error(None, None))
-    out = {"kernel": k, "small": bool(args.small), "graph": bool(args.graph), "graph_steps": args.graph_steps if args.graph else 0, "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
+    out = {"kernel": k, "small": bool(args.small), "graph": bool(args.graph), "graph_steps": (per_call if k == "conv1d_decode" else args.graph_steps) if args.graph else 0, "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
     if bytes_alg:
         out.update(algorithmic_bytes=bytes_alg, gbs_median=bytes_alg / (med * 1e-3) / 1e9, hbm_peak_gbs=peaks["hbm_gbs"],
                    frac_of_hbm_peak=bytes_alg / (med * 1e-3) / 1e9 / peaks["hbm_gbs"], peak_source=peaks["source"])
@@ -625,7 +637,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
     ap.add_argument("--layout", default="KN", choices=["KN", "NK"], help="with --kernel decode: projection weight layout")
     ap.add_argument("--graph-steps", type=int, default=1, help="with --kernel decode --graph: consecutive steps recorded into one graph")
-    ap.add_argument("--graph", action="store_true", help="with --kernel decode: replay the step from a CUDA graph")
+    ap.add_argument("--graph", action="store_true", help="with --kernel decode / conv1d_decode: replay the step(s) from a CUDA graph")
     args = ap.parse_args()
     if args.kernel:
         return run_kernel(args)
