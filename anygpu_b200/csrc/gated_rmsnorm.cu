@@ -192,6 +192,57 @@ __global__ void __launch_bounds__(128) gated_mul_sumsq_kernel(const T* x, int64_
 	if (threadIdx.x == 0) sumsq[row] = total;
 }
 
+// The same with 16-byte vectors (rows, w and d aligned to them): up to kNormCache vectors per thread requested up front.
+template <typename T>
+__global__ void __launch_bounds__(128) gated_mul_sumsq_vec_kernel(const T* x, int64_t xs, const T* __restrict__ z, int64_t zs,
+	const T* __restrict__ w, T* y /* may alias x */, int64_t ys, float* __restrict__ sumsq, int d)
+{
+	constexpr int E = NV<T>::E;
+	__shared__ float red[4];
+	const int64_t row = blockIdx.x;
+	const T* xr = x + row * xs;
+	const T* zr = z + row * zs;
+	T* yr = y + row * ys;
+	const int nvec = d / E;
+	float ss = 0.f;
+	for (int i0 = threadIdx.x; i0 < nvec; i0 += kNormCache * 128)
+	{
+		Pack<T, E> rx[kNormCache], rz[kNormCache];
+#pragma unroll
+		for (int it = 0; it < kNormCache; ++it)
+		{
+			const int i = i0 + it * 128;
+			if (i < nvec)
+			{
+				rx[it].load_pinned(xr + i * E);
+				rz[it].load_pinned(zr + i * E);
+			}
+		}
+#pragma unroll
+		for (int it = 0; it < kNormCache; ++it)
+		{
+			const int i = i0 + it * 128;
+			if (i < nvec)
+			{
+				float xv[E], zv[E], wv[E], o[E];
+				rx[it].unpack(xv);
+				rz[it].unpack(zv);
+				NV<T>::load(w + i * E, wv);
+#pragma unroll
+				for (int e = 0; e < E; ++e)
+				{
+					const float gv = xv[e] * silu_f32(zv[e]);
+					ss += gv * gv;
+					o[e] = gv * wv[e];
+				}
+				NV<T>::store(yr + i * E, o);
+			}
+		}
+	}
+	const float total = block_sum<128>(ss, red);
+	if (threadIdx.x == 0) sumsq[row] = total;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) row_scale_rsqrt_kernel(T* __restrict__ out, int64_t ld, const float* __restrict__ sumsq,
 	int64_t rows, int cols, float inv_d, float eps)
@@ -202,6 +253,24 @@ __global__ void __launch_bounds__(256) row_scale_rsqrt_kernel(T* __restrict__ ou
 	const int c = static_cast<int>(i - r * cols);
 	T* p = out + r * ld + c;
 	stf(p, ldf(p) * rsqrtf(sumsq[r] * inv_d + eps));
+}
+
+// The same with 16-byte vectors: grid (vector blocks of a row, rows), no division.
+template <typename T>
+__global__ void __launch_bounds__(256) row_scale_rsqrt_vec_kernel(T* __restrict__ out, int64_t ld, const float* __restrict__ sumsq,
+	int cols, float inv_d, float eps)
+{
+	constexpr int E = NV<T>::E;
+	const int c = (blockIdx.x * blockDim.x + threadIdx.x) * E;
+	if (c >= cols) return;
+	const int64_t r = blockIdx.y + static_cast<int64_t>(blockIdx.z) * gridDim.y;
+	const float sc = rsqrtf(sumsq[r] * inv_d + eps);
+	T* p = out + r * ld + c;
+	float v[E];
+	NV<T>::load(p, v);
+#pragma unroll
+	for (int e = 0; e < E; ++e) v[e] *= sc;
+	NV<T>::store(p, v);
 }
 
 // ---- plain RMSNorm (the input norm of the decoder layer around the mixer) ----------------------------------------------
@@ -343,6 +412,19 @@ int gated_mul_sumsq(int dtype, const void* x, int64_t xs, const void* z, int64_t
 {
 	if (rows > 0x7fffffffLL || d > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 	const unsigned g = static_cast<unsigned>(rows);
+	const size_t esz = dtype == B200_F16 ? 2 : 4;
+	const int64_t ev = 16 / static_cast<int64_t>(esz);
+	if (d % ev == 0 && xs % ev == 0 && zs % ev == 0 && ys % ev == 0 && aligned16(x) && aligned16(z) && aligned16(w) && aligned16(y))
+	{
+		if (dtype == B200_F16)
+			gated_mul_sumsq_vec_kernel<__half><<<g, 128, 0, st>>>(static_cast<const __half*>(x), xs, static_cast<const __half*>(z), zs,
+				static_cast<const __half*>(w), static_cast<__half*>(y), ys, sumsq, static_cast<int>(d));
+		else
+			gated_mul_sumsq_vec_kernel<float><<<g, 128, 0, st>>>(static_cast<const float*>(x), xs, static_cast<const float*>(z), zs,
+				static_cast<const float*>(w), static_cast<float*>(y), ys, sumsq, static_cast<int>(d));
+		B200_LAUNCH_CHECK();
+		return B200_OK;
+	}
 	if (dtype == B200_F16)
 		gated_mul_sumsq_kernel<__half><<<g, 128, 0, st>>>(static_cast<const __half*>(x), xs, static_cast<const __half*>(z), zs,
 			static_cast<const __half*>(w), static_cast<__half*>(y), ys, sumsq, static_cast<int>(d));
@@ -356,6 +438,23 @@ int gated_mul_sumsq(int dtype, const void* x, int64_t xs, const void* z, int64_t
 int row_scale_rsqrt(int dtype, void* out, int64_t ld, const float* sumsq, int64_t rows, int64_t cols, float inv_d, float eps,
 	cudaStream_t st)
 {
+	{
+		const int64_t ev = dtype == B200_F16 ? 8 : 4;
+		// rows as grid y * z (z > 1 only beyond 65535 rows, which must then split evenly)
+		int64_t gy = rows, gz = 1;
+		while (gy > 65535 && gz < 65535) { gz *= 2; gy = rows / gz; }
+		if (cols % ev == 0 && ld % ev == 0 && aligned16(out) && cols <= 0x7fffffffLL && gy * gz == rows && gy <= 65535 && rows > 0 &&
+			(dtype == B200_F16 || dtype == B200_F32))
+		{
+			const dim3 g(static_cast<unsigned>(cdiv(cols / ev, 256)), static_cast<unsigned>(gy), static_cast<unsigned>(gz));
+			if (dtype == B200_F16)
+				row_scale_rsqrt_vec_kernel<__half><<<g, 256, 0, st>>>(static_cast<__half*>(out), ld, sumsq, static_cast<int>(cols), inv_d, eps);
+			else
+				row_scale_rsqrt_vec_kernel<float><<<g, 256, 0, st>>>(static_cast<float*>(out), ld, sumsq, static_cast<int>(cols), inv_d, eps);
+			B200_LAUNCH_CHECK();
+			return B200_OK;
+		}
+	}
 	const int64_t blocks = cdiv(rows * cols, 256);
 	if (blocks > 0x7fffffffLL || cols > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 	if (dtype == B200_F16)
