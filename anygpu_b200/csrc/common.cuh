@@ -44,6 +44,21 @@ constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs
 uint32_t* device_error_word();
 
 // Kernel launch with programmatic stream serialization (see pdl_wait below); `pdl` false gives a normal launch.
+// Opt-in to more than 48 KiB of dynamic shared memory, once per device and kernel (the attribute belongs to the device's
+// context: a process that drives several GPUs needs it on each). `done` is the call site's static per-device flag array.
+template <typename K>
+inline cudaError_t allow_dynamic_smem(K* kernel, int bytes, bool (&done)[64])
+{
+	int dev = 0;
+	cudaError_t e = cudaGetDevice(&dev);
+	if (e != cudaSuccess) return e;
+	if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+	if (done[dev]) return cudaSuccess;
+	e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+	if (e == cudaSuccess) done[dev] = true;
+	return e;
+}
+
 bool pdl_enabled();  // false when the environment variable B200_NO_PDL is set to 1
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_chained(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args)

@@ -492,12 +492,8 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 	const __half* residual, int64_t ldr)
 {
 	using namespace gemm2;
-	static bool attr_set = false;
-	if (!attr_set)
-	{
-		B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_pair_kernel<B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-		attr_set = true;
-	}
+	static bool smem_ok[64] = {};
+	B200_CUDA_TRY(allow_dynamic_smem(gemm_f16_tcgen05_pair_kernel<B_MN>, SMEM_BYTES, smem_ok));
 	const int m_tiles = static_cast<int>(cdiv(M, 2 * BM)), n_tiles = static_cast<int>(cdiv(N, BN));
 	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
 	const int64_t pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
@@ -512,12 +508,8 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 	const __half* residual, int64_t ldr)
 {
 	using namespace gemm;
-	static bool attr_set = false;
-	if (!attr_set)
-	{
-		B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<B_MN, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-		attr_set = true;
-	}
+	static bool smem_ok[64] = {};
+	B200_CUDA_TRY(allow_dynamic_smem(gemm_f16_tcgen05_kernel<B_MN, C>, C::SMEM_BYTES, smem_ok));
 	const int m_tiles = static_cast<int>(cdiv(M, BM)), n_tiles = static_cast<int>(cdiv(N, C::BN));
 	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
 	const int64_t slots = static_cast<int64_t>(kNumSMs) * C::MIN_CTAS;

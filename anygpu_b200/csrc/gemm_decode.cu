@@ -490,12 +490,8 @@ template <int B_MN, int A_ROWS>
 static int launch_streamk(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmP, int M, const StreamKPlan& p, cudaStream_t st)
 {
 	using R = dgemm::Ring<A_ROWS>;
-	static bool attr_set = false;
-	if (!attr_set)
-	{
-		B200_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_streamk_kernel<B_MN, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, R::SMEM_BYTES));
-		attr_set = true;
-	}
+	static bool smem_ok[64] = {};
+	B200_CUDA_TRY(allow_dynamic_smem(gemm_f16_streamk_kernel<B_MN, A_ROWS>, R::SMEM_BYTES, smem_ok));
 	B200_CUDA_TRY(launch_chained(pdl_enabled(), gemm_f16_streamk_kernel<B_MN, A_ROWS>, dim3(p.grid), dim3(dgemm::THREADS), R::SMEM_BYTES, st,
 		tmA, tmB, tmP, M, p.k_blocks, p.total, p.max_seg, device_error_word()));
 	return B200_OK;

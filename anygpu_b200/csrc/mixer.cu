@@ -3,6 +3,7 @@
 //   prefill: in_proj GEMM -> causal conv1d+SiLU (token-major) -> SSD chunked scan -> gated RMSNorm -> out_proj GEMM
 //   decode : in_proj GEMM -> conv_state update -> ssm_state recurrence -> gated RMSNorm -> out_proj GEMM
 // Six to eight launches on one stream, no allocation, no host synchronisation.
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -335,7 +336,10 @@ extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_confi
 	char* out_dev = p + io;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-	// one sequence per pipeline step (sequences are independent through every stage of the mixer)
+	// one sequence per pipeline step (sequences are independent through every stage of the mixer). The copy streams and events
+	// are shared by all calls on a device: calls from several host threads enqueue one after the other.
+	static std::mutex pipe_mutex;
+	std::lock_guard<std::mutex> pipe_lock(pipe_mutex);
 	HostPipe* hp = nullptr;
 	int rc = host_pipe(&hp, batch);
 	if (rc) return rc;

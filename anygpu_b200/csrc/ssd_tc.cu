@@ -699,16 +699,16 @@ int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs
 	if (d.N == 64)
 	{
 		const int smem = nkb * (cstate::A_KB_BYTES + 64 * 128) + 1024;
-		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_state_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (cstate::A_KB_BYTES + 64 * 128) + 1024)); set = true; }
+		static bool smem_ok[64] = {};
+		B200_CUDA_TRY(allow_dynamic_smem(ssd_chunk_state_tc_kernel<64>, 4 * (cstate::A_KB_BYTES + 64 * 128) + 1024, smem_ok));
 		ssd_chunk_state_tc_kernel<64><<<grid, cstate::THREADS, smem, st>>>(tmX, tmB, tmS, w.dt, w.dacs, d.seqlen, d.H, d.G, d.Q, d.nchunks,
 			device_error_word());
 	}
 	else
 	{
 		const int smem = nkb * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024;
-		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_state_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 4 * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024)); set = true; }
+		static bool smem_ok[64] = {};
+		B200_CUDA_TRY(allow_dynamic_smem(ssd_chunk_state_tc_kernel<128>, 4 * (cstate::A_KB_BYTES + 2 * 64 * 128) + 1024, smem_ok));
 		ssd_chunk_state_tc_kernel<128><<<grid, cstate::THREADS, smem, st>>>(tmX, tmB, tmS, w.dt, w.dacs, d.seqlen, d.H, d.G, d.Q, d.nchunks,
 			device_error_word());
 	}
@@ -742,16 +742,16 @@ int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs,
 	if (d.N == 64)
 	{
 		using Lt = cscan::Layout<64, 4, 1>;
-		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<64, 4, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		static bool smem_ok[64] = {};
+		B200_CUDA_TRY(allow_dynamic_smem(ssd_chunk_scan_tc_kernel<64, 4, 1>, Lt::TOTAL, smem_ok));
 		ssd_chunk_scan_tc_kernel<64, 4, 1><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
 			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
 	}
 	else
 	{
 		using Lt = cscan::Layout<128, 1, 1>;
-		static bool set = false;
-		if (!set) { B200_CUDA_TRY(cudaFuncSetAttribute(ssd_chunk_scan_tc_kernel<128, 1, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, Lt::TOTAL)); set = true; }
+		static bool smem_ok[64] = {};
+		B200_CUDA_TRY(allow_dynamic_smem(ssd_chunk_scan_tc_kernel<128, 1, 1>, Lt::TOTAL, smem_ok));
 		ssd_chunk_scan_tc_kernel<128, 1, 1><<<grid, cscan::THREADS, Lt::TOTAL, st>>>(tmX, tmB, tmC, tmP, tmY, D, w.dt, w.dacs, w.colf, d.seqlen,
 			d.H, d.G, d.Q, d.nchunks, hpc, device_error_word());
 	}
