@@ -47,6 +47,65 @@ def measured_peaks():
     return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
 
 
+class NvmlSampler:
+    """Reads SM clock, power and clock-event reasons of one GPU through NVML (read-only queries, the data `nvidia-smi` prints)
+    from a thread every millisecond while the timed region runs: the region of the default run lasts ~10 ms, too short for the
+    100 ms period of `nvidia-smi -lms`."""
+
+    def __init__(self, cuda_index):
+        self.rows, self.stop_flag, self.thread, self.handle, self.nv = [], False, None, None, None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            uuid = getattr(torch.cuda.get_device_properties(cuda_index), "uuid", None)
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(uuid)).encode()) if uuid is not None else None
+            except Exception:
+                self.handle = None
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+            self.nv = pynvml
+        except Exception:
+            self.handle = None
+
+    def available(self):
+        return self.handle is not None
+
+    def start(self):
+        self.thread = threading.Thread(target=self._run, daemon=True)
+        self.thread.start()
+
+    def _run(self):
+        nv, h = self.nv, self.handle
+        reasons_of = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self.stop_flag:
+            try:
+                self.rows.append((time.time(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM), reasons_of(h),
+                                  nv.nvmlDeviceGetPowerUsage(h) / 1000.0))
+            except Exception:
+                break
+            time.sleep(0.001)
+
+    def stop(self, t0, t1):
+        self.stop_flag = True
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
+        rows = [r for r in self.rows if t0 <= r[0] <= t1] or self.rows
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        nv = self.nv
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown, "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown, "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        seen = sorted(n for n, bit in names.items() if any(r[2] & bit for r in rows))
+        try:
+            sm_max = float(nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM))
+        except Exception:
+            sm_max = None
+        return {"sm_mhz": statistics.median(float(r[1]) for r in rows), "sm_max_mhz": sm_max, "reasons": seen, "samples": len(rows),
+                "power_w_max": max(r[3] for r in rows), "source": "nvml, 1 ms period, samples inside the timed region"}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -230,8 +289,10 @@ def run_gpu(args):
     for i in range(args.warmup):
         mixer.prefill(us[i % nbuf], out=out)
     barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = NvmlSampler(local_rank) if rank == 0 else None
     if rank == 0:
+        if not sampler.available():
+            sampler = ClockSampler(local_rank)  # nvidia-smi at its 100 ms period: few samples fall into a short region
         sampler.start()
         time.sleep(0.25)
     lib.b200_stage_timing_enable(1)
