@@ -22,9 +22,10 @@ def build(with_ref=True):
     """Compile liboracle.so (always) and, only where the anyGPU checkout exists, _ref/libanygpu_ref.so (its CPU operators) and
     _ref/ref_cuda_bench (a timing program around its CUDA kernels)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
-    if with_ref and os.path.exists("/root/reference/srcs/core/core.cpp"):
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
-        subprocess.check_call(["make", "-s", "-C", _HERE, "ref_cuda"])
+    ref = os.environ.get("ANYGPU_REF", "/root/reference")  # where the anyGPU checkout lies (the Makefile's REF)
+    if with_ref and os.path.exists(os.path.join(ref, "srcs", "core", "core.cpp")):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref}"])
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref_cuda", f"REF={ref}"])
 
 
 def lib():
