@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(256) conv1d_seq_scalar_kernel(const T* __restr
 // consecutive tokens. All TL + W - 1 row fragments are loaded before the first use, so a thread keeps TL + W - 1
 // loads in flight while its register footprint stays small enough for ~28 resident warps per SM.
 template <typename T, int V, int W, int TL>
-__global__ void __launch_bounds__(128) conv1d_tok_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+__global__ void __launch_bounds__(128, 7) conv1d_tok_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
 	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin,
 	int seqlen, int dims, unsigned cvec /* ceil(dims / V) */, unsigned nwork /* cvec * token blocks */)
 {

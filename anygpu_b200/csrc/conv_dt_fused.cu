@@ -8,7 +8,7 @@
 namespace b200 {
 
 template <typename T, int W>
-__global__ void __launch_bounds__(128) conv1d_tok_dt_fused_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
+__global__ void __launch_bounds__(128, 7) conv1d_tok_dt_fused_kernel(const T* __restrict__ x, int64_t xs, const T* __restrict__ w,
 	const T* __restrict__ bias, T* __restrict__ y, int64_t ys, const T* __restrict__ init, T* __restrict__ fin, int seqlen, int dims,
 	unsigned cvec, unsigned nwork,
 	const T* __restrict__ dt, int64_t dts, const float* __restrict__ A, int a_is_log, const float* __restrict__ dt_bias, int dt_softplus,
