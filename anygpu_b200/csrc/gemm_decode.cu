@@ -313,7 +313,7 @@ __device__ __forceinline__ void unpack4(const Half4& v, float* f)
 // the rolling causal conv1d update (state [M, conv_dim, W-1] shifted by one, y = silu(bias + sum_k w[k] * window[k]), the
 // arithmetic of conv1d_update_kernel on the f16-rounded projection) and are written to xbc[M, conv_dim]; every column is
 // written to zx[M, ldz] as f16.
-__global__ void __launch_bounds__(256) streamk_reduce_conv_kernel(const float* __restrict__ part, __half* __restrict__ zx, int64_t ldz,
+__global__ void __launch_bounds__(256, 5) streamk_reduce_conv_kernel(const float* __restrict__ part, __half* __restrict__ zx, int64_t ldz,
 	int M, int N, int k_blocks, int total_units, int grid, int max_seg, int conv_lo, int conv_dim, int W,
 	__half* __restrict__ conv_state, const __half* __restrict__ conv_w, const __half* __restrict__ conv_b, __half* __restrict__ xbc)
 {
