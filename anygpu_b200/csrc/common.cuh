@@ -31,8 +31,16 @@ inline int record_cuda(cudaError_t e)
 		if (e__ != cudaSuccess) return b200::record_cuda(e__); \
 	} while (0)
 
+// Kernel launches issued by the library in this process (b200_launch_count reads and resets it): every launch site passes
+// through B200_LAUNCH_CHECK or launch_chained.
+void count_launch();
+
 // Launch check that does not synchronise.
-#define B200_LAUNCH_CHECK() B200_CUDA_TRY(cudaGetLastError())
+#define B200_LAUNCH_CHECK()                \
+	do {                                   \
+		b200::count_launch();              \
+		B200_CUDA_TRY(cudaGetLastError()); \
+	} while (0)
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int64_t cdiv(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -73,6 +81,7 @@ inline cudaError_t launch_chained(bool pdl, void (*kernel)(KArgs...), dim3 grid,
 	attr[0].val.programmaticStreamSerializationAllowed = 1;
 	cfg.attrs = attr;
 	cfg.numAttrs = pdl ? 1 : 0;
+	count_launch();
 	return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

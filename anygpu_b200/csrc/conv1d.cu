@@ -393,8 +393,10 @@ static int conv1d_tok(const void* xv, int64_t xs, const void* wv, const void* bv
 {
 	constexpr int V = 4;  // 8 bytes of f16 / 16 bytes of f32 per access
 	const uintptr_t amask = V * sizeof(T) - 1;
+	// the width-4 body also fetches the 4 taps of a channel and the 4 biases of a channel quad with one access each
+	const bool wb_ok = W != 4 || ((reinterpret_cast<uintptr_t>(wv) & amask) == 0 && (reinterpret_cast<uintptr_t>(bv) & amask) == 0);
 	const bool vec = (reinterpret_cast<uintptr_t>(xv) & amask) == 0 && (reinterpret_cast<uintptr_t>(yv) & amask) == 0 && xs % V == 0 &&
-		ys % V == 0 && dims % V == 0;
+		ys % V == 0 && dims % V == 0 && wb_ok;
 	if (vec)
 		return launch_tok<T, V>(static_cast<const T*>(xv), xs, static_cast<const T*>(wv), static_cast<const T*>(bv),
 			static_cast<T*>(yv), ys, static_cast<const T*>(init), static_cast<T*>(fin), batch, seqlen, dims, W, st);

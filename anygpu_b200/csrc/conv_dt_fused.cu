@@ -30,11 +30,13 @@ __global__ void __launch_bounds__(128, 7) conv1d_tok_dt_fused_kernel(const T* __
 }
 
 // True when the fused launch covers this problem (otherwise the caller runs the two operators one after the other).
-bool conv_dt_fused_applies(int dtype, const void* x, int64_t xs, const void* y, int64_t ys, int64_t batch, int64_t seqlen, int64_t dims,
-	int width)
+bool conv_dt_fused_applies(int dtype, const void* x, int64_t xs, const void* y, int64_t ys, const void* w, const void* bias, int64_t batch,
+	int64_t seqlen, int64_t dims, int width)
 {
 	const size_t esz = dtype == B200_F16 ? 2 : 4;
 	const uintptr_t amask = 4 * esz - 1;
+	// the width-4 body reads the taps of a channel and the biases of a channel quad with one vector access each
+	if (width == 4 && ((reinterpret_cast<uintptr_t>(w) & amask) != 0 || (reinterpret_cast<uintptr_t>(bias) & amask) != 0)) return false;
 	return (dtype == B200_F16 || dtype == B200_F32) && width >= 1 && width <= 4 && (reinterpret_cast<uintptr_t>(x) & amask) == 0 &&
 		(reinterpret_cast<uintptr_t>(y) & amask) == 0 && xs % 4 == 0 && ys % 4 == 0 && dims % 4 == 0 && batch > 0 && batch < 65535 &&
 		seqlen > 0 && seqlen <= 0x7fffffffLL && dims <= 0x7fffffffLL && cdiv(dims, 4) * cdiv(seqlen, 8) <= 0x7fffffffLL;

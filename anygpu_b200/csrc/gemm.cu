@@ -520,19 +520,37 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 	return B200_OK;
 }
 
+// Which tensor-core kernel a problem takes: CTA pairs on 256x256 tiles once those fill half the machine, wide 128x256 tiles once
+// they fill most of it, otherwise skinny 128x64 tiles (two CTAs per SM), with 64-row X boxes for M <= 64.
+struct GemmChoice
+{
+	bool paired, wide, tiny_m;
+};
+static GemmChoice gemm_f16_choice(int64_t M, int64_t N)
+{
+	GemmChoice c;
+	c.wide = cdiv(M, gemm::BM) * cdiv(N, 256) >= 96;
+	c.paired = cdiv(M, 256) * cdiv(N, 256) >= kNumSMs / 2;
+	c.tiny_m = !c.paired && !c.wide && M <= 64;
+	return c;
+}
+
+// true when the tensor-core kernels can take the problem: TMA needs 16-byte aligned bases and row strides
+static bool gemm_f16_tc_ok(const void* x, int64_t ldx, const void* w, const void* y, int64_t ldy, int64_t K, int64_t N)
+{
+	return K % 8 == 0 && N % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && aligned16(x) && aligned16(w) && aligned16(y);
+}
+
 static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout, __half* y, int64_t ldy, int64_t M, int64_t K,
 	int64_t N, cudaStream_t st, const __half* residual = nullptr, int64_t ldr = 0)
 {
 	using namespace gemm;
-	if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldy % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y))
-		return B200_ERR_MISALIGNED;
+	if (!gemm_f16_tc_ok(x, ldx, w, y, ldy, K, N)) return B200_ERR_MISALIGNED;
 	if (residual && (ldr % 8 != 0 || !aligned16(residual))) return B200_ERR_MISALIGNED;
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
-	// wide tiles once they fill most of the machine; otherwise skinny tiles, two CTAs per SM
-	const bool wide = cdiv(M, BM) * cdiv(N, 256) >= 96;
-	const bool paired = cdiv(M, 256) * cdiv(N, 256) >= kNumSMs / 2;  // CTA pairs on 256x256 tiles
+	const GemmChoice ch = gemm_f16_choice(M, N);
+	const bool wide = ch.wide, paired = ch.paired, tiny_m = ch.tiny_m;
 	const uint32_t bn = paired ? 128 : (wide ? 256 : 64);
-	const bool tiny_m = !paired && !wide && M <= 64;
 	CUtensorMap tmA, tmB, tmY;
 	int rc = tmap_2d_f16(&tmY, y, static_cast<uint64_t>(M), static_cast<uint64_t>(N), static_cast<uint64_t>(ldy), 64, 32);
 	if (rc) return rc;
@@ -564,10 +582,12 @@ int linear_f16_residual(const void* x, int64_t ldx, const void* w, int w_layout,
 		static_cast<const __half*>(residual), ldr);
 }
 
-// ---- f32 SIMT kernel --------------------------------------------------------------------------------------
-// 64x64 output tile, 16x16 threads, 4x4 per thread, k in slices of 16. ws_k / ws_n: element strides of W along k and n.
-__global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restrict__ X, int64_t ldx, const float* __restrict__ W,
-	int64_t ws_k, int64_t ws_n, float* __restrict__ Y, int64_t ldy, int M, int N, int K)
+// ---- SIMT kernel (fp32 tensors; f16 tensors whose shape or alignment the tensor-core kernels cannot take) -----------
+// 64x64 output tile, 16x16 threads, 4x4 per thread, k in slices of 16, fp32 accumulation in the order k = 0, 1, 2, ...
+// ws_k / ws_n: element strides of W along k and n.
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ X, int64_t ldx, const T* __restrict__ W,
+	int64_t ws_k, int64_t ws_n, T* __restrict__ Y, int64_t ldy, int M, int N, int K)
 {
 	__shared__ __align__(16) float sa[16][64 + 4];  // [k][m]
 	__shared__ __align__(16) float sb[16][64 + 4];  // [k][n]
@@ -581,14 +601,14 @@ __global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restr
 			{
 				const int kk = idx & 15, mm = idx >> 4;  // X: k contiguous
 				const int m = m0 + mm, k = k0 + kk;
-				sa[kk][mm] = (m < M && k < K) ? X[static_cast<int64_t>(m) * ldx + k] : 0.f;
+				sa[kk][mm] = (m < M && k < K) ? ldf(X + static_cast<int64_t>(m) * ldx + k) : 0.f;
 			}
 			{
 				int kk, nn;
 				if (ws_n == 1) { nn = idx & 63; kk = idx >> 6; }  // W (K,N): n contiguous
 				else { kk = idx & 15; nn = idx >> 4; }             // W (N,K): k contiguous
 				const int n = n0 + nn, k = k0 + kk;
-				sb[kk][nn] = (n < N && k < K) ? W[static_cast<int64_t>(k) * ws_k + static_cast<int64_t>(n) * ws_n] : 0.f;
+				sb[kk][nn] = (n < N && k < K) ? ldf(W + static_cast<int64_t>(k) * ws_k + static_cast<int64_t>(n) * ws_n) : 0.f;
 			}
 		}
 		__syncthreads();
@@ -612,11 +632,12 @@ __global__ void __launch_bounds__(256) gemm_f32_simt_kernel(const float* __restr
 		for (int j = 0; j < 4; ++j)
 		{
 			const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-			if (m < M && n < N) Y[static_cast<int64_t>(m) * ldy + n] = acc[i][j];
+			if (m < M && n < N) stf(Y + static_cast<int64_t>(m) * ldy + n, acc[i][j]);
 		}
 }
 
-static int gemm_f32(const float* x, int64_t ldx, const float* w, int w_layout, float* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+template <typename T>
+static int gemm_simt(const T* x, int64_t ldx, const T* w, int w_layout, T* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
 	cudaStream_t st)
 {
 	if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
@@ -624,7 +645,7 @@ static int gemm_f32(const float* x, int64_t ldx, const float* w, int w_layout, f
 	if (g.y > 65535u) return B200_ERR_UNSUPPORTED;
 	const int64_t ws_k = w_layout == B200_W_KN ? N : 1;
 	const int64_t ws_n = w_layout == B200_W_KN ? 1 : K;
-	gemm_f32_simt_kernel<<<g, 256, 0, st>>>(x, ldx, w, ws_k, ws_n, y, ldy, static_cast<int>(M), static_cast<int>(N),
+	gemm_simt_kernel<T><<<g, 256, 0, st>>>(x, ldx, w, ws_k, ws_n, y, ldy, static_cast<int>(M), static_cast<int>(N),
 		static_cast<int>(K));
 	B200_LAUNCH_CHECK();
 	return B200_OK;
@@ -643,10 +664,27 @@ extern "C" int b200_linear(int dtype, const void* x, int64_t ldx, const void* w,
 	if (M == 0) return B200_OK;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	if (dtype == B200_F16)
+	{
+		// anyGPU's tensor_linear takes any shape: what TMA cannot address (a dimension or stride that is not a multiple of 8
+		// elements, a base off a 16-byte boundary) runs on the SIMT kernel instead of being refused
+		if (!gemm_f16_tc_ok(x, ldx, w, y, ldy, K, N))
+			return gemm_simt<__half>(static_cast<const __half*>(x), ldx, static_cast<const __half*>(w), w_layout, static_cast<__half*>(y),
+				ldy, M, K, N, st);
 		return gemm_f16(static_cast<const __half*>(x), ldx, static_cast<const __half*>(w), w_layout, static_cast<__half*>(y), ldy, M,
 			K, N, st);
+	}
 	if (dtype == B200_F32)
-		return gemm_f32(static_cast<const float*>(x), ldx, static_cast<const float*>(w), w_layout, static_cast<float*>(y), ldy, M, K,
-			N, st);
+		return gemm_simt<float>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), w_layout, static_cast<float*>(y), ldy, M,
+			K, N, st);
 	return B200_ERR_UNSUPPORTED;
+}
+
+extern "C" const char* b200_linear_kernel_name(int dtype, int64_t M, int64_t K, int64_t N)
+{
+	if (dtype == B200_F32) return "gemm_simt_kernel<float>";
+	if (dtype != B200_F16 || M <= 0 || K <= 0 || N <= 0) return "";
+	if (K % 8 != 0 || N % 8 != 0) return "gemm_simt_kernel<__half>";
+	const GemmChoice c = gemm_f16_choice(M, N);
+	if (c.paired) return "gemm_f16_tcgen05_pair_kernel";
+	return c.wide ? "gemm_f16_tcgen05_kernel (128x256 tiles)" : (c.tiny_m ? "gemm_f16_tcgen05_kernel (64-row X, 128x64 tiles)" : "gemm_f16_tcgen05_kernel (128x64 tiles)");
 }

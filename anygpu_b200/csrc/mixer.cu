@@ -13,6 +13,8 @@ namespace b200 {
 struct MixerDims
 {
 	int64_t conv_dim, d_in_proj;
+	int64_t ldz;  // row stride of the in_proj output inside the workspaces: d_in_proj rounded up to 8 elements, so that its rows (and
+	              // the z | xBC | dt slices, whose offsets are multiples of 8 for headdim and d_state multiples of 8) stay 16-byte aligned
 	size_t esz;
 };
 
@@ -27,14 +29,15 @@ static bool dims_ok(const b200_mamba2_config* c, int dtype, MixerDims* m)
 	if (dtype != B200_F16 && dtype != B200_F32) return false;
 	m->conv_dim = c->d_inner + 2 * c->ngroups * c->d_state;
 	m->d_in_proj = 2 * c->d_inner + 2 * c->ngroups * c->d_state + c->nheads;
+	m->ldz = (m->d_in_proj + 7) / 8 * 8;
 	m->esz = dtype == B200_F16 ? 2 : 4;
 	return true;
 }
 
 // conv1d + the scan's dt stage in one launch (conv_dt_fused.cu), and the scan without / with chosen stages (ssd.cu)
 constexpr int kSsdStageDt = 1, kSsdStageStates = 2, kSsdStagePass = 4, kSsdStageSummary = 8;
-bool conv_dt_fused_applies(int dtype, const void* x, int64_t xs, const void* y, int64_t ys, int64_t batch, int64_t seqlen, int64_t dims,
-	int width);
+bool conv_dt_fused_applies(int dtype, const void* x, int64_t xs, const void* y, int64_t ys, const void* w, const void* bias, int64_t batch,
+	int64_t seqlen, int64_t dims, int width);
 int conv1d_tokens_with_scan_dt(int dtype, const void* x, int64_t xs, const void* w, const void* bias, void* y, int64_t ys,
 	const void* init, void* fin, int64_t batch, int64_t seqlen, int64_t dims, int width, const void* dt, int64_t dts, const float* A,
 	int a_is_log, const float* dt_bias, int dt_softplus, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, void* ssd_workspace,
@@ -102,7 +105,7 @@ static PrefillWs carve_prefill(void* base, const b200_mamba2_config* c, const Mi
 	const size_t T = static_cast<size_t>(batch) * seqlen;
 	char* p = static_cast<char*>(base);
 	size_t off = 0;
-	w.zxbcdt = p + off; off += align_up(T * m.d_in_proj * m.esz, 256);
+	w.zxbcdt = p + off; off += align_up(T * m.ldz * m.esz, 256);
 	w.xbc = p + off; off += align_up(T * m.conv_dim * m.esz, 256);
 	w.y = p + off; off += align_up(T * c->d_inner * m.esz, 256);
 	w.ssd = p + off;
@@ -140,7 +143,8 @@ static int residual_add(int dtype, void* out, int64_t ldo, const void* res, int6
 }
 
 // out = y . W_out (+ residual): the projection that ends the mixer; the residual of the layer around it rides in the epilogue
-// of the f16 tensor-core GEMM, otherwise it is added by a second kernel.
+// of the f16 tensor-core GEMM; where that kernel cannot take the shape (fp32 tensors, sizes or strides off the 8-element grid,
+// which b200_linear runs on its SIMT kernel) it is added by a second kernel.
 static int out_proj_residual(int dtype, const void* y, int64_t ldy, const void* w, int layout, void* out, int64_t ldo, int64_t T,
 	int64_t K, int64_t N, const void* residual, int64_t ldr, cudaStream_t st)
 {
@@ -170,19 +174,19 @@ static int mixer_conv_ssd(int dtype, const b200_mamba2_config* cfg, const b200_m
 	const int64_t d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
 	const size_t e = m.esz;
 	const char* dtp = zxbcdt + (d_inner + m.conv_dim) * e;
-	const bool dt_in_conv = conv_dt_fused_applies(dtype, zxbcdt + d_inner * e, m.d_in_proj, xbc, m.conv_dim, batch, seqlen, m.conv_dim,
+	const bool dt_in_conv = conv_dt_fused_applies(dtype, zxbcdt + d_inner * e, m.ldz, xbc, m.conv_dim, w->conv1d_weight, w->conv1d_bias, batch, seqlen, m.conv_dim,
 		static_cast<int>(cfg->d_conv)) && cfg->chunk <= 256 && batch * cdiv(seqlen, cfg->chunk) * cfg->nheads <= 0x7fffffffLL;
 	int rc;
 	if (dt_in_conv)
-		rc = conv1d_tokens_with_scan_dt(dtype, zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, xbc, m.conv_dim,
-			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), dtp, m.d_in_proj, w->A_log, 1, w->dt_bias,
+		rc = conv1d_tokens_with_scan_dt(dtype, zxbcdt + d_inner * e, m.ldz, w->conv1d_weight, w->conv1d_bias, xbc, m.conv_dim,
+			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), dtp, m.ldz, w->A_log, 1, w->dt_bias,
 			B200_DT_SOFTPLUS_EXACT, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, ssd, ssd_bytes, st);
 	else
-		rc = b200_causal_conv1d_tokens(dtype, zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, xbc, m.conv_dim,
+		rc = b200_causal_conv1d_tokens(dtype, zxbcdt + d_inner * e, m.ldz, w->conv1d_weight, w->conv1d_bias, xbc, m.conv_dim,
 			conv_state_in, conv_state_out, batch, seqlen, m.conv_dim, static_cast<int>(cfg->d_conv), st);
 	if (rc) return rc;
 	if (mark) stage_mark(2, st);
-	return ssd_combined_stages(dtype, xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, xbc + d_inner * e, m.conv_dim,
+	return ssd_combined_stages(dtype, xbc, m.conv_dim, dtp, m.ldz, w->A_log, 1, xbc + d_inner * e, m.conv_dim,
 		xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, initial_states, y, d_inner, ssm_state_out, batch, seqlen, cfg->nheads,
 		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ssd, ssd_bytes, st,
 		(dt_in_conv ? 0 : kSsdStageDt) | kSsdStageStates | kSsdStagePass);
@@ -210,7 +214,7 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 	const int64_t d_inner = cfg->d_inner;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 	stage_mark(0, st);
-	int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model,
+	int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.ldz, T, cfg->d_model,
 		m.d_in_proj, stream);
 	if (rc) return rc;
 	stage_mark(1, st);
@@ -218,7 +222,7 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 		conv_state_out, ssm_state_out, st, true);
 	if (rc) return rc;
 	stage_mark(3, st);
-	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,
+	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.ldz, w->norm_weight, ws.y, d_inner, T, d_inner,
 		cfg->norm_group_size, cfg->eps, stream);
 	if (rc) return rc;
 	stage_mark(4, st);
@@ -472,7 +476,7 @@ static DecodeLayout decode_layout(const b200_mamba2_config* cfg, const MixerDims
 	DecodeLayout L;
 	size_t off = 0;
 	L.zx = off;
-	off += align_up(batch * m.d_in_proj * m.esz, 256);
+	off += align_up(batch * m.ldz * m.esz, 256);
 	L.xbc = off;
 	off += align_up(batch * m.conv_dim * m.esz, 256);
 	L.y = off;
@@ -531,33 +535,33 @@ static int mixer_decode_impl(int dtype, const b200_mamba2_config* cfg, const b20
 	int rc;
 	if (fuse_in)
 	{
-		rc = decode_in_proj_conv(u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model, m.d_in_proj,
+		rc = decode_in_proj_conv(u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.ldz, batch, cfg->d_model, m.d_in_proj,
 			d_inner, m.conv_dim, static_cast<int>(cfg->d_conv), conv_state, w->conv1d_weight, w->conv1d_bias, xbc, part, st);
 		if (rc) return rc;
 	}
 	else
 	{
-		rc = b200_linear(dtype, u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.d_in_proj, batch, cfg->d_model,
+		rc = b200_linear(dtype, u_t, cfg->d_model, w->in_proj_weight, w->in_proj_layout, zx, m.ldz, batch, cfg->d_model,
 			m.d_in_proj, stream);
 		if (rc) return rc;
-		rc = b200_causal_conv1d_update(dtype, zx + d_inner * e, m.d_in_proj, conv_state, w->conv1d_weight, w->conv1d_bias, xbc,
+		rc = b200_causal_conv1d_update(dtype, zx + d_inner * e, m.ldz, conv_state, w->conv1d_weight, w->conv1d_bias, xbc,
 			m.conv_dim, batch, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
 		if (rc) return rc;
 	}
 	if (fuse_gate)
 	{
-		rc = ssm_update_gated_f16(ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1, xbc + d_inner * e,
-			m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, zx, m.d_in_proj, w->norm_weight, sumsq, batch,
+		rc = ssm_update_gated_f16(ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.ldz, w->A_log, 1, xbc + d_inner * e,
+			m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, zx, m.ldz, w->norm_weight, sumsq, batch,
 			cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, 1, st);
 		if (rc) return rc;
 		return decode_out_proj_scale(y, d_inner, w->out_proj_weight, w->out_proj_layout, out_t, cfg->d_model, batch, d_inner, cfg->d_model,
 			sumsq, static_cast<int>(cfg->nheads) * ssm_update_gated_partials(), d_inner, cfg->eps, part, st, residual, ldr);
 	}
-	rc = b200_selective_state_update(dtype, ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.d_in_proj, w->A_log, 1,
+	rc = b200_selective_state_update(dtype, ssm_state, xbc, m.conv_dim, zx + (d_inner + m.conv_dim) * e, m.ldz, w->A_log, 1,
 		xbc + d_inner * e, m.conv_dim, xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, y, d_inner, batch, cfg->nheads,
 		cfg->headdim, cfg->ngroups, cfg->d_state, 1, stream);
 	if (rc) return rc;
-	rc = b200_gated_rmsnorm(dtype, y, d_inner, zx, m.d_in_proj, w->norm_weight, y, d_inner, batch, d_inner, cfg->norm_group_size,
+	rc = b200_gated_rmsnorm(dtype, y, d_inner, zx, m.ldz, w->norm_weight, y, d_inner, batch, d_inner, cfg->norm_group_size,
 		cfg->eps, stream);
 	if (rc) return rc;
 	if (fuse_out)
@@ -647,7 +651,7 @@ extern "C" int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_con
 		if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return B200_ERR_MISALIGNED;
 		ws = carve_prefill(workspace, cfg, m, 1, T);
 		if (workspace_bytes < ws.bytes) return B200_ERR_WORKSPACE;
-		const int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model,
+		const int rc = b200_linear(dtype, u, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.ldz, T, cfg->d_model,
 			m.d_in_proj, stream);
 		if (rc) return rc;
 	}
@@ -666,12 +670,12 @@ extern "C" int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_con
 			if (cs && cs_bytes) B200_CUDA_TRY(cudaMemsetAsync(cs, 0, cs_bytes, st));
 			continue;
 		}
-		const int rc = mixer_conv_ssd(dtype, cfg, w, m, ws.zxbcdt + t0 * m.d_in_proj * e, ws.xbc + t0 * m.conv_dim * e,
+		const int rc = mixer_conv_ssd(dtype, cfg, w, m, ws.zxbcdt + t0 * m.ldz * e, ws.xbc + t0 * m.conv_dim * e,
 			ws.y + t0 * d_inner * e, ws.ssd, ws.ssd_bytes, 1, len, init, nullptr, cs, fin, st, false);
 		if (rc) return rc;
 	}
 	if (T == 0) return B200_OK;
-	int rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner,
+	int rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.ldz, w->norm_weight, ws.y, d_inner, T, d_inner,
 		cfg->norm_group_size, cfg->eps, stream);
 	if (rc) return rc;
 	return b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out, cfg->d_model, T, d_inner, cfg->d_model, stream);
@@ -700,7 +704,7 @@ static SpWs carve_sp(void* base, const b200_mamba2_config* c, const MixerDims& m
 	char* p = static_cast<char*>(base);
 	size_t off = 0;
 	const int64_t hw = c->d_conv - 1;
-	w.halo_zx = p + off; off += align_up(static_cast<size_t>(batch) * hw * m.d_in_proj * m.esz, 256);
+	w.halo_zx = p + off; off += align_up(static_cast<size_t>(batch) * hw * m.ldz * m.esz, 256);
 	w.halo_cs = p + off; off += align_up(static_cast<size_t>(batch) * m.conv_dim * hw * m.esz, 256);
 	w.halo_y = p + off; off += align_up(static_cast<size_t>(batch) * m.conv_dim * hw * m.esz, 256);
 	w.inner = p + off;
@@ -738,22 +742,22 @@ extern "C" int b200_mamba2_mixer_prefill_sp_begin(int dtype, const b200_mamba2_c
 	if (u_halo != nullptr && hw > 0)
 	{
 		// the conv inputs of the d_conv-1 tokens before the segment: project them and let the conv kernel lay them out as a state
-		rc = b200_linear(dtype, u_halo, cfg->d_model, w->in_proj_weight, w->in_proj_layout, sp.halo_zx, m.d_in_proj, batch * hw, cfg->d_model,
+		rc = b200_linear(dtype, u_halo, cfg->d_model, w->in_proj_weight, w->in_proj_layout, sp.halo_zx, m.ldz, batch * hw, cfg->d_model,
 			m.d_in_proj, stream);
 		if (rc) return rc;
-		rc = b200_causal_conv1d_tokens(dtype, sp.halo_zx + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, sp.halo_y /* unused */,
+		rc = b200_causal_conv1d_tokens(dtype, sp.halo_zx + d_inner * e, m.ldz, w->conv1d_weight, w->conv1d_bias, sp.halo_y /* unused */,
 			m.conv_dim, nullptr, sp.halo_cs, batch, hw, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
 		if (rc) return rc;
 		conv_in = sp.halo_cs;
 	}
-	rc = b200_linear(dtype, u_seg, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.d_in_proj, T, cfg->d_model, m.d_in_proj,
+	rc = b200_linear(dtype, u_seg, cfg->d_model, w->in_proj_weight, w->in_proj_layout, ws.zxbcdt, m.ldz, T, cfg->d_model, m.d_in_proj,
 		stream);
 	if (rc) return rc;
 	const char* dtp = ws.zxbcdt + (d_inner + m.conv_dim) * e;
-	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.d_in_proj, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim, conv_in,
+	rc = b200_causal_conv1d_tokens(dtype, ws.zxbcdt + d_inner * e, m.ldz, w->conv1d_weight, w->conv1d_bias, ws.xbc, m.conv_dim, conv_in,
 		conv_state_out, batch, seglen, m.conv_dim, static_cast<int>(cfg->d_conv), stream);
 	if (rc) return rc;
-	rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
+	rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.ldz, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
 		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, nullptr, ws.y, d_inner, seg_state, batch, seglen, cfg->nheads, cfg->headdim,
 		cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream,
 		kSsdStageDt | kSsdStageStates | kSsdStageSummary);
@@ -785,11 +789,11 @@ extern "C" int b200_mamba2_mixer_prefill_sp_finish(int dtype, const b200_mamba2_
 	const int64_t T = batch * seglen, d_inner = cfg->d_inner, GN = cfg->ngroups * cfg->d_state;
 	const size_t e = m.esz;
 	const char* dtp = ws.zxbcdt + (d_inner + m.conv_dim) * e;
-	int rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.d_in_proj, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
+	int rc = ssd_combined_stages(dtype, ws.xbc, m.conv_dim, dtp, m.ldz, w->A_log, 1, ws.xbc + d_inner * e, m.conv_dim,
 		ws.xbc + (d_inner + GN) * e, m.conv_dim, w->D, w->dt_bias, state_in, ws.y, d_inner, ssm_state_out, batch, seglen, cfg->nheads,
 		cfg->headdim, cfg->ngroups, cfg->d_state, cfg->chunk, B200_DT_SOFTPLUS_EXACT, ws.ssd, ws.ssd_bytes, stream, kSsdStagePass);
 	if (rc) return rc;
-	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.d_in_proj, w->norm_weight, ws.y, d_inner, T, d_inner, cfg->norm_group_size,
+	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.ldz, w->norm_weight, ws.y, d_inner, T, d_inner, cfg->norm_group_size,
 		cfg->eps, stream);
 	if (rc) return rc;
 	return b200_linear(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out_seg, cfg->d_model, T, d_inner, cfg->d_model, stream);

@@ -1,11 +1,15 @@
 // Library-wide state of the C ABI: status strings, the per-thread CUDA error record and the device error word
 // that bounded device-side waits set when they give up.
 #include "common.cuh"
+#include <atomic>
 #include <cstdlib>
 
 namespace b200 {
 
 thread_local int g_last_cuda_error = 0;
+
+static std::atomic<long long> g_launches{ 0 };
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 __device__ uint32_t g_device_error_word = 0;
 
@@ -55,7 +59,12 @@ extern "C" const char* b200_status_string(int status)
 
 extern "C" int b200_last_cuda_error(void) { return g_last_cuda_error; }
 
-extern "C" int b200_abi_version(void) { return 1; }
+extern "C" int b200_abi_version(void) { return 2; }
+
+extern "C" long long b200_launch_count(int reset)
+{
+	return reset ? g_launches.exchange(0, std::memory_order_relaxed) : g_launches.load(std::memory_order_relaxed);
+}
 
 extern "C" int b200_last_device_error(void* stream, uint32_t* detail)
 {

@@ -38,6 +38,11 @@ static int run_tc(const void* x, int64_t xs, const void* dt, int64_t dts, const 
 	int rc = B200_OK;
 	if (stages & kSsdStageDt) rc = ssd_dt_cumsum<__half>(static_cast<const __half*>(dt), dts, A, a_is_log, dt_bias, dt_softplus, d, w, st);
 	if (rc) return rc;
+	// a whole scan (no stage left to another call): one kernel where it covers the shape and the problem is large enough in
+	// (batch x heads) for it
+	if ((stages & (kSsdStageStates | kSsdStagePass | kSsdStageSummary)) == (kSsdStageStates | kSsdStagePass) &&
+		ssd_fused_supported(d, x, xs, Bm, bs, Cm, cs, y, ys, init, fin) && ssd_fused_preferred(d))
+		return ssd_fused_tc(xh, xs, bh, bs, ch, cs, D, init, static_cast<__half*>(y), ys, fin, d, w, st);
 	if (stages & kSsdStageStates) rc = ssd_chunk_state_tc(xh, xs, bh, bs, d, w, st);
 	if (rc) return rc;
 	if (stages & kSsdStageSummary) rc = ssd_state_passing(nullptr, fin, true, d, w, st, false);

@@ -71,6 +71,15 @@ int ssd_chunk_state_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs
 int ssd_chunk_scan_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D, __half* y,
 	int64_t ys, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
 
+// The whole scan after the dt stage as one kernel (ssd_fused.cu): chunk states, state passing and chunk scan without the
+// per-chunk states ever reaching HBM. `supported`: shapes and alignments it covers; `preferred`: whether it is expected to beat
+// the staged kernels for this problem size (B200_SSD_FUSED=1 / 0 in the environment forces the answer).
+bool ssd_fused_supported(const SsdDims& d, const void* x, int64_t xs, const void* Bm, int64_t bs, const void* Cm, int64_t cs, const void* y,
+	int64_t ys, const float* init, const float* fin);
+bool ssd_fused_preferred(const SsdDims& d);
+int ssd_fused_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D,
+	const float* init, __half* y, int64_t ys, float* fin, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
+
 template <typename T>
 int ssd_chunk_scan_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const T* Cm, int64_t cs, const float* D, T* y, int64_t ys,
 	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);

@@ -1,0 +1,451 @@
+// SSD chunked scan as ONE tensor-core kernel for f16 activations: chunk states, state passing and chunk scan in a single
+// pass over the sequence (the dt stage, softplus and in-chunk cumulative sums, still runs before it).
+//
+// One CTA owns one (batch, head) pair and walks its sequence in blocks of 128 tokens, carrying the [P x N] state in registers
+// (fp32). Per block, with l, s = token inside the block, dA = the cumulative sum of dt*A up to and including a token:
+//   CB  = C . B^T                                              tcgen05, M = l (128), N = s (128), K = n
+//   S   = CB o exp(dA[l] - dA[s]) dt[s] o (s <= l), S[l,l] += D  CUDA cores: TMEM -> f16 tile in shared memory
+//   Y   = S . X  +  rowdec[l] * (C . prev^T)                   tcgen05, M = l, N = p, K = s and K = n; rowdec = exp(dA[l] - dA[before block])
+//   ST  = X^T . (w o B),  w[l] = exp(dA[last] - dA[l]) dt[l]    tcgen05, M = p, N = n, K = l (B is scaled in place once CB is done)
+//   state <- exp(dA[last] - dA[before block]) state + ST        registers; its f16 copy is the `prev` operand of the next block
+// which is the arithmetic of mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:51-160) with the chunk
+// states never leaving the SM: x, B and C are read once, y is written once, and nothing else touches HBM. The result does not
+// depend on how the sequence is cut into blocks, so the public `chunk` (128 or 256) only fixes where the dt stage restarts its
+// cumulative sums. Two CTAs share an SM (104 KiB of shared memory, 256 tensor-memory columns each); while one waits for its
+// loads or its MMAs the other computes.
+// Every decay is the exponential of a non-positive difference. Every mbarrier wait is bounded; on a timeout the CTA records a
+// code, drains and frees its tensor memory.
+#include <cstdlib>
+
+#include "ssd_common.cuh"
+#include "tcgen05.cuh"
+
+namespace b200 {
+
+using namespace tc;
+
+namespace sfused {
+constexpr int THREADS = 256;
+constexpr int QI = 128;                  // tokens per block
+constexpr int TILE = QI * 128;           // a [128 rows][64 f16] tile: 16 KiB
+constexpr int OFF_C = 0;                 // C  [128 l][64 n]   K-major A operand of CB and of C.prev^T
+constexpr int OFF_B = OFF_C + TILE;      // B  [128 s][64 n]   K-major B operand of CB; scaled rows: MN-major B operand of ST
+constexpr int OFF_X = OFF_B + TILE;      // X  [128 s][64 p]   MN-major B operand of S.X and MN-major A operand of ST
+constexpr int OFF_S = OFF_X + TILE;      // S  2 x [128 l][64 s]  K-major A operand (one tile per 64-wide K-block)
+constexpr int OFF_P = OFF_S + 2 * TILE;  // prev [64 p][64 n]  K-major B operand of C.prev^T
+constexpr int OFF_Y = OFF_P + TILE / 2;  // y staging [128 l][64 p], 128-byte swizzled like the TMA store expects
+constexpr int TOTAL = OFF_Y + TILE + 1024;
+constexpr uint32_t TMEM_COLS = 256;      // CB [0,128) (ST reuses [0,64) once S is written) | Y [128,192) | C.prev^T [192,256)
+constexpr float kLog2e = 1.4426950408889634f;
+static_assert(2 * (TOTAL + 4096) <= 232448, "two CTAs must fit one SM");
+}  // namespace sfused
+
+__device__ __forceinline__ float ex2f(float v)
+{
+	float r;
+	asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+	return r;
+}
+
+__global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmX,
+	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmY,
+	const float* __restrict__ D, const float* __restrict__ dt, const float* __restrict__ dacs, const float* __restrict__ colf,
+	const float* init, float* fin /* may alias init: every thread reads its slice first */, int64_t seqlen, int H, int G, int Q, int nchunks, uint32_t* err_word)
+{
+	using namespace sfused;
+	extern __shared__ uint8_t smem_raw[];
+	__shared__ uint64_t bar_in, bar_cb, bar_mma;
+	__shared__ uint32_t tmem_slot;
+	__shared__ int abort_flag;
+	__shared__ __align__(16) float sc_dA[QI], sc_dt[QI], sc_cf[QI], sc_rowdec[QI], sc_w[QI];
+	__shared__ float sc_dec;
+
+	const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+	uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int q = warp & 3;        // TMEM lane quadrant this warp may read
+	const int half = warp >> 2;    // which 64-wide K-block of S / which 32 columns of an accumulator this warp owns
+	const int r = q * 32 + lane;   // row (l, or p for the state) inside the block
+	const int h = static_cast<int>(blockIdx.x % H);
+	const int64_t b = blockIdx.x / H;
+	const int g = h / (H / G);
+	const int nsub = nchunks * (Q / QI);
+	const int64_t bh = b * H + h;
+	const float* dacs_bh = dacs + bh * nchunks * static_cast<int64_t>(Q);
+	const float* dt_bh = dt + bh * nchunks * static_cast<int64_t>(Q);
+	const float* colf_bh = colf + bh * nchunks * static_cast<int64_t>(Q);
+	const float dh = D ? __ldg(D + h) : 0.f;
+	volatile int* abortp = &abort_flag;
+	const uint32_t in = smem_u32(&bar_in), cbb = smem_u32(&bar_cb), mmab = smem_u32(&bar_mma);
+
+	if (threadIdx.x == 0)
+	{
+		abort_flag = 0;
+		mbar_init(in, 1);
+		mbar_init(cbb, 1);
+		mbar_init(mmab, 1);
+		fence_mbar_init();
+		prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmY);
+	}
+	if (warp == 0)
+	{
+		tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
+		tmem_relinquish();
+	}
+	tc_fence_before();
+	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_slot;
+	const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+
+	// tiles of block j: rows past the end of the sequence arrive as zeros
+	auto issue_loads = [&](int j) {
+		const int t0 = j * QI;
+		mbar_arrive_expect_tx(in, 3 * TILE);
+#pragma unroll
+		for (int i = 0; i < 2; ++i)
+		{
+			tma_load_3d(base + OFF_C + i * 8192, &tmC, in, g * 64, t0 + i * 64, static_cast<int>(b));
+			tma_load_3d(base + OFF_B + i * 8192, &tmB, in, g * 64, t0 + i * 64, static_cast<int>(b));
+			tma_load_3d(base + OFF_X + i * 8192, &tmX, in, h * 64, t0 + i * 64, static_cast<int>(b));
+		}
+	};
+	if (threadIdx.x == 0) issue_loads(0);
+
+	// per-row scalars of the next block, fetched one block ahead (warps 0-3: thread = row)
+	float nx_dA = 0.f, nx_dt = 0.f, nx_cf = 0.f, nx_last = 0.f, nx_base = 0.f;
+	auto fetch_scalars = [&](int j) {
+		if (warp < 4 && j < nsub)
+		{
+			const int o = j * QI;
+			nx_dA = __ldg(dacs_bh + o + r);
+			nx_dt = __ldg(dt_bh + o + r);
+			nx_cf = __ldg(colf_bh + o + r);
+			nx_last = __ldg(dacs_bh + o + QI - 1);
+			nx_base = (o % Q) != 0 ? __ldg(dacs_bh + o - 1) : 0.f;  // the cumulative sums restart at every public chunk
+		}
+	};
+	fetch_scalars(0);
+
+	// the state: thread (q < 2) owns row p = r, columns n = half*32 .. +31
+	float state[32];
+#pragma unroll
+	for (int e = 0; e < 32; ++e) state[e] = 0.f;
+	if (q < 2)
+	{
+		if (init)
+		{
+			const float4* ip = reinterpret_cast<const float4*>(init + (bh * 64 + r) * 64 + half * 32);
+#pragma unroll
+			for (int v = 0; v < 8; ++v)
+			{
+				const float4 t = ip[v];
+				state[4 * v] = t.x; state[4 * v + 1] = t.y; state[4 * v + 2] = t.z; state[4 * v + 3] = t.w;
+			}
+		}
+		uint8_t* prow = gen + OFF_P + r * 128;
+#pragma unroll
+		for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(prow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(state + v * 8);
+	}
+	{
+		// the parts of S above the diagonal stay zero for the whole kernel
+		Half8 zero;
+#pragma unroll
+		for (int e = 0; e < 4; ++e) zero.h[e] = __floats2half2_rn(0.f, 0.f);
+		for (int i = threadIdx.x; i < 2 * TILE / 16; i += THREADS) *reinterpret_cast<Half8*>(gen + OFF_S + i * 16) = zero;
+	}
+	fence_proxy_async_smem();
+	__syncthreads();
+
+	constexpr uint32_t idesc_cb = make_idesc_f16(QI, QI, 0);
+	constexpr uint32_t idesc_y = make_idesc_f16(QI, 64, 1);      // B operand (x) MN-major
+	constexpr uint32_t idesc_z = make_idesc_f16(QI, 64, 0);
+	constexpr uint32_t idesc_st = make_idesc_f16(128, 64, 1, 1);  // A (x) and B (scaled B) MN-major
+	uint32_t fail_site = 0;
+
+	for (int j = 0; j < nsub; ++j)
+	{
+		const uint32_t par = static_cast<uint32_t>(j) & 1u;
+		// ---- (A) scalars of this block; CB = C . B^T -------------------------------------------------------------------
+		if (warp < 4)
+		{
+			sc_dA[r] = nx_dA;
+			sc_dt[r] = nx_dt;
+			sc_cf[r] = nx_cf;
+			sc_rowdec[r] = ex2f((nx_dA - nx_base) * kLog2e);
+			sc_w[r] = ex2f((nx_last - nx_dA) * kLog2e) * nx_dt;
+			if (r == QI - 1) sc_dec = ex2f((nx_dA - nx_base) * kLog2e);
+		}
+		if (threadIdx.x == 0)
+		{
+			bulk_wait_group_read<0>();  // the previous block's y store has read its staging tile
+			if (mbar_wait(in, par, abortp))
+			{
+				tc_fence_after();
+				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_C, 16, 1024);
+				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_B, 16, 1024);
+#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_cb, k != 0 ? 1u : 0u);
+				mma_commit(cbb);
+			}
+			else
+				fail_site = kErrProducerWait;
+		}
+		__syncthreads();
+		if (*abortp) break;
+
+		// ---- (B) S tiles from CB; B rows scaled in place ----------------------------------------------------------------
+		const float dl2 = sc_dA[r] * kLog2e;
+		fetch_scalars(j + 1);
+		if (mbar_wait(cbb, par, abortp))
+		{
+			tc_fence_after();
+			const int wrow0 = q * 32;
+#pragma unroll
+			for (int ch = 0; ch < 2; ++ch)
+			{
+				const int s0 = half * 64 + ch * 32;  // first of 32 columns
+				if (s0 > wrow0 + 31) continue;      // above the diagonal: stays zero
+				uint32_t cbv[32];
+				tmem_ld_32x32(t_lane + static_cast<uint32_t>(s0), cbv);
+				uint8_t* srow = gen + OFF_S + half * TILE + r * 128;
+				if (half * 64 + 63 < wrow0)
+				{
+					// K-block entirely below the diagonal: exp(dA[l] - dA[s]) dt[s] = exp(dA[l] - dA[block end]) * colf[s], both factors <= 1
+					const float rk = ex2f(fmaf(sc_dA[half * 64 + 63], -kLog2e, dl2));
+					const float4* cfp = reinterpret_cast<const float4*>(sc_cf + s0);
+					tmem_ld_wait();
+#pragma unroll
+					for (int v = 0; v < 4; ++v)
+					{
+						float o[8];
+#pragma unroll
+						for (int hq = 0; hq < 2; ++hq)
+						{
+							const float4 cf = cfp[v * 2 + hq];
+							const float cfa[4] = { cf.x, cf.y, cf.z, cf.w };
+#pragma unroll
+							for (int e = 0; e < 4; ++e) o[hq * 4 + e] = __uint_as_float(cbv[v * 8 + hq * 4 + e]) * (rk * cfa[e]);
+						}
+						*reinterpret_cast<Half8*>(srow + (((ch * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
+					}
+				}
+				else
+				{
+					// crossed by the diagonal: exponential of the (non-positive) difference, causal mask, D on the diagonal
+					const float4* dsp = reinterpret_cast<const float4*>(sc_dA + s0);
+					const float4* dtp = reinterpret_cast<const float4*>(sc_dt + s0);
+					tmem_ld_wait();
+#pragma unroll
+					for (int v = 0; v < 4; ++v)
+					{
+						float o[8];
+#pragma unroll
+						for (int hq = 0; hq < 2; ++hq)
+						{
+							const float4 ds = dsp[v * 2 + hq];
+							const float4 dv = dtp[v * 2 + hq];
+							const float dsa[4] = { ds.x, ds.y, ds.z, ds.w };
+							const float dta[4] = { dv.x, dv.y, dv.z, dv.w };
+#pragma unroll
+							for (int e = 0; e < 4; ++e)
+							{
+								const int jj = v * 8 + hq * 4 + e;
+								const float wgt = ex2f(fmaf(dsa[e], -kLog2e, dl2)) * dta[e];
+								float val = (s0 + jj <= r) ? __uint_as_float(cbv[jj]) * wgt : 0.f;
+								if (s0 + jj == r) val += dh;
+								o[hq * 4 + e] = val;
+							}
+						}
+						*reinterpret_cast<Half8*>(srow + (((ch * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
+					}
+				}
+			}
+			// B[l, :] *= w[l] (a row-wise scale keeps every element where the swizzle put it). 1024 16-byte pieces: 12 per thread
+			// for the two warps without S work, 4 per thread for the two with the least.
+			{
+				int first = -1, count = 0;
+				if (warp == 4 || warp == 5) { first = (warp - 4) * 32 + lane; count = 12; }
+				else if (warp == 0 || warp == 6) { first = 768 + (warp == 6 ? 32 : 0) + lane; count = 4; }
+				for (int i = 0; i < count; ++i)
+				{
+					const int idx = first + i * 64;
+					Half8* p = reinterpret_cast<Half8*>(gen + OFF_B + idx * 16);
+					float f[8];
+					unpack8(*p, f);
+					const float sc = sc_w[idx >> 3];
+#pragma unroll
+					for (int e = 0; e < 8; ++e) f[e] *= sc;
+					*p = pack8(f);
+				}
+			}
+		}
+		else
+			fail_site = kErrScanWait;
+		fence_proxy_async_smem();
+		tc_fence_before();
+		__syncthreads();
+		if (*abortp) break;
+
+		// ---- (C) Y = S . X, Z = C . prev^T, ST = X^T . Bs ----------------------------------------------------------------
+		if (threadIdx.x == 0)
+		{
+			tc_fence_after();
+#pragma unroll
+			for (int kb = 0; kb < 2; ++kb)
+			{
+				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_S + kb * TILE, 16, 1024);
+				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_X + kb * 8192, 8192, 1024);
+#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					mma_f16_ss(tmem_base + 128u, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
+						(kb | k) != 0 ? 1u : 0u);
+			}
+			{
+				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_C, 16, 1024);
+				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_P, 16, 1024);
+#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					mma_f16_ss(tmem_base + 192u, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_z, k != 0 ? 1u : 0u);
+			}
+#pragma unroll
+			for (int kb = 0; kb < 2; ++kb)
+			{
+				// M = 128 although the state has 64 rows (p): rows 64-127 multiply whatever follows the x tile and are never read
+				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_X + kb * 8192, 8192, 1024);
+				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_B + kb * 8192, 8192, 1024);
+#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 128), b_desc + static_cast<uint64_t>(k * 128), idesc_st,
+						(kb | k) != 0 ? 1u : 0u);
+			}
+			mma_commit(mmab);
+		}
+
+		// ---- (D) y = Y + rowdec * Z; state update; next block's loads ---------------------------------------------------
+		if (mbar_wait(mmab, par, abortp))
+		{
+			tc_fence_after();
+			if (threadIdx.x == 0 && j + 1 < nsub) issue_loads(j + 1);
+			uint32_t yr[32], zr[32];
+			tmem_ld_32x32(t_lane + 128u + static_cast<uint32_t>(half * 32), yr);
+			tmem_ld_32x32(t_lane + 192u + static_cast<uint32_t>(half * 32), zr);
+			tmem_ld_wait();
+			const float rd = sc_rowdec[r];
+			uint8_t* yrow = gen + OFF_Y + r * 128;
+#pragma unroll
+			for (int v = 0; v < 4; ++v)
+			{
+				float o[8];
+#pragma unroll
+				for (int e = 0; e < 8; ++e) o[e] = fmaf(rd, __uint_as_float(zr[v * 8 + e]), __uint_as_float(yr[v * 8 + e]));
+				*reinterpret_cast<Half8*>(yrow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
+			}
+			if (q < 2)
+			{
+				uint32_t sv[32];
+				tmem_ld_32x32(t_lane + static_cast<uint32_t>(half * 32), sv);
+				tmem_ld_wait();
+				const float dec = sc_dec;
+#pragma unroll
+				for (int e = 0; e < 32; ++e) state[e] = fmaf(dec, state[e], __uint_as_float(sv[e]));
+				uint8_t* prow = gen + OFF_P + r * 128;
+#pragma unroll
+				for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(prow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(state + v * 8);
+			}
+		}
+		else
+			fail_site = kErrEpilogueWait;
+		fence_proxy_async_smem();
+		tc_fence_before();
+		__syncthreads();
+		if (*abortp) break;
+		if (threadIdx.x == 0)
+		{
+			const int t0 = j * QI;
+			// rows past the end of the sequence are clipped by the store; a box that starts past it is not issued at all
+			if (t0 < seqlen) tma_store_3d(&tmY, base + OFF_Y, h * 64, t0, static_cast<int>(b));
+			if (t0 + 64 < seqlen) tma_store_3d(&tmY, base + OFF_Y + 8192, h * 64, t0 + 64, static_cast<int>(b));
+			bulk_commit_group();
+		}
+	}
+
+	if (!*abortp && fin != nullptr && q < 2)
+	{
+		float4* fp = reinterpret_cast<float4*>(fin + (bh * 64 + r) * 64 + half * 32);
+#pragma unroll
+		for (int v = 0; v < 8; ++v) fp[v] = make_float4(state[4 * v], state[4 * v + 1], state[4 * v + 2], state[4 * v + 3]);
+	}
+	if (threadIdx.x == 0) bulk_wait_group<0>();  // stores must have left shared memory before the CTA exits
+	if (*abortp)
+	{
+		if (fail_site != 0 && lane == 0) report_timeout(err_word, fail_site);
+		for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // loads that may still be in flight land before the CTA's memory is released
+	}
+	tc_fence_before();
+	__syncthreads();
+	if (warp == 0)
+	{
+		tc_fence_after();
+		tmem_dealloc(tmem_base, TMEM_COLS);
+	}
+}
+
+// Shapes the one-kernel scan covers (the rest takes the staged kernels).
+bool ssd_fused_supported(const SsdDims& d, const void* x, int64_t xs, const void* Bm, int64_t bs, const void* Cm, int64_t cs, const void* y,
+	int64_t ys, const float* init, const float* fin)
+{
+	if (d.P != 64 || d.N != 64 || (d.Q != 128 && d.Q != 256)) return false;
+	if (xs % 8 || bs % 8 || cs % 8 || ys % 8) return false;
+	if (!aligned16(x) || !aligned16(Bm) || !aligned16(Cm) || !aligned16(y)) return false;
+	if ((init && !aligned16(init)) || (fin && !aligned16(fin))) return false;
+	if (d.batch > 0x7fffffffLL || d.seqlen > 0x7fffffffLL || d.batch * d.H > 0x7fffffffLL) return false;
+	return true;
+}
+
+// 1: always, 0: never, -1: by size (environment variable B200_SSD_FUSED, read on every call so that a test can switch it)
+static int fused_override()
+{
+	const char* e = std::getenv("B200_SSD_FUSED");
+	if (!e || !*e) return -1;
+	return e[0] == '0' ? 0 : 1;
+}
+
+// The one-kernel scan walks a sequence block by block (about 2.5 us per 128 tokens, whatever the number of (batch, head) pairs
+// up to the 296 CTAs the GPU holds), the staged kernels spread the chunks of a sequence over the GPU: a few very long sequences
+// are faster staged.
+bool ssd_fused_preferred(const SsdDims& d)
+{
+	const int o = fused_override();
+	if (o >= 0) return o == 1;
+	const double waves = static_cast<double>(cdiv(d.batch * d.H, 2 * kNumSMs));
+	const double nsub = static_cast<double>(d.nchunks) * (d.Q / sfused::QI);
+	const double fused_us = waves * nsub * 2.6 + 8.0;
+	const double staged_us = 35.0 + static_cast<double>(d.batch) * d.seqlen * d.H * 0.22e-3;
+	return fused_us < staged_us;
+}
+
+int ssd_fused_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D,
+	const float* init, __half* y, int64_t ys, float* fin, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st)
+{
+	CUtensorMap tmX, tmB, tmC, tmY;
+	const uint64_t L = static_cast<uint64_t>(d.seqlen), Bt = static_cast<uint64_t>(d.batch);
+	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(xs), L * xs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(bs), L * bs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmC, Cm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(cs), L * cs, 64, 64);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmY, y, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(ys), L * ys, 64, 64);
+	if (rc) return rc;
+	static bool smem_ok[64] = {};
+	B200_CUDA_TRY(allow_dynamic_smem(ssd_fused_tc_kernel, sfused::TOTAL, smem_ok));
+	const unsigned grid = static_cast<unsigned>(d.batch * d.H);
+	ssd_fused_tc_kernel<<<grid, sfused::THREADS, sfused::TOTAL, st>>>(tmX, tmB, tmC, tmY, D, w.dt, w.dacs, w.colf, init, fin, d.seqlen, d.H, d.G,
+		d.Q, d.nchunks, device_error_word());
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+}  // namespace b200

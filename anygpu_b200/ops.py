@@ -128,15 +128,17 @@ def _tok_stride(t, inner):
 
 
 def tensor_mamba_chunk_scan_combined(x, dt, A, B, C, chunk_size, D=None, dt_bias=None, initial_states=None, a_is_log=False,
-                                     exact_final_state=False):
+                                     exact_final_state=False, final_states_out=None):
     """Argument order of mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:167-172), dt_softplus on.
     x (b,l,H,P), dt (b,l,H), A (H) fp32, B/C (b,l,G,N), D (H) fp32, dt_bias (H) fp32, initial_states (b,H,P,N) fp32.
     Returns (y (b,l,H,P), final_states (b,H,P,N) fp32). When l is not a multiple of chunk_size, final_states follows the
-    reference script (padded positions decay it) unless exact_final_state is set (state after the last real token)."""
+    reference script (padded positions decay it) unless exact_final_state is set (state after the last real token).
+    final_states_out: where to write final_states (may be the initial_states tensor itself)."""
     b, l, H, P = x.shape
     G, N = B.shape[2], B.shape[3]
     y = torch.empty((b, l, H, P), dtype=x.dtype, device=x.device)
-    fs = torch.empty((b, H, P, N), dtype=torch.float32, device=x.device)
+    fs = final_states_out if final_states_out is not None else torch.empty((b, H, P, N), dtype=torch.float32, device=x.device)
+    assert fs.dtype == torch.float32 and fs.is_contiguous() and tuple(fs.shape) == (b, H, P, N)
     lib = capi.load()
     nbytes = lib.b200_mamba_chunk_scan_combined_workspace_bytes(b, l, H, P, G, N, chunk_size)
     ws = _workspace(nbytes, x.device)

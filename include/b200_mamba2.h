@@ -65,6 +65,9 @@ const char* b200_status_string(int status);
 int b200_last_cuda_error(void);
 /* ABI version; bumped when a signature changes. */
 int b200_abi_version(void);
+/* Number of kernel launches the library has issued in this process since the last call with reset != 0 (a benchmark harness
+ * counts the launches of its timed region with it). No counterpart in anyGPU. */
+long long b200_launch_count(int reset);
 /* Reads (and clears) the device-side error word that bounded waits set. Synchronises `stream`.
  * Returns B200_OK or B200_ERR_DEVICE_TIMEOUT; *detail (optional) receives the raw word. */
 int b200_last_device_error(void* stream, uint32_t* detail);
@@ -72,10 +75,13 @@ int b200_last_device_error(void* stream, uint32_t* detail);
 /* ---- Y[M,N] = X[M,K] . W ------------------------------------------------------------------------------
  * Replaces opt2::cu_tensor_mm_f16 (srcs/kernels/cuda/mm_ops.cu:231-350) and cu_tensor_mm_f32_opt0
  * (mm_ops.cu:7-51) behind tensor_mm / tensor_linear (srcs/ops/mm_ops.hpp:48-71,206-232).
- * f16: tcgen05 tensor-core kernel, fp32 accumulation, K % 8 == 0, N % 8 == 0, ldx % 8 == 0, ldy % 8 == 0.
- * f32: exact fp32 SIMT kernel (any shape).  ldx / ldy: row strides of X and Y in elements. */
+ * f16: tcgen05 tensor-core kernels with fp32 accumulation when K, N, ldx, ldy are multiples of 8 and x, w, y start on 16-byte
+ * boundaries (what TMA can address); any other f16 shape runs on a SIMT kernel (fp32 accumulation), as tensor_linear accepts
+ * every shape. f32: exact fp32 SIMT kernel.  ldx / ldy: row strides of X and Y in elements. */
 int b200_linear(int dtype, const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy,
 	int64_t M, int64_t K, int64_t N, void* stream);
+/* Name of the kernel b200_linear launches for a problem of this size (for aligned operands): what a profile of the call shows. */
+const char* b200_linear_kernel_name(int dtype, int64_t M, int64_t K, int64_t N);
 
 /* ---- causal conv1d + SiLU, (batch, dims, seq_len) layout ---------------------------------------------------
  * Replaces cu_tensor_causal_conv1d_f32 (srcs/kernels/cuda/causal_conv1d.cu:78-101) behind

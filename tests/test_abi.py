@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     lib = capi.load()
     for name in declared_functions():
         assert hasattr(lib, name), name
-    assert lib.b200_abi_version() == 1
+    assert lib.b200_abi_version() == 2
     assert lib.b200_status_string(0) == b"ok"
     assert lib.b200_status_string(-4) == b"device-side wait timed out"
 
@@ -37,7 +37,12 @@ def test_null_and_shape_validation_needs_no_gpu():
     assert lib.b200_linear(capi.F16, one, 8, one, 0, one, 8, 1, 0, 8, None) == -1
     assert lib.b200_linear(capi.F16, one, 4, one, 0, one, 8, 1, 8, 8, None) == -1  # ldx < K
     assert lib.b200_linear(capi.F16, one, 8, one, 7, one, 8, 1, 8, 8, None) == -6  # unknown weight layout
-    assert lib.b200_linear(capi.F16, one, 12, one, 0, one, 8, 4, 12, 8, None) == -2  # K % 8 != 0 for the f16 kernel
+    # shapes TMA cannot address (K % 8 != 0) are routed to the SIMT kernel, like every fp32 problem
+    assert lib.b200_linear_kernel_name(capi.F16, 4, 12, 8) == b"gemm_simt_kernel<__half>"
+    assert lib.b200_linear_kernel_name(capi.F32, 4, 16, 8) == b"gemm_simt_kernel<float>"
+    assert lib.b200_linear_kernel_name(capi.F16, 8192, 2048, 8384) == b"gemm_f16_tcgen05_pair_kernel"
+    assert lib.b200_linear_kernel_name(capi.F16, 64, 2560, 10448).startswith(b"gemm_f16_tcgen05_kernel")
+    assert lib.b200_launch_count(1) >= 0 and lib.b200_launch_count(0) == 0
     assert lib.b200_causal_conv1d(capi.F16, one, one, one, one, 1, 8, 8, 5, None) == -1  # width > 4
     assert lib.b200_causal_conv1d(capi.F16, one, None, one, one, 1, 8, 8, 4, None) == -7
     assert lib.b200_causal_conv1d(7, one, one, one, one, 1, 8, 8, 4, None) == -6

@@ -59,6 +59,37 @@ def test_cfg2_first_chunk_matches_oracle(cfg2_run):
     assert rel_l2(got, want) < 2e-3
 
 
+def test_cfg2_last_chunk_with_carried_state_matches_oracle(cfg2_run, ops):
+    """The LAST chunk (tokens 1792..2047) of sequence 3 at full width: the oracle runs that one chunk operator by operator
+    (f16 rounding at the operator boundaries) from the state the GPU carried through the first seven chunks, with the three
+    tokens before the chunk as conv1d history. Checks a late chunk - decays, carried state and conv history included - where
+    the first-chunk test sees none of them."""
+    cfg, w, u, mixer, ud, out, _ = cfg2_run
+    t0, t1 = 1792, 2048
+    d_inner, H, P, G, N, W = cfg["d_inner"], cfg["nheads"], cfg["headdim"], cfg["ngroups"], cfg["d_state"], cfg["d_conv"]
+    conv_dim = d_inner + 2 * G * N
+    cache = ops.ZambaMambaCache.zeros(cfg, 1, torch.float16)
+    mixer.prefill(ud[3:4, :t0].contiguous(), cache)
+    state = host(cache.ssm_state)
+    r16 = orc.round_f16
+    zx = r16(orc.linear(u[3, t0 - (W - 1):t1], w["in_proj_weight"]))                       # [259, d_in_proj]
+    xbc_in = np.ascontiguousarray(zx[:, d_inner:d_inner + conv_dim].T[None])                 # (1, conv_dim, 259)
+    xbc = r16(orc.causal_conv1d(xbc_in, w["conv1d_weight"], w["conv1d_bias"]))[0, :, W - 1:].T  # drop the history columns
+    xbc = np.ascontiguousarray(xbc)[None]                                                      # (1, 256, conv_dim)
+    zx = zx[W - 1:]
+    y, fs = orc.ssd_chunk_scan(np.ascontiguousarray(xbc[..., :d_inner]).reshape(1, t1 - t0, H, P),
+                               np.ascontiguousarray(zx[None, :, d_inner + conv_dim:]), -np.exp(w["A_log"]),
+                               np.ascontiguousarray(xbc[..., d_inner:d_inner + G * N]).reshape(1, t1 - t0, G, N),
+                               np.ascontiguousarray(xbc[..., d_inner + G * N:]).reshape(1, t1 - t0, G, N), cfg["chunk"], D=w["D"],
+                               dt_bias=w["dt_bias"], initial_states=state)
+    g = r16(orc.gated_rmsnorm(r16(y).reshape(t1 - t0, d_inner), np.ascontiguousarray(zx[:, :d_inner]), w["norm_weight"], cfg["eps"]))
+    want = r16(orc.linear(g, w["out_proj_weight"]))
+    got = host(out[3, t0:t1])
+    assert_close_f16(got, want, "cfg2 last chunk of sequence 3 from the carried state", max_fail_fraction=1e-4)
+    full_cache = cfg2_run[6]
+    assert_close_f16(host(full_cache.ssm_state[3:4]), fs, "cfg2 final state of sequence 3 through the last chunk", max_fail_fraction=1e-5)
+
+
 def test_cfg2_batch_independence_is_bit_exact(cfg2_run):
     cfg, w, u, mixer, ud, out, _ = cfg2_run
     alone = mixer.prefill(ud[2:3].contiguous())

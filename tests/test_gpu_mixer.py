@@ -71,6 +71,30 @@ def test_mixer_prefill_f16(ops, cfg, layout):
     assert_close_f16(host(cache.conv_state), want["conv_state"], "conv state")
 
 
+@pytest.mark.parametrize("nheads,d_state", [(4, 64), (3, 16), (12, 64)])
+def test_mixer_f16_head_counts_off_the_8_element_grid(ops, nheads, d_state):
+    """d_in_proj = 2 d_inner + 2 G N + nheads is a multiple of 8 only when nheads is: with 4, 3 or 12 heads the projection
+    runs on the SIMT GEMM and the in_proj output keeps a padded row stride inside the workspace. Prefill, states and a decode
+    step against the oracle."""
+    cfg = dict(batch=2, seqlen=200, d_model=128, d_inner=nheads * 64, nheads=nheads, headdim=64, d_state=d_state, ngroups=1, d_conv=4,
+               chunk=64, eps=1e-5)
+    assert (2 * cfg["d_inner"] + 2 * d_state + nheads) % 8 != 0
+    w = f16w(synth.make_weights(cfg, 21))
+    u = synth.to_f16_values(synth.make_input(cfg, 21, batch=2, seqlen=201))
+    want = orc.mixer_prefill(u[:, :200], w, dict(cfg, chunk=8), f16io=True)  # 200 = 25 chunks of 8: no padding in the oracle
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16))
+    cache = ops.ZambaMambaCache.zeros(cfg, 2, torch.float16)
+    ud = torch.from_numpy(u).cuda().half()
+    out = host(mixer.prefill(ud[:, :200].contiguous(), cache))
+    assert_close_f16(out, want["out"], f"mixer out, {nheads} heads", max_fail_fraction=1e-4)
+    assert_close_f16(host(cache.ssm_state), want["final_state"], "final ssm state", max_fail_fraction=1e-5)
+    assert_close_f16(host(cache.conv_state), want["conv_state"], "conv state")
+    ocs, oss = want["conv_state"].copy(), want["final_state"].copy()
+    got = host(mixer.decode(ud[:, 200].contiguous(), cache))
+    wd = orc.mixer_decode(np.ascontiguousarray(u[:, 200]), w, cfg, ocs, oss, f16io=True)
+    assert_close_f16(got, wd, f"decode step, {nheads} heads", max_fail_fraction=1e-3)
+
+
 def test_mixer_prefill_host_call_equals_device_call(ops):
     cfg = SMALL
     w = f16w(synth.make_weights(cfg, 2))

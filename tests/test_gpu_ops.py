@@ -96,6 +96,30 @@ def test_conv1d_token_layout_strided_with_states(ops, dims, stride, off, dtype):
     (assert_close_f16 if dtype == "f16" else assert_abs)(host(y0), want0, "conv tokens zero pad")
 
 
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_conv1d_token_layout_weight_and_bias_views_off_the_vector_grid(ops, dtype):
+    """Weights and biases that are views into larger buffers at an element offset that is not a multiple of 4: the vectorised
+    body (one access per channel's 4 taps, one per 4 biases) cannot take them; the call must still give the oracle's result."""
+    r = np.random.default_rng(23)
+    b, l, dims, w = 2, 40, 64, 4
+    td = torch.float16 if dtype == "f16" else torch.float32
+    x = r.standard_normal((b, l, dims), np.float32)
+    wt, bs = r.standard_normal((dims, w), np.float32) * 0.5, r.standard_normal(dims).astype(np.float32) * 0.1
+    if dtype == "f16":
+        x, wt, bs = map(f16v, (x, wt, bs))
+    want = orc.causal_conv1d(np.ascontiguousarray(x.transpose(0, 2, 1)), wt, bs).transpose(0, 2, 1)
+    for w_off, b_off in ((1, 0), (0, 3), (2, 1)):
+        wbuf = torch.zeros(dims * w + 8, dtype=td, device="cuda")
+        bbuf = torch.zeros(dims + 8, dtype=td, device="cuda")
+        wv = wbuf[w_off:w_off + dims * w].view(dims, w)
+        bv = bbuf[b_off:b_off + dims]
+        wv.copy_(dev(wt, td))
+        bv.copy_(dev(bs, td))
+        y, fin = ops.tensor_causal_conv1d_tokens(dev(x, td), wv, bv, want_final_state=True)
+        (assert_close_f16 if dtype == "f16" else assert_abs)(host(y), want, f"conv tokens, weight offset {w_off}, bias offset {b_off}")
+        assert np.array_equal(host(fin), x[:, -(w - 1):].transpose(0, 2, 1))
+
+
 def test_conv1d_short_sequence_final_state(ops):
     r = np.random.default_rng(5)
     x = f16v(r.standard_normal((2, 2, 16), np.float32))  # seqlen 2 < width-1
@@ -198,6 +222,20 @@ def test_linear_f16_tcgen05(ops, M, K, N, layout):
     assert rel_l2(host(y), want) < 1e-3  # the reference's f16 mm test allows 1e-2 (tests/tests.cpp:138-165)
 
 
+@pytest.mark.parametrize("M,K,N", [(33, 256, 644), (7, 100, 24), (130, 515, 515), (64, 256, 1064 + 4)])
+@pytest.mark.parametrize("layout", ["KN", "NK"])
+def test_linear_f16_shapes_off_the_8_element_grid(ops, M, K, N, layout):
+    """tensor_linear takes any shape (srcs/ops/mm_ops.hpp:206-232): f16 problems whose K or N is not a multiple of 8 (what TMA
+    cannot address) run on the SIMT kernel and must meet the same rule."""
+    r = np.random.default_rng(M + K + N)
+    x = f16v(r.standard_normal((M, K), np.float32))
+    w = f16v(r.standard_normal((K, N), np.float32) * 0.05)
+    wd = dev(w if layout == "KN" else np.ascontiguousarray(w.T), torch.float16)
+    y = ops.tensor_linear(dev(x, torch.float16), wd, w_layout=ops.W_KN if layout == "KN" else ops.W_NK)
+    want = (x.astype(np.float64) @ w.astype(np.float64)).astype(np.float32)
+    assert_close_f16(host(y), want, f"linear {M}x{K}x{N} {layout}")
+
+
 def test_linear_f16_strided_rows(ops):
     r = np.random.default_rng(9)
     wide = f16v(r.standard_normal((96, 1064), np.float32))
@@ -221,6 +259,19 @@ def test_ssd_f32_golden(ops, golden_dir, name):
     assert_abs(host(fs), g["final_states"], name + " final_states", 1e-4)
 
 
+@pytest.fixture(params=["staged", "fused"])
+def ssd_path(request):
+    """Runs a scan test twice: through the staged kernels (chunk state, state passing, chunk scan) and through the one-kernel
+    scan (taken where it covers the shape; the library otherwise chooses by problem size)."""
+    old = os.environ.get("B200_SSD_FUSED")
+    os.environ["B200_SSD_FUSED"] = "1" if request.param == "fused" else "0"
+    yield request.param
+    if old is None:
+        os.environ.pop("B200_SSD_FUSED", None)
+    else:
+        os.environ["B200_SSD_FUSED"] = old
+
+
 def _ssd_inputs(seed, b, l, H, P, G, N):
     r = np.random.default_rng(seed)
     x = r.standard_normal((b, l, H, P), np.float32) * 0.5
@@ -237,8 +288,8 @@ def _ssd_inputs(seed, b, l, H, P, G, N):
 @pytest.mark.parametrize("dims", [(1, 512, 4, 64, 1, 64, 256), (2, 256, 8, 64, 2, 64, 128), (1, 300, 4, 64, 1, 64, 256),
                                   (1, 128, 2, 64, 1, 128, 64), (2, 64, 8, 64, 1, 16, 32), (1, 96, 2, 32, 1, 16, 32),
                                   (1, 256, 2, 64, 1, 128, 128), (1, 512, 4, 64, 2, 128, 256), (3, 1024, 16, 64, 1, 64, 256),
-                                  (1, 200, 12, 64, 3, 64, 128)])
-def test_ssd_f16_vs_oracle(ops, dims):
+                                  (1, 200, 12, 64, 3, 64, 128), (2, 640, 6, 64, 2, 64, 256), (5, 100, 3, 64, 1, 64, 256)])
+def test_ssd_f16_vs_oracle(ops, dims, ssd_path):
     b, l, H, P, G, N, Q = dims
     x, dt, A, B, C, D, dt_bias = _ssd_inputs(sum(dims), b, l, H, P, G, N)
     x, dt, B, C = map(f16v, (x, dt, B, C))
@@ -251,7 +302,7 @@ def test_ssd_f16_vs_oracle(ops, dims):
     assert_close_f16(host(fs), wfs, f"ssd final_states {dims}")
 
 
-def test_ssd_f16_in_place_slices(ops):
+def test_ssd_f16_in_place_slices(ops, ssd_path):
     # x | B | C read in place from one [b,l,conv_dim] tensor and dt from another wide tensor, as the mixer does
     b, l, H, P, G, N, Q = 2, 384, 4, 64, 1, 64, 128
     x, dt, A, B, C, D, dt_bias = _ssd_inputs(77, b, l, H, P, G, N)
@@ -265,6 +316,34 @@ def test_ssd_f16_in_place_slices(ops):
     wy, wfs = orc.ssd_chunk_scan(x, dt, A, B, C, Q, D=D, dt_bias=dt_bias)
     assert_close_f16(host(y), wy, "ssd in-place y")
     assert_close_f16(host(fs), wfs, "ssd in-place final_states")
+
+
+def test_ssd_fused_matches_staged_and_state_in_place(ops):
+    """The one-kernel scan against the staged kernels on the same inputs (both round the same operands to f16, so they agree far
+    inside the oracle tolerance), and final_states written over initial_states (the chunked-prefill calling pattern)."""
+    b, l, H, P, G, N, Q = 3, 900, 8, 64, 2, 64, 256
+    x, dt, A, B, C, D, dt_bias = _ssd_inputs(5, b, l, H, P, G, N)
+    h = torch.float16
+    init = dev(np.random.default_rng(2).standard_normal((b, H, P, N), np.float32) * 0.1)
+    args = (dev(x, h), dev(dt, h), dev(A), dev(B, h), dev(C, h), Q)
+    kw = dict(D=dev(D), dt_bias=dev(dt_bias))
+    res = {}
+    for mode in ("0", "1"):
+        os.environ["B200_SSD_FUSED"] = mode
+        try:
+            res[mode] = ops.tensor_mamba_chunk_scan_combined(*args, initial_states=init, exact_final_state=True, **kw)
+        finally:
+            os.environ.pop("B200_SSD_FUSED", None)
+    assert_close_f16(host(res["1"][0]), host(res["0"][0]), "fused vs staged y")
+    assert rel_l2(host(res["1"][0]), host(res["0"][0])) < 1e-3
+    assert_abs(host(res["1"][1]), host(res["0"][1]), "fused vs staged final state", 2e-3)
+    os.environ["B200_SSD_FUSED"] = "1"
+    try:
+        st = init.clone()
+        ops.tensor_mamba_chunk_scan_combined(*args, initial_states=st, final_states_out=st, exact_final_state=True, **kw)
+    finally:
+        os.environ.pop("B200_SSD_FUSED", None)
+    assert torch.equal(st, res["1"][1])
 
 
 # ---- decode recurrence --------------------------------------------------------------------------------------------
@@ -318,7 +397,7 @@ def test_rms_norm_golden_from_reference(ops, golden_dir):
 
 
 @pytest.mark.parametrize("dtype", ["f16", "f32"])
-def test_ssd_ragged_length_final_state_modes(ops, dtype):
+def test_ssd_ragged_length_final_state_modes(ops, dtype, ssd_path):
     """seqlen % chunk != 0: y is exact in both modes; final_states follows the reference script (padded tail decays it) by
     default and is the state after the last real token with exact_final_state."""
     b, l, H, P, G, N, Q = 2, 300, 4, 64, 1, 64, 128

@@ -6,6 +6,8 @@ device image. This test drives that entry point through the C ABI twice in a row
 another shape, so stale scratch contents from the first would show) and checks each result against the ordinary
 entry point fed with a caller-provided workspace. Both run the same kernels on the same data, so the results must be
 identical bit for bit; the assertion still states the f16 tolerance used elsewhere (rel 2e-2 / abs 2e-3) as the bound.
+Each result of the static entry point is also compared with the CPU oracle directly (same rule, zero elements outside),
+so that it does not stand on its sibling alone.
 
 This file sorts last on purpose: a run that stops at the first failure has already executed every other test.
 """
@@ -16,6 +18,7 @@ import pytest
 
 torch = pytest.importorskip("torch")
 
+from oracle import oracle as orc  # noqa: E402
 from tolerance import assert_close_f16  # noqa: E402
 
 pytestmark = pytest.mark.gpu
@@ -66,6 +69,10 @@ def test_static_scratch_entry_point_matches_workspace_entry_point_twice():
         assert_close_f16(y_st, y_ws, f"y, static vs workspace entry point {dims}")
         assert_close_f16(fs_st, fs_ws, f"final_states, static vs workspace entry point {dims}")
         assert np.array_equal(y_st, y_ws) and np.array_equal(fs_st, fs_ws)
+        x, dt, A, B, C, D, dt_bias, init = (t.float().cpu().numpy() for t in args)
+        wy, wfs = orc.ssd_chunk_scan(x, dt, A, B, C, chunk, D=D, dt_bias=dt_bias, initial_states=init)
+        assert_close_f16(y_st, wy, f"y, static entry point vs oracle {dims}")
+        assert_close_f16(fs_st, wfs, f"final_states, static entry point vs oracle {dims}")
 
 
 def test_static_scratch_entry_point_rejects_oversized_problems():
