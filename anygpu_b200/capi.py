@@ -43,6 +43,7 @@ SIGNATURES = {
     "b200_last_device_error": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
     "b200_launch_count": (ctypes.c_longlong, [_int]),
     "b200_linear_kernel_name": (ctypes.c_char_p, [_int, _i64, _i64, _i64]),
+    "b200_debug_linear_starved_producer": (_int, [_vp, _i64, _vp, _int, _vp, _i64, _i64, _i64, _i64, ctypes.c_uint32, _vp]),
     "b200_linear": (_int, [_int, _vp, _i64, _vp, _int, _vp, _i64, _i64, _i64, _i64, _vp]),
     "b200_causal_conv1d": (_int, [_int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "b200_causal_conv1d_tokens": (_int, [_int, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _vp, _i64, _i64, _i64, _int, _vp]),

@@ -45,7 +45,9 @@ using CfgSkinny64 = Cfg<64, 13, 1, 1, 64>;  // M <= 64: 13 x 16 KiB ring, 104 Ki
 template <int B_MN, class C>
 __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M, int N, int K, int m_tiles, int n_tiles,
-	uint32_t* err_word, const __half* __restrict__ residual, int64_t ldr)
+	uint32_t* err_word, const __half* __restrict__ residual, int64_t ldr,
+	uint32_t spin_limit /* polls after which a wait gives up */, int producer_short /* K-blocks per tile that the producer leaves out: 0
+	except in the self-test of the give-up path, where the MMA thread then waits for a stage that never fills */)
 {
 	using namespace gemm;
 	using namespace tc;
@@ -99,9 +101,9 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 			{
 				const int m0 = (tile % m_tiles) * BM;
 				const int n0 = (tile / m_tiles) * BN;
-				for (int kb = 0; kb < k_blocks; ++kb)
+				for (int kb = 0; kb < k_blocks - producer_short; ++kb)
 				{
-					if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp))
+					if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abortp, spin_limit))
 					{
 						report_timeout(err_word, kErrProducerWait);
 						goto role_done;
@@ -137,7 +139,7 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 			uint32_t acc_phase = 0;
 			for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
 			{
-				if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1u, abortp))
+				if (!mbar_wait(smem_u32(&bar_tempty[acc]), acc_phase ^ 1u, abortp, spin_limit))
 				{
 					report_timeout(err_word, kErrMmaWaitTmem);
 					goto role_done;
@@ -146,7 +148,7 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 				const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
 				for (int kb = 0; kb < k_blocks; ++kb)
 				{
-					if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp))
+					if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abortp, spin_limit))
 					{
 						report_timeout(err_word, kErrMmaWaitFull);
 						goto role_done;
@@ -185,7 +187,7 @@ __global__ void __launch_bounds__(gemm::THREADS, C::MIN_CTAS) gemm_f16_tcgen05_k
 		{
 			const int m0 = (tile % m_tiles) * BM;
 			const int n0 = (tile / m_tiles) * BN;
-			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp))
+			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp, spin_limit))
 			{
 				if (lane == 0) report_timeout(err_word, kErrEpilogueWait);
 				goto role_done;
@@ -503,9 +505,16 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 	return B200_OK;
 }
 
+// What the self-test of the give-up path asks of the next launch of the single-CTA kernel (b200_debug_linear_starved_producer).
+struct GemmDebug
+{
+	uint32_t spin_limit = tc::kSpinLimit;
+	int producer_short = 0;
+};
+
 template <int B_MN, class C>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmY, int M, int N, int K, cudaStream_t st,
-	const __half* residual, int64_t ldr)
+	const __half* residual, int64_t ldr, const GemmDebug& dbg = GemmDebug())
 {
 	using namespace gemm;
 	static bool smem_ok[64] = {};
@@ -515,7 +524,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 	const int64_t slots = static_cast<int64_t>(kNumSMs) * C::MIN_CTAS;
 	const unsigned grid = static_cast<unsigned>(tiles < slots ? tiles : slots);
 	gemm_f16_tcgen05_kernel<B_MN, C><<<grid, THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles, n_tiles, device_error_word(),
-		residual, ldr);
+		residual, ldr, dbg.spin_limit, dbg.producer_short);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }
@@ -542,7 +551,7 @@ static bool gemm_f16_tc_ok(const void* x, int64_t ldx, const void* w, const void
 }
 
 static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout, __half* y, int64_t ldy, int64_t M, int64_t K,
-	int64_t N, cudaStream_t st, const __half* residual = nullptr, int64_t ldr = 0)
+	int64_t N, cudaStream_t st, const __half* residual = nullptr, int64_t ldr = 0, const GemmDebug& dbg = GemmDebug())
 {
 	using namespace gemm;
 	if (!gemm_f16_tc_ok(x, ldx, w, y, ldy, K, N)) return B200_ERR_MISALIGNED;
@@ -565,11 +574,11 @@ static int gemm_f16(const __half* x, int64_t ldx, const __half* w, int w_layout,
 	if (paired) return w_layout == B200_W_NK ? launch_gemm_pair<0>(tmA, tmB, tmY, m, n, k, st, residual, ldr) : launch_gemm_pair<1>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
 	if (w_layout == B200_W_NK)
 	{
-		if (wide) return launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
-		return tiny_m ? launch_gemm<0, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st, residual, ldr) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
+		if (wide) return launch_gemm<0, CfgWide>(tmA, tmB, tmY, m, n, k, st, residual, ldr, dbg);
+		return tiny_m ? launch_gemm<0, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st, residual, ldr, dbg) : launch_gemm<0, CfgSkinny>(tmA, tmB, tmY, m, n, k, st, residual, ldr, dbg);
 	}
-	if (wide) return launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
-	return tiny_m ? launch_gemm<1, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st, residual, ldr) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st, residual, ldr);
+	if (wide) return launch_gemm<1, CfgWide>(tmA, tmB, tmY, m, n, k, st, residual, ldr, dbg);
+	return tiny_m ? launch_gemm<1, CfgSkinny64>(tmA, tmB, tmY, m, n, k, st, residual, ldr, dbg) : launch_gemm<1, CfgSkinny>(tmA, tmB, tmY, m, n, k, st, residual, ldr, dbg);
 }
 
 // Y = X . W + R, f16 (R: residual stream of the layer around the projection, added in the epilogue).
@@ -677,6 +686,20 @@ extern "C" int b200_linear(int dtype, const void* x, int64_t ldx, const void* w,
 		return gemm_simt<float>(static_cast<const float*>(x), ldx, static_cast<const float*>(w), w_layout, static_cast<float*>(y), ldy, M,
 			K, N, st);
 	return B200_ERR_UNSUPPORTED;
+}
+
+extern "C" int b200_debug_linear_starved_producer(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M,
+	int64_t K, int64_t N, uint32_t spin_limit, void* stream)
+{
+	if (!x || !w || !y) return B200_ERR_NULL;
+	if (M <= 0 || K < 2 * gemm::BK || N <= 0 || ldx < K || ldy < N || spin_limit == 0) return B200_ERR_BAD_SHAPE;
+	if (w_layout != B200_W_KN && w_layout != B200_W_NK) return B200_ERR_UNSUPPORTED;
+	if (!gemm_f16_tc_ok(x, ldx, w, y, ldy, K, N) || gemm_f16_choice(M, N).paired) return B200_ERR_UNSUPPORTED;  // single-CTA kernel only
+	GemmDebug dbg;
+	dbg.spin_limit = spin_limit;
+	dbg.producer_short = 1;
+	return gemm_f16(static_cast<const __half*>(x), ldx, static_cast<const __half*>(w), w_layout, static_cast<__half*>(y), ldy, M, K, N,
+		static_cast<cudaStream_t>(stream), nullptr, 0, dbg);
 }
 
 extern "C" const char* b200_linear_kernel_name(int dtype, int64_t M, int64_t K, int64_t N)

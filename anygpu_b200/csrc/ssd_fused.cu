@@ -11,11 +11,16 @@
 // which is the arithmetic of mamba_chunk_scan_combined_ref (scripts/zamba2/mamba_chunk_scan_comb.py:51-160) with the chunk
 // states never leaving the SM: x, B and C are read once, y is written once, and nothing else touches HBM. The result does not
 // depend on how the sequence is cut into blocks, so the public `chunk` (128 or 256) only fixes where the dt stage restarts its
-// cumulative sums. Two CTAs share an SM (104 KiB of shared memory, 256 tensor-memory columns each); while one waits for its
-// loads or its MMAs the other computes.
+// cumulative sums.
+// Roles: eight compute warps (TMEM lane quadrant x column half) and one producer warp whose lane 0 issues every TMA copy and
+// every MMA; they meet only at mbarriers. A block's chain is: tiles land -> CB -> S -> MMAs -> tiles of the next block (the
+// buffers are single: 104 KiB of shared memory and 256 tensor-memory columns per CTA, so that two CTAs share an SM); the
+// y epilogue and the state update of a block run while the next block's tiles are on their way, and the next tiles are
+// requested into L2 one block ahead.
 // Every decay is the exponential of a non-positive difference. Every mbarrier wait is bounded; on a timeout the CTA records a
 // code, drains and frees its tensor memory.
 #include <cstdlib>
+#include <type_traits>
 
 #include "ssd_common.cuh"
 #include "tcgen05.cuh"
@@ -25,7 +30,8 @@ namespace b200 {
 using namespace tc;
 
 namespace sfused {
-constexpr int THREADS = 256;
+constexpr int NCW = 8;                   // compute warps: 4 TMEM lane quadrants x 2 column halves
+constexpr int THREADS = (NCW + 1) * 32;  // + the producer warp
 constexpr int QI = 128;                  // tokens per block
 constexpr int TILE = QI * 128;           // a [128 rows][64 f16] tile: 16 KiB
 constexpr int OFF_C = 0;                 // C  [128 l][64 n]   K-major A operand of CB and of C.prev^T
@@ -47,24 +53,33 @@ __device__ __forceinline__ float ex2f(float v)
 	return r;
 }
 
+__device__ __forceinline__ void named_barrier_sync(int id, int nthreads)
+{
+	asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmX,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmY,
-	const float* __restrict__ D, const float* __restrict__ dt, const float* __restrict__ dacs, const float* __restrict__ colf,
-	const float* init, float* fin /* may alias init: every thread reads its slice first */, int64_t seqlen, int H, int G, int Q, int nchunks, uint32_t* err_word)
+	const float* __restrict__ D, const float* __restrict__ dt, const float* __restrict__ dacs,
+	const float* init, float* fin /* may alias init: every thread reads its slice first */, int64_t seqlen, int H, int G, int Q, int nchunks,
+	uint32_t* err_word)
 {
 	using namespace sfused;
 	extern __shared__ uint8_t smem_raw[];
-	__shared__ uint64_t bar_in, bar_cb, bar_mma;
+	// producer -> compute: bar_cb (CB in tensor memory), bar_y (S.X and C.prev^T done), bar_st (state MMAs done; also frees the tiles)
+	// compute -> producer: bar_s (S tile and scaled B written: one arrival per compute warp), bar_epi (block's results read out of
+	// tensor memory, y staged, prev written: one arrival per compute warp); bar_in: the TMA loads of a block
+	__shared__ uint64_t bar_in, bar_cb, bar_y, bar_st, bar_s, bar_epi;
 	__shared__ uint32_t tmem_slot;
 	__shared__ int abort_flag;
-	__shared__ __align__(16) float sc_dA[QI], sc_dt[QI], sc_cf[QI], sc_rowdec[QI], sc_w[QI];
-	__shared__ float sc_dec;
+	__shared__ __align__(16) float sc_dA2[2][QI], sc_q2[2][QI], sc_cf[2][QI], sc_rowdec[2][QI], sc_w[2][QI];  // sc_cf: see below
+	__shared__ float sc_dec[2];
 
 	const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
 	uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 	const int q = warp & 3;        // TMEM lane quadrant this warp may read
-	const int half = warp >> 2;    // which 64-wide K-block of S / which 32 columns of an accumulator this warp owns
+	const int half = (warp >> 2) & 1;  // which 64-wide K-block of S / which 32 columns of an accumulator this warp owns
 	const int r = q * 32 + lane;   // row (l, or p for the state) inside the block
 	const int h = static_cast<int>(blockIdx.x % H);
 	const int64_t b = blockIdx.x / H;
@@ -73,17 +88,19 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 	const int64_t bh = b * H + h;
 	const float* dacs_bh = dacs + bh * nchunks * static_cast<int64_t>(Q);
 	const float* dt_bh = dt + bh * nchunks * static_cast<int64_t>(Q);
-	const float* colf_bh = colf + bh * nchunks * static_cast<int64_t>(Q);
-	const float dh = D ? __ldg(D + h) : 0.f;
 	volatile int* abortp = &abort_flag;
-	const uint32_t in = smem_u32(&bar_in), cbb = smem_u32(&bar_cb), mmab = smem_u32(&bar_mma);
+	const uint32_t in = smem_u32(&bar_in), cbb = smem_u32(&bar_cb), yb = smem_u32(&bar_y), stb = smem_u32(&bar_st),
+		sb = smem_u32(&bar_s), epib = smem_u32(&bar_epi);
 
 	if (threadIdx.x == 0)
 	{
 		abort_flag = 0;
 		mbar_init(in, 1);
 		mbar_init(cbb, 1);
-		mbar_init(mmab, 1);
+		mbar_init(yb, 1);
+		mbar_init(stb, 1);
+		mbar_init(sb, NCW);
+		mbar_init(epib, NCW);
 		fence_mbar_init();
 		prefetch_tmap(&tmX); prefetch_tmap(&tmB); prefetch_tmap(&tmC); prefetch_tmap(&tmY);
 	}
@@ -92,129 +109,225 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 		tmem_alloc(smem_u32(&tmem_slot), TMEM_COLS);
 		tmem_relinquish();
 	}
-	tc_fence_before();
-	__syncthreads();
-	tc_fence_after();
-	const uint32_t tmem_base = tmem_slot;
-	const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-
-	// tiles of block j: rows past the end of the sequence arrive as zeros
-	auto issue_loads = [&](int j) {
-		const int t0 = j * QI;
-		mbar_arrive_expect_tx(in, 3 * TILE);
-#pragma unroll
-		for (int i = 0; i < 2; ++i)
-		{
-			tma_load_3d(base + OFF_C + i * 8192, &tmC, in, g * 64, t0 + i * 64, static_cast<int>(b));
-			tma_load_3d(base + OFF_B + i * 8192, &tmB, in, g * 64, t0 + i * 64, static_cast<int>(b));
-			tma_load_3d(base + OFF_X + i * 8192, &tmX, in, h * 64, t0 + i * 64, static_cast<int>(b));
-		}
-	};
-	if (threadIdx.x == 0) issue_loads(0);
-
-	// per-row scalars of the next block, fetched one block ahead (warps 0-3: thread = row)
-	float nx_dA = 0.f, nx_dt = 0.f, nx_cf = 0.f, nx_last = 0.f, nx_base = 0.f;
-	auto fetch_scalars = [&](int j) {
-		if (warp < 4 && j < nsub)
-		{
-			const int o = j * QI;
-			nx_dA = __ldg(dacs_bh + o + r);
-			nx_dt = __ldg(dt_bh + o + r);
-			nx_cf = __ldg(colf_bh + o + r);
-			nx_last = __ldg(dacs_bh + o + QI - 1);
-			nx_base = (o % Q) != 0 ? __ldg(dacs_bh + o - 1) : 0.f;  // the cumulative sums restart at every public chunk
-		}
-	};
-	fetch_scalars(0);
-
-	// the state: thread (q < 2) owns row p = r, columns n = half*32 .. +31
-	float state[32];
-#pragma unroll
-	for (int e = 0; e < 32; ++e) state[e] = 0.f;
-	if (q < 2)
-	{
-		if (init)
-		{
-			const float4* ip = reinterpret_cast<const float4*>(init + (bh * 64 + r) * 64 + half * 32);
-#pragma unroll
-			for (int v = 0; v < 8; ++v)
-			{
-				const float4 t = ip[v];
-				state[4 * v] = t.x; state[4 * v + 1] = t.y; state[4 * v + 2] = t.z; state[4 * v + 3] = t.w;
-			}
-		}
-		uint8_t* prow = gen + OFF_P + r * 128;
-#pragma unroll
-		for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(prow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(state + v * 8);
-	}
+	if (warp < NCW)
 	{
 		// the parts of S above the diagonal stay zero for the whole kernel
 		Half8 zero;
 #pragma unroll
 		for (int e = 0; e < 4; ++e) zero.h[e] = __floats2half2_rn(0.f, 0.f);
-		for (int i = threadIdx.x; i < 2 * TILE / 16; i += THREADS) *reinterpret_cast<Half8*>(gen + OFF_S + i * 16) = zero;
+		for (int i = threadIdx.x; i < 2 * TILE / 16; i += NCW * 32) *reinterpret_cast<Half8*>(gen + OFF_S + i * 16) = zero;
 	}
-	fence_proxy_async_smem();
+	tc_fence_before();
 	__syncthreads();
+	tc_fence_after();
+	const uint32_t tmem_base = tmem_slot;
 
-	constexpr uint32_t idesc_cb = make_idesc_f16(QI, QI, 0);
-	constexpr uint32_t idesc_y = make_idesc_f16(QI, 64, 1);      // B operand (x) MN-major
-	constexpr uint32_t idesc_z = make_idesc_f16(QI, 64, 0);
-	constexpr uint32_t idesc_st = make_idesc_f16(128, 64, 1, 1);  // A (x) and B (scaled B) MN-major
-	uint32_t fail_site = 0;
-
-	for (int j = 0; j < nsub; ++j)
+	if (warp == NCW)
 	{
-		const uint32_t par = static_cast<uint32_t>(j) & 1u;
-		// ---- (A) scalars of this block; CB = C . B^T -------------------------------------------------------------------
-		if (warp < 4)
+		// ================================= producer warp: every TMA copy and every MMA =================================
+		if (lane == 0)
 		{
-			sc_dA[r] = nx_dA;
-			sc_dt[r] = nx_dt;
-			sc_cf[r] = nx_cf;
-			sc_rowdec[r] = ex2f((nx_dA - nx_base) * kLog2e);
-			sc_w[r] = ex2f((nx_last - nx_dA) * kLog2e) * nx_dt;
-			if (r == QI - 1) sc_dec = ex2f((nx_dA - nx_base) * kLog2e);
-		}
-		if (threadIdx.x == 0)
-		{
-			bulk_wait_group_read<0>();  // the previous block's y store has read its staging tile
-			if (mbar_wait(in, par, abortp))
+			uint32_t fail = 0;
+			// the three tiles of block j (one 128-row box each; rows past the end of the sequence arrive as zeros), and a request
+			// that brings the tiles of block j+1 into L2 meanwhile: a block's loads start only when the MMAs of the block before
+			// have released the buffers, so their latency is on the critical path of every block
+			auto issue_loads = [&](int j) {
+				const int t0 = j * QI;
+				mbar_arrive_expect_tx(in, 3 * TILE);
+				tma_load_3d(base + OFF_C, &tmC, in, g * 64, t0, static_cast<int>(b));
+				tma_load_3d(base + OFF_B, &tmB, in, g * 64, t0, static_cast<int>(b));
+				tma_load_3d(base + OFF_X, &tmX, in, h * 64, t0, static_cast<int>(b));
+				if (j + 1 < nsub)
+				{
+					tma_prefetch_3d(&tmC, g * 64, t0 + QI, static_cast<int>(b));
+					tma_prefetch_3d(&tmB, g * 64, t0 + QI, static_cast<int>(b));
+					tma_prefetch_3d(&tmX, h * 64, t0 + QI, static_cast<int>(b));
+				}
+			};
+			auto store_y = [&](int j) {
+				const int t0 = j * QI;
+				// rows past the end of the sequence are clipped by the store; a box that starts past it is not issued at all
+				if (t0 < seqlen) tma_store_3d(&tmY, base + OFF_Y, h * 64, t0, static_cast<int>(b));
+				if (t0 + 64 < seqlen) tma_store_3d(&tmY, base + OFF_Y + 8192, h * 64, t0 + 64, static_cast<int>(b));
+				bulk_commit_group();
+			};
+			constexpr uint32_t idesc_cb = make_idesc_f16(QI, QI, 0);
+			constexpr uint32_t idesc_y = make_idesc_f16(QI, 64, 1);      // B operand (x) MN-major
+			constexpr uint32_t idesc_z = make_idesc_f16(QI, 64, 0);
+			constexpr uint32_t idesc_st = make_idesc_f16(128, 64, 1, 1);  // A (x) and B (scaled B) MN-major
+			const uint64_t c_desc = make_smem_desc_sw128(base + OFF_C, 16, 1024);
+			const uint64_t bk_desc = make_smem_desc_sw128(base + OFF_B, 16, 1024);
+			const uint64_t p_desc = make_smem_desc_sw128(base + OFF_P, 16, 1024);
+			issue_loads(0);
+			for (int j = 0; j < nsub && fail == 0; ++j)
 			{
+				const uint32_t par = static_cast<uint32_t>(j) & 1u;
+				if (!mbar_wait(in, par, abortp)) { fail = kErrProducerWait; break; }
+				if (j > 0)
+				{
+					// block j-1 has been read out of tensor memory (its CB / ST columns and accumulators may be overwritten), its prev
+					// tile is written and its y tile is staged
+					if (!mbar_wait(epib, par ^ 1u, abortp)) { fail = kErrProducerWait; break; }
+				}
 				tc_fence_after();
-				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_C, 16, 1024);
-				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_B, 16, 1024);
 #pragma unroll
 				for (int k = 0; k < 4; ++k)
-					mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_cb, k != 0 ? 1u : 0u);
+					mma_f16_ss(tmem_base, c_desc + static_cast<uint64_t>(k * 2), bk_desc + static_cast<uint64_t>(k * 2), idesc_cb, k != 0 ? 1u : 0u);
 				mma_commit(cbb);
-			}
-			else
-				fail_site = kErrProducerWait;
-		}
-		__syncthreads();
-		if (*abortp) break;
-
-		// ---- (B) S tiles from CB; B rows scaled in place ----------------------------------------------------------------
-		const float dl2 = sc_dA[r] * kLog2e;
-		fetch_scalars(j + 1);
-		if (mbar_wait(cbb, par, abortp))
-		{
-			tc_fence_after();
-			const int wrow0 = q * 32;
+				if (j > 0) store_y(j - 1);  // after the CB issue: the compute warps wait for CB, nobody waits for the store
+				if (!mbar_wait(sb, par, abortp)) { fail = kErrMmaWaitFull; break; }
+				tc_fence_after();
+				bulk_wait_group_read<0>();  // the previous y store has read the staging tile that this block's epilogue rewrites
 #pragma unroll
-			for (int ch = 0; ch < 2; ++ch)
-			{
-				const int s0 = half * 64 + ch * 32;  // first of 32 columns
-				if (s0 > wrow0 + 31) continue;      // above the diagonal: stays zero
-				uint32_t cbv[32];
-				tmem_ld_32x32(t_lane + static_cast<uint32_t>(s0), cbv);
-				uint8_t* srow = gen + OFF_S + half * TILE + r * 128;
-				if (half * 64 + 63 < wrow0)
+				for (int kb = 0; kb < 2; ++kb)
 				{
-					// K-block entirely below the diagonal: exp(dA[l] - dA[s]) dt[s] = exp(dA[l] - dA[block end]) * colf[s], both factors <= 1
-					const float rk = ex2f(fmaf(sc_dA[half * 64 + 63], -kLog2e, dl2));
-					const float4* cfp = reinterpret_cast<const float4*>(sc_cf + s0);
+					const uint64_t a_desc = make_smem_desc_sw128(base + OFF_S + kb * TILE, 16, 1024);
+					const uint64_t b_desc = make_smem_desc_sw128(base + OFF_X + kb * 8192, 8192, 1024);
+#pragma unroll
+					for (int k = 0; k < 4; ++k)
+						mma_f16_ss(tmem_base + 128u, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
+							(kb | k) != 0 ? 1u : 0u);
+				}
+#pragma unroll
+				for (int k = 0; k < 4; ++k)
+					mma_f16_ss(tmem_base + 192u, c_desc + static_cast<uint64_t>(k * 2), p_desc + static_cast<uint64_t>(k * 2), idesc_z, k != 0 ? 1u : 0u);
+				mma_commit(yb);
+#pragma unroll
+				for (int kb = 0; kb < 2; ++kb)
+				{
+					// M = 128 although the state has 64 rows (p): rows 64-127 multiply whatever follows the x tile and are never read
+					const uint64_t a_desc = make_smem_desc_sw128(base + OFF_X + kb * 8192, 8192, 1024);
+					const uint64_t b_desc = make_smem_desc_sw128(base + OFF_B + kb * 8192, 8192, 1024);
+#pragma unroll
+					for (int k = 0; k < 4; ++k)
+						mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 128), b_desc + static_cast<uint64_t>(k * 128), idesc_st,
+							(kb | k) != 0 ? 1u : 0u);
+				}
+				mma_commit(stb);
+				if (j + 1 < nsub)
+				{
+					// the next block's tiles go where this block's are: every MMA that reads them must have completed
+					if (!mbar_wait(stb, par, abortp)) { fail = kErrMmaWaitTmem; break; }
+					issue_loads(j + 1);
+				}
+			}
+			if (fail == 0)
+			{
+				if (mbar_wait(epib, static_cast<uint32_t>(nsub - 1) & 1u, abortp)) store_y(nsub - 1);
+				else fail = kErrProducerWait;
+			}
+			if (fail != 0) report_timeout(err_word, fail);
+			bulk_wait_group<0>();  // stores must have left shared memory before the CTA exits
+		}
+	}
+	else
+	{
+		// ================================= compute warps =================================================================
+		const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+		const float dh = D ? __ldg(D + h) : 0.f;
+		bool dead = false;  // a wait gave up: keep walking the loop (the barriers still need this warp) but do no work
+
+		// per-row scalars of the next block, fetched one block ahead (warps 0-3: thread = row)
+		float nx_dA = 0.f, nx_dt = 0.f, nx_last = 0.f, nx_base = 0.f;
+		auto fetch_scalars = [&](int j) {
+			if (warp < 4 && j < nsub)
+			{
+				const int o = j * QI;
+				nx_dA = __ldg(dacs_bh + o + r);
+				nx_dt = __ldg(dt_bh + o + r);
+				nx_last = __ldg(dacs_bh + o + QI - 1);
+				nx_base = (o % Q) != 0 ? __ldg(dacs_bh + o - 1) : 0.f;  // the cumulative sums restart at every public chunk
+			}
+		};
+		fetch_scalars(0);
+
+		// the state: thread (q < 2) owns row p = r, columns n = half*32 .. +31
+		float state[32];
+#pragma unroll
+		for (int e = 0; e < 32; ++e) state[e] = 0.f;
+		if (q < 2)
+		{
+			if (init)
+			{
+				const float4* ip = reinterpret_cast<const float4*>(init + (bh * 64 + r) * 64 + half * 32);
+#pragma unroll
+				for (int v = 0; v < 8; ++v)
+				{
+					const float4 t = ip[v];
+					state[4 * v] = t.x; state[4 * v + 1] = t.y; state[4 * v + 2] = t.z; state[4 * v + 3] = t.w;
+				}
+			}
+			uint8_t* prow = gen + OFF_P + r * 128;
+#pragma unroll
+			for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(prow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(state + v * 8);
+		}
+
+		for (int j = 0; j < nsub; ++j)
+		{
+			const uint32_t par = static_cast<uint32_t>(j) & 1u;
+			const int sbuf = j & 1;
+			// ---- scalars of this block (two sets: a warp still in the previous block's epilogue reads the other one) --------
+			if (warp < 4)
+			{
+				const float a2 = nx_dA * kLog2e;
+				sc_dA2[sbuf][r] = a2;
+				sc_q2[sbuf][r] = a2 - __log2f(nx_dt);
+				// column factor of the pieces of S that lie below the diagonal piece of their rows: for l past the end e of the
+				// 32-column piece that holds s, exp(dA[l] - dA[s]) dt[s] = exp(dA[l] - dA[e]) * (exp(dA[e] - dA[s]) dt[s]), both exponents <= 0
+				sc_cf[sbuf][r] = ex2f(__shfl_sync(0xffffffffu, a2, 31) - a2) * nx_dt;
+				sc_rowdec[sbuf][r] = ex2f((nx_dA - nx_base) * kLog2e);
+				sc_w[sbuf][r] = ex2f((nx_last - nx_dA) * kLog2e) * nx_dt;
+				if (r == QI - 1) sc_dec[sbuf] = ex2f((nx_dA - nx_base) * kLog2e);
+			}
+			named_barrier_sync(1, NCW * 32);
+			const float dl2 = sc_dA2[sbuf][r];
+			fetch_scalars(j + 1);
+
+			// ---- S tiles from CB; B rows scaled in place ---------------------------------------------------------------------
+			if (!dead && mbar_wait(cbb, par, abortp))
+			{
+				tc_fence_after();
+				const int wrow0 = q * 32;
+				uint8_t* srow = gen + OFF_S + (q >> 1) * TILE + r * 128;  // the diagonal piece of quadrant q lies in K-block q / 2
+				// One 32 x 32 piece of S: thread = row r, columns s0 .. s0+31, weight = 2^(dl2 - q2[s]) with
+				// q2[s] = dA[s] log2(e) - log2(dt[s]) (dt[s] = 0 gives q2 = +inf and the weight 0). DIAG: the piece holds the diagonal
+				// (s0 == first row of the warp): causal mask, and D added on the diagonal.
+				auto s_piece_exact = [&](const uint32_t* cbv, int s0, int ch, auto diag_tag) {
+					constexpr bool DIAG = decltype(diag_tag)::value;
+					const float4* qp = reinterpret_cast<const float4*>(sc_q2[sbuf] + s0);
+#pragma unroll
+					for (int v = 0; v < 4; ++v)
+					{
+						float o[8];
+#pragma unroll
+						for (int hq = 0; hq < 2; ++hq)
+						{
+							const float4 qv = qp[v * 2 + hq];
+							const float qa[4] = { qv.x, qv.y, qv.z, qv.w };
+#pragma unroll
+							for (int e = 0; e < 4; ++e)
+							{
+								const int jj = v * 8 + hq * 4 + e;
+								float val = __uint_as_float(cbv[jj]) * ex2f(dl2 - qa[e]);
+								if (DIAG)
+								{
+									val = jj <= lane ? val : 0.f;
+									if (jj == lane) val += dh;
+								}
+								o[hq * 4 + e] = val;
+							}
+						}
+						*reinterpret_cast<Half8*>(srow + (((ch * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
+					}
+				};
+				// Pieces of 32 x 32 (rows of quadrant q, columns 32 pc .. 32 pc + 31, pc <= q); pc == q holds the diagonal. Dealt to the
+				// two warps of a quadrant so that no warp has more than a diagonal piece and one other.
+				auto s_piece_below = [&](int pc) {
+					uint32_t cbv[32];
+					tmem_ld_32x32(t_lane + static_cast<uint32_t>(pc * 32), cbv);
+					const float rk = ex2f(dl2 - sc_dA2[sbuf][pc * 32 + 31]);
+					const float4* cfp = reinterpret_cast<const float4*>(sc_cf[sbuf] + pc * 32);
+					uint8_t* sr = gen + OFF_S + (pc >> 1) * TILE + r * 128;
 					tmem_ld_wait();
 #pragma unroll
 					for (int v = 0; v < 4; ++v)
@@ -228,161 +341,114 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 #pragma unroll
 							for (int e = 0; e < 4; ++e) o[hq * 4 + e] = __uint_as_float(cbv[v * 8 + hq * 4 + e]) * (rk * cfa[e]);
 						}
-						*reinterpret_cast<Half8*>(srow + (((ch * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
+						*reinterpret_cast<Half8*>(sr + ((((pc & 1) * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
 					}
+				};
+				auto s_piece_diag = [&]() {
+					uint32_t cbv[32];
+					tmem_ld_32x32(t_lane + static_cast<uint32_t>(wrow0), cbv);
+					tmem_ld_wait();
+					s_piece_exact(cbv, wrow0, q & 1, std::true_type{});
+				};
+				(void)srow;
+				if (half == 0)
+				{
+					if (q < 2) s_piece_diag();                           // q0: its only piece; q1: the diagonal one
+					else { s_piece_below(0); s_piece_below(1); }         // q2, q3: two pieces below
 				}
 				else
 				{
-					// crossed by the diagonal: exponential of the (non-positive) difference, causal mask, D on the diagonal
-					const float4* dsp = reinterpret_cast<const float4*>(sc_dA + s0);
-					const float4* dtp = reinterpret_cast<const float4*>(sc_dt + s0);
-					tmem_ld_wait();
-#pragma unroll
-					for (int v = 0; v < 4; ++v)
+					if (q == 1) s_piece_below(0);
+					else if (q == 2) s_piece_diag();
+					else if (q == 3) { s_piece_diag(); s_piece_below(2); }
+				}
+				// B[l, :] *= w[l] (a row-wise scale keeps every element where the swizzle put it). 1024 16-byte pieces: 20 per thread
+				// for the warp without S work, 12 per thread for the warp with one piece below the diagonal.
+				{
+					int first = -1, count = 0;
+					if (warp == 4) { first = lane; count = 20; }
+					else if (warp == 5) { first = 640 + lane; count = 12; }
+					for (int i = 0; i < count; ++i)
 					{
-						float o[8];
+						const int idx = first + i * 32;
+						Half8* p = reinterpret_cast<Half8*>(gen + OFF_B + idx * 16);
+						float f[8];
+						unpack8(*p, f);
+						const float sc = sc_w[sbuf][idx >> 3];
 #pragma unroll
-						for (int hq = 0; hq < 2; ++hq)
-						{
-							const float4 ds = dsp[v * 2 + hq];
-							const float4 dv = dtp[v * 2 + hq];
-							const float dsa[4] = { ds.x, ds.y, ds.z, ds.w };
-							const float dta[4] = { dv.x, dv.y, dv.z, dv.w };
-#pragma unroll
-							for (int e = 0; e < 4; ++e)
-							{
-								const int jj = v * 8 + hq * 4 + e;
-								const float wgt = ex2f(fmaf(dsa[e], -kLog2e, dl2)) * dta[e];
-								float val = (s0 + jj <= r) ? __uint_as_float(cbv[jj]) * wgt : 0.f;
-								if (s0 + jj == r) val += dh;
-								o[hq * 4 + e] = val;
-							}
-						}
-						*reinterpret_cast<Half8*>(srow + (((ch * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
+						for (int e = 0; e < 8; ++e) f[e] *= sc;
+						*p = pack8(f);
 					}
 				}
 			}
-			// B[l, :] *= w[l] (a row-wise scale keeps every element where the swizzle put it). 1024 16-byte pieces: 12 per thread
-			// for the two warps without S work, 4 per thread for the two with the least.
+			else
+				dead = true;
+			fence_proxy_async_smem();
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive(sb);
+
+			// ---- y = Y + rowdec * Z (the state MMAs still run) ----------------------------------------------------------------
+			if (!dead && mbar_wait(yb, par, abortp))
 			{
-				int first = -1, count = 0;
-				if (warp == 4 || warp == 5) { first = (warp - 4) * 32 + lane; count = 12; }
-				else if (warp == 0 || warp == 6) { first = 768 + (warp == 6 ? 32 : 0) + lane; count = 4; }
-				for (int i = 0; i < count; ++i)
-				{
-					const int idx = first + i * 64;
-					Half8* p = reinterpret_cast<Half8*>(gen + OFF_B + idx * 16);
-					float f[8];
-					unpack8(*p, f);
-					const float sc = sc_w[idx >> 3];
+				tc_fence_after();
+				const float rd = sc_rowdec[sbuf][r];
+				uint8_t* yrow = gen + OFF_Y + r * 128;
 #pragma unroll
-					for (int e = 0; e < 8; ++e) f[e] *= sc;
-					*p = pack8(f);
+				for (int hh = 0; hh < 2; ++hh)  // 16 columns at a time: fewer live registers
+				{
+					uint32_t yr[16], zr[16];
+					tmem_ld_32x16(t_lane + 128u + static_cast<uint32_t>(half * 32 + hh * 16), yr);
+					tmem_ld_32x16(t_lane + 192u + static_cast<uint32_t>(half * 32 + hh * 16), zr);
+					tmem_ld_wait();
+#pragma unroll
+					for (int v = 0; v < 2; ++v)
+					{
+						float o[8];
+#pragma unroll
+						for (int e = 0; e < 8; ++e) o[e] = fmaf(rd, __uint_as_float(zr[v * 8 + e]), __uint_as_float(yr[v * 8 + e]));
+						*reinterpret_cast<Half8*>(yrow + (((half * 4 + hh * 2 + v) ^ (r & 7)) << 4)) = pack8(o);
+					}
 				}
 			}
-		}
-		else
-			fail_site = kErrScanWait;
-		fence_proxy_async_smem();
-		tc_fence_before();
-		__syncthreads();
-		if (*abortp) break;
-
-		// ---- (C) Y = S . X, Z = C . prev^T, ST = X^T . Bs ----------------------------------------------------------------
-		if (threadIdx.x == 0)
-		{
-			tc_fence_after();
-#pragma unroll
-			for (int kb = 0; kb < 2; ++kb)
-			{
-				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_S + kb * TILE, 16, 1024);
-				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_X + kb * 8192, 8192, 1024);
-#pragma unroll
-				for (int k = 0; k < 4; ++k)
-					mma_f16_ss(tmem_base + 128u, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 128), idesc_y,
-						(kb | k) != 0 ? 1u : 0u);
-			}
-			{
-				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_C, 16, 1024);
-				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_P, 16, 1024);
-#pragma unroll
-				for (int k = 0; k < 4; ++k)
-					mma_f16_ss(tmem_base + 192u, a_desc + static_cast<uint64_t>(k * 2), b_desc + static_cast<uint64_t>(k * 2), idesc_z, k != 0 ? 1u : 0u);
-			}
-#pragma unroll
-			for (int kb = 0; kb < 2; ++kb)
-			{
-				// M = 128 although the state has 64 rows (p): rows 64-127 multiply whatever follows the x tile and are never read
-				const uint64_t a_desc = make_smem_desc_sw128(base + OFF_X + kb * 8192, 8192, 1024);
-				const uint64_t b_desc = make_smem_desc_sw128(base + OFF_B + kb * 8192, 8192, 1024);
-#pragma unroll
-				for (int k = 0; k < 4; ++k)
-					mma_f16_ss(tmem_base, a_desc + static_cast<uint64_t>(k * 128), b_desc + static_cast<uint64_t>(k * 128), idesc_st,
-						(kb | k) != 0 ? 1u : 0u);
-			}
-			mma_commit(mmab);
-		}
-
-		// ---- (D) y = Y + rowdec * Z; state update; next block's loads ---------------------------------------------------
-		if (mbar_wait(mmab, par, abortp))
-		{
-			tc_fence_after();
-			if (threadIdx.x == 0 && j + 1 < nsub) issue_loads(j + 1);
-			uint32_t yr[32], zr[32];
-			tmem_ld_32x32(t_lane + 128u + static_cast<uint32_t>(half * 32), yr);
-			tmem_ld_32x32(t_lane + 192u + static_cast<uint32_t>(half * 32), zr);
-			tmem_ld_wait();
-			const float rd = sc_rowdec[r];
-			uint8_t* yrow = gen + OFF_Y + r * 128;
-#pragma unroll
-			for (int v = 0; v < 4; ++v)
-			{
-				float o[8];
-#pragma unroll
-				for (int e = 0; e < 8; ++e) o[e] = fmaf(rd, __uint_as_float(zr[v * 8 + e]), __uint_as_float(yr[v * 8 + e]));
-				*reinterpret_cast<Half8*>(yrow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(o);
-			}
+			else
+				dead = true;
+			// ---- state <- decay * state + ST; its f16 copy is the next block's prev operand -------------------------------------
 			if (q < 2)
 			{
-				uint32_t sv[32];
-				tmem_ld_32x32(t_lane + static_cast<uint32_t>(half * 32), sv);
-				tmem_ld_wait();
-				const float dec = sc_dec;
+				if (!dead && mbar_wait(stb, par, abortp))
+				{
+					tc_fence_after();
+					uint32_t sv[32];
+					tmem_ld_32x32(t_lane + static_cast<uint32_t>(half * 32), sv);
+					tmem_ld_wait();
+					const float dec = sc_dec[sbuf];
 #pragma unroll
-				for (int e = 0; e < 32; ++e) state[e] = fmaf(dec, state[e], __uint_as_float(sv[e]));
-				uint8_t* prow = gen + OFF_P + r * 128;
+					for (int e = 0; e < 32; ++e) state[e] = fmaf(dec, state[e], __uint_as_float(sv[e]));
+					uint8_t* prow = gen + OFF_P + r * 128;
 #pragma unroll
-				for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(prow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(state + v * 8);
+					for (int v = 0; v < 4; ++v) *reinterpret_cast<Half8*>(prow + (((half * 4 + v) ^ (r & 7)) << 4)) = pack8(state + v * 8);
+				}
+				else
+					dead = true;
 			}
+			fence_proxy_async_smem();
+			tc_fence_before();
+			__syncwarp();
+			if (lane == 0) mbar_arrive(epib);
 		}
-		else
-			fail_site = kErrEpilogueWait;
-		fence_proxy_async_smem();
-		tc_fence_before();
-		__syncthreads();
-		if (*abortp) break;
-		if (threadIdx.x == 0)
+		if (dead && lane == 0) report_timeout(err_word, kErrScanWait);
+		if (!dead && !*abortp && fin != nullptr && q < 2)
 		{
-			const int t0 = j * QI;
-			// rows past the end of the sequence are clipped by the store; a box that starts past it is not issued at all
-			if (t0 < seqlen) tma_store_3d(&tmY, base + OFF_Y, h * 64, t0, static_cast<int>(b));
-			if (t0 + 64 < seqlen) tma_store_3d(&tmY, base + OFF_Y + 8192, h * 64, t0 + 64, static_cast<int>(b));
-			bulk_commit_group();
+			float4* fp = reinterpret_cast<float4*>(fin + (bh * 64 + r) * 64 + half * 32);
+#pragma unroll
+			for (int v = 0; v < 8; ++v) fp[v] = make_float4(state[4 * v], state[4 * v + 1], state[4 * v + 2], state[4 * v + 3]);
 		}
 	}
 
-	if (!*abortp && fin != nullptr && q < 2)
-	{
-		float4* fp = reinterpret_cast<float4*>(fin + (bh * 64 + r) * 64 + half * 32);
-#pragma unroll
-		for (int v = 0; v < 8; ++v) fp[v] = make_float4(state[4 * v], state[4 * v + 1], state[4 * v + 2], state[4 * v + 3]);
-	}
-	if (threadIdx.x == 0) bulk_wait_group<0>();  // stores must have left shared memory before the CTA exits
+	__syncwarp();
 	if (*abortp)
-	{
-		if (fail_site != 0 && lane == 0) report_timeout(err_word, fail_site);
 		for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // loads that may still be in flight land before the CTA's memory is released
-	}
 	tc_fence_before();
 	__syncthreads();
 	if (warp == 0)
@@ -431,18 +497,18 @@ int ssd_fused_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, cons
 {
 	CUtensorMap tmX, tmB, tmC, tmY;
 	const uint64_t L = static_cast<uint64_t>(d.seqlen), Bt = static_cast<uint64_t>(d.batch);
-	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(xs), L * xs, 64, 64);
+	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(xs), L * xs, 64, sfused::QI);
 	if (rc) return rc;
-	rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(bs), L * bs, 64, 64);
+	rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(bs), L * bs, 64, sfused::QI);
 	if (rc) return rc;
-	rc = tmap_3d_f16(&tmC, Cm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(cs), L * cs, 64, 64);
+	rc = tmap_3d_f16(&tmC, Cm, static_cast<uint64_t>(d.G) * d.N, L, Bt, static_cast<uint64_t>(cs), L * cs, 64, sfused::QI);
 	if (rc) return rc;
 	rc = tmap_3d_f16(&tmY, y, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(ys), L * ys, 64, 64);
 	if (rc) return rc;
 	static bool smem_ok[64] = {};
 	B200_CUDA_TRY(allow_dynamic_smem(ssd_fused_tc_kernel, sfused::TOTAL, smem_ok));
 	const unsigned grid = static_cast<unsigned>(d.batch * d.H);
-	ssd_fused_tc_kernel<<<grid, sfused::THREADS, sfused::TOTAL, st>>>(tmX, tmB, tmC, tmY, D, w.dt, w.dacs, w.colf, init, fin, d.seqlen, d.H, d.G,
+	ssd_fused_tc_kernel<<<grid, sfused::THREADS, sfused::TOTAL, st>>>(tmX, tmB, tmC, tmY, D, w.dt, w.dacs, init, fin, d.seqlen, d.H, d.G,
 		d.Q, d.nchunks, device_error_word());
 	B200_LAUNCH_CHECK();
 	return B200_OK;

@@ -52,9 +52,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 
 // Bounded wait. Returns false when it gave up (or another role already aborted); never spins forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t limit = kSpinLimit)
 {
-	for (uint32_t i = 0; i < kSpinLimit; ++i)
+	for (uint32_t i = 0; i < limit; ++i)
 	{
 		if (mbar_try_wait(bar, parity)) return true;
 		if ((i & 255u) == 255u && *abort_flag) return false;
@@ -87,6 +87,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
 	asm volatile(
 		"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
 		::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+		: "memory");
+}
+
+// Asks for the tile to be brought into L2 (no destination in shared memory, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_3d(const CUtensorMap* m, int x, int y, int z)
+{
+	asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+		::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z)
 		: "memory");
 }
 

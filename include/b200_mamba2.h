@@ -83,6 +83,16 @@ int b200_linear(int dtype, const void* x, int64_t ldx, const void* w, int w_layo
 /* Name of the kernel b200_linear launches for a problem of this size (for aligned operands): what a profile of the call shows. */
 const char* b200_linear_kernel_name(int dtype, int64_t M, int64_t K, int64_t N);
 
+/* Self-test of the give-up path of the bounded device-side waits (no counterpart in anyGPU). Runs the single-CTA f16 kernel of
+ * b200_linear on the given problem with its TMA producer told to leave out the last K-block of every tile, and with the poll
+ * limit of the kernel's waits lowered to `spin_limit`: the MMA-issuing thread waits for a stage that never fills, gives up after
+ * that many polls, the CTA records the site in the device error word, lets its copies and MMAs in flight land, frees its tensor
+ * memory and returns - no trap, no fault, the context stays usable. Y holds no meaningful result afterwards. The call returns
+ * B200_OK (the launch succeeded); b200_last_device_error then reports B200_ERR_DEVICE_TIMEOUT. f16 only; problems large enough
+ * for the CTA-pair kernel are rejected with B200_ERR_UNSUPPORTED. */
+int b200_debug_linear_starved_producer(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M,
+	int64_t K, int64_t N, uint32_t spin_limit, void* stream);
+
 /* ---- causal conv1d + SiLU, (batch, dims, seq_len) layout ---------------------------------------------------
  * Replaces cu_tensor_causal_conv1d_f32 (srcs/kernels/cuda/causal_conv1d.cu:78-101) behind
  * tensor_causal_conv1d (srcs/fused/causal_conv1d.hpp:90-117). y[b,d,s] = silu(bias[d] + sum_k w[d,k] x[b,d,s+k-(W-1)]),

@@ -87,7 +87,7 @@ def test_cfg2_last_chunk_with_carried_state_matches_oracle(cfg2_run, ops):
     got = host(out[3, t0:t1])
     assert_close_f16(got, want, "cfg2 last chunk of sequence 3 from the carried state", max_fail_fraction=1e-4)
     full_cache = cfg2_run[6]
-    assert_close_f16(host(full_cache.ssm_state[3:4]), fs, "cfg2 final state of sequence 3 through the last chunk", max_fail_fraction=1e-5)
+    assert_close_f16(host(full_cache.ssm_state[3:4]), fs, "cfg2 final state of sequence 3 through the last chunk")
 
 
 def test_cfg2_batch_independence_is_bit_exact(cfg2_run):
@@ -116,8 +116,8 @@ def test_cfg2_state_carry_and_decode_continuation(cfg2_run, ops):
     got = host(torch.stack(outs, dim=1))
     want = host(out[:, 1024:1032])
     # two different kernel chains (chunked tensor-core scan vs per-token recurrence) on f16 activations
-    assert_close_f16(got, want, "decode continuation vs prefill", max_fail_fraction=2e-3)
-    assert rel_l2(got, want) < 3e-3
+    # measured: 7.6e-5 of the elements outside (near-zero outputs, largest error 3.9e-3)
+    assert_close_f16(got, want, "decode continuation vs prefill", max_fail_fraction=5e-4)
 
 
 def test_cfg2_ssd_scan_vs_recurrence_kernel_and_oracle_rows(ops):
@@ -186,9 +186,9 @@ def test_cfg3_decode_full_size_128_steps(ops):
     ocs, oss = np.ascontiguousarray(cs[rows]), np.ascontiguousarray(ss[rows])
     want = np.stack([orc.mixer_decode(np.ascontiguousarray(us[rows, t]), w, cfg, ocs, oss, f16io=True) for t in range(steps)], axis=1)
     got = host(outs[rows])
-    assert_close_f16(got, want, "cfg3 decode, 2 of 64 rows, 128 steps", max_fail_fraction=2e-3)
-    assert rel_l2(got, want) < 3e-3
-    assert_close_f16(host(cache.ssm_state[rows]), oss, "ssm_state after 128 steps", max_fail_fraction=1e-4)
+    # measured: 1 of 655360 elements outside (1.5e-6), largest error 3.9e-3
+    assert_close_f16(got, want, "cfg3 decode, 2 of 64 rows, 128 steps", max_fail_fraction=1.5e-5)
+    assert_close_f16(host(cache.ssm_state[rows]), oss, "ssm_state after 128 steps")
 
 
 def test_cfg4_shape_two_groups_first_tokens_match_oracle(ops):
@@ -199,8 +199,8 @@ def test_cfg4_shape_two_groups_first_tokens_match_oracle(ops):
     out = mixer.prefill(torch.from_numpy(u).cuda().half())
     want = orc.mixer_prefill(u[:, :128], w, dict(cfg, chunk=128), f16io=True)["out"]  # 128 tokens: exact by causality
     got = host(out[:, :128])
-    # every output element is a 7168-term sum whose operands carry independent f16 roundings on the two sides; with outputs
-    # of magnitude ~3 (f16 spacing 2e-3) a small tail of near-zero results misses abs 2e-3 by one or two spacings
-    assert_close_f16(got, want, "cfg4-shaped layer, first 128 tokens", max_fail_fraction=1e-3)
-    assert_close_f16(got, want, "cfg4-shaped layer, first 128 tokens (abs 6e-3)", abs_=6e-3)
-    assert rel_l2(got, want) < 2e-3
+    # Every output is a 7168-term dot product of the gated-norm result g (|g| up to ~40, where f16 values lie 3e-2 apart) with
+    # weights of size ~0.02: one element of g that rounds the other way on the two sides moves an output by up to 6e-4, and a row
+    # holds a handful of them. Measured: 3.6e-4 of the elements outside rel 2e-2 / abs 2e-3, all of them near-zero outputs with
+    # an error of at most 3.9e-3 (every element is inside twice the absolute bound), rel-L2 5e-4.
+    assert_close_f16(got, want, "cfg4-shaped layer, first 128 tokens", max_fail_fraction=1e-3, outer=2.0)

@@ -2,10 +2,9 @@
 
 Gate: per-operator parity with zero elements outside tolerance lives in test_gpu_ops.py. End to end, the f16 mixer is
 compared with the oracle that rounds to binary16 at the same operator boundaries (what a chain of Tensor<float16>
-operators does); a vanishing fraction of near-zero outputs of the 4096-term out_proj sums can miss abs 2e-3 after
-the in_proj output itself has been rounded, so the end-to-end assertion allows 1e-4 of the elements outside
-rel 2e-2 / abs 2e-3 and additionally requires the reference's global rel-L2 metric (tests/test_tools.hpp:77-103,
-threshold 1e-2) to be below 2e-3."""
+operators does). At the sizes of this file every end-to-end comparison measures ZERO elements outside rel 2e-2 / abs 2e-3
+(the session prints the measured figures), so zero is what the assertions allow; the reference's global rel-L2 metric
+(tests/test_tools.hpp:77-103, threshold 1e-2) is additionally required to stay below 2e-3 (3e-3 for decode chains)."""
 import os
 
 import numpy as np
@@ -64,10 +63,10 @@ def test_mixer_prefill_f16(ops, cfg, layout):
     mixer = ops.Mamba2Mixer(cfg, wt)
     cache = ops.ZambaMambaCache.zeros(cfg, cfg["batch"], torch.float16)
     out = host(mixer.prefill(torch.from_numpy(u).cuda().half(), cache))
-    assert_close_f16(out, want["out"], "mixer out vs op-boundary-rounded oracle", max_fail_fraction=1e-4)
+    assert_close_f16(out, want["out"], "mixer out vs op-boundary-rounded oracle")
     assert rel_l2(out, want["out"]) < 2e-3
     assert rel_l2(out, pure["out"]) < 2e-3  # against the pure-fp32 oracle as well
-    assert_close_f16(host(cache.ssm_state), want["final_state"], "final ssm state", max_fail_fraction=1e-5)
+    assert_close_f16(host(cache.ssm_state), want["final_state"], "final ssm state")
     assert_close_f16(host(cache.conv_state), want["conv_state"], "conv state")
 
 
@@ -86,13 +85,13 @@ def test_mixer_f16_head_counts_off_the_8_element_grid(ops, nheads, d_state):
     cache = ops.ZambaMambaCache.zeros(cfg, 2, torch.float16)
     ud = torch.from_numpy(u).cuda().half()
     out = host(mixer.prefill(ud[:, :200].contiguous(), cache))
-    assert_close_f16(out, want["out"], f"mixer out, {nheads} heads", max_fail_fraction=1e-4)
-    assert_close_f16(host(cache.ssm_state), want["final_state"], "final ssm state", max_fail_fraction=1e-5)
+    assert_close_f16(out, want["out"], f"mixer out, {nheads} heads")
+    assert_close_f16(host(cache.ssm_state), want["final_state"], "final ssm state")
     assert_close_f16(host(cache.conv_state), want["conv_state"], "conv state")
     ocs, oss = want["conv_state"].copy(), want["final_state"].copy()
     got = host(mixer.decode(ud[:, 200].contiguous(), cache))
     wd = orc.mixer_decode(np.ascontiguousarray(u[:, 200]), w, cfg, ocs, oss, f16io=True)
-    assert_close_f16(got, wd, f"decode step, {nheads} heads", max_fail_fraction=1e-3)
+    assert_close_f16(got, wd, f"decode step, {nheads} heads")
 
 
 def test_mixer_prefill_host_call_equals_device_call(ops):
@@ -125,7 +124,7 @@ def test_mixer_decode_steps(ops, dtype):
         got = host(mixer.decode(torch.from_numpy(np.ascontiguousarray(us[:, t])).cuda().to(td), cache))
         want = orc.mixer_decode(np.ascontiguousarray(us[:, t]), w, cfg, ocs, oss, f16io=(dtype == "f16"))
         if dtype == "f16":
-            assert_close_f16(got, want, f"decode step {t}", max_fail_fraction=1e-3)
+            assert_close_f16(got, want, f"decode step {t}")
             assert rel_l2(got, want) < 2e-3
         else:
             assert_abs(got, want, f"decode step {t}", 1e-3)
@@ -185,7 +184,7 @@ def test_prefill_then_decode_continues_the_sequence(ops):
     outs = [host(mixer.decode(ud[:, 128 + t].contiguous(), cache)) for t in range(8)]
     full = orc.mixer_prefill(u, w, dict(cfg, chunk=8), f16io=True)  # 136 = 17 chunks of 8: no padding in the oracle
     got = np.stack(outs, axis=1)
-    assert_close_f16(got, full["out"][:, 128:], "decode continues prefill", max_fail_fraction=2e-3)
+    assert_close_f16(got, full["out"][:, 128:], "decode continues prefill")
     assert rel_l2(got, full["out"][:, 128:]) < 3e-3
 
 
@@ -210,7 +209,7 @@ def test_head_sharded_tp_ranks_emulated_on_one_gpu(ops, tp):
         out_sum += po.float()
         ss_sum += ss
     got = host(last.finish(out_sum.half(), ss_sum))
-    assert_close_f16(got, want, f"tp{tp} vs oracle", max_fail_fraction=2e-4)
+    assert_close_f16(got, want, f"tp{tp} vs oracle")
     assert rel_l2(got, want) < 2e-3
     assert rel_l2(got, whole) < 2e-3
 
@@ -239,7 +238,7 @@ def test_decoder_layer_f16_prefill_then_decode(ops, layout):
     hd = torch.from_numpy(h).cuda().half()
     want = orc.decoder_prefill(h[:, :256], w, w_in, 1e-5, cfg, f16io=True)
     out = host(layer.prefill(hd[:, :256].contiguous(), cache))
-    assert_close_f16(out, want["out"], "decoder layer prefill", max_fail_fraction=1e-4)
+    assert_close_f16(out, want["out"], "decoder layer prefill")
     assert rel_l2(out, want["out"]) < 2e-3
     # in place: the residual stream is overwritten by the layer's output
     buf = hd[:, :256].contiguous()
@@ -250,7 +249,7 @@ def test_decoder_layer_f16_prefill_then_decode(ops, layout):
         ht = np.ascontiguousarray(h[:, 256 + t])
         got = host(layer.decode(hd[:, 256 + t].contiguous(), cache))
         wd = orc.decoder_decode(ht, w, w_in, 1e-5, cfg, ocs, oss, f16io=True)
-        assert_close_f16(got, wd, f"decoder layer decode step {t}", max_fail_fraction=2e-3)
+        assert_close_f16(got, wd, f"decoder layer decode step {t}")
         assert rel_l2(got, wd) < 3e-3
 
 
@@ -272,11 +271,11 @@ def test_prefill_in_pieces_equals_one_prefill(ops, pieces):
         t0 += n
     got = torch.cat(outs, dim=1)
     want = orc.mixer_prefill(u[:, :512], w, dict(cfg, chunk=8), f16io=True)  # 512 = 64 chunks of 8: no padding in the oracle
-    assert_close_f16(host(got), want["out"], f"pieces {pieces} vs oracle", max_fail_fraction=1e-3)
+    assert_close_f16(host(got), want["out"], f"pieces {pieces} vs oracle")
     assert rel_l2(host(got), want["out"]) < 2e-3
     assert rel_l2(host(got), host(whole)) < 2e-3
     assert torch.equal(cache.conv_state, whole_cache.conv_state)  # the last three inputs, whatever the split
-    assert_close_f16(host(cache.ssm_state), want["final_state"], "ssm state after the pieces", max_fail_fraction=1e-4)
+    assert_close_f16(host(cache.ssm_state), want["final_state"], "ssm state after the pieces")
     d1 = mixer.decode(ud[:, 512].contiguous(), cache)
     d2 = mixer.decode(ud[:, 512].contiguous(), whole_cache)
     assert rel_l2(host(d1), host(d2)) < 3e-3
@@ -320,7 +319,7 @@ def test_packed_variable_length_batch_equals_separate_prefills(ops, lens, dtype)
         want = orc.mixer_prefill(u[None, cu[s]:cu[s + 1]], w, dict(cfg, chunk=4), f16io=dtype == "f16",
                                  initial_states=host(init[s:s + 1]))
         if dtype == "f16":
-            assert_close_f16(host(got[cu[s]:cu[s + 1]])[None], want["out"], "packed sequence vs oracle", max_fail_fraction=1e-3)
+            assert_close_f16(host(got[cu[s]:cu[s + 1]])[None], want["out"], "packed sequence vs oracle")
         assert rel_l2(host(got[cu[s]:cu[s + 1]])[None], want["out"]) < (2e-3 if dtype == "f16" else 1e-4)
 
 
@@ -355,9 +354,9 @@ def test_sequence_parallel_segments_emulated_on_one_gpu(ops, bounds, dtype):
     got = torch.cat(outs, dim=1)
     if dtype == "f16":
         want = orc.mixer_prefill(u, w, dict(cfg, chunk=8), f16io=True)
-        assert_close_f16(host(got), want["out"], "segments vs oracle", max_fail_fraction=1e-3)
+        assert_close_f16(host(got), want["out"], "segments vs oracle")
         assert rel_l2(host(got), host(whole)) < 2e-3
-        assert_close_f16(host(caches[-1].ssm_state), want["final_state"], "final state on the last rank", max_fail_fraction=1e-4)
+        assert_close_f16(host(caches[-1].ssm_state), want["final_state"], "final state on the last rank")
     else:
         want = orc.mixer_prefill(u, w, dict(cfg, chunk=8))
         assert_abs(host(got), want["out"], "segments vs oracle", 1e-3)

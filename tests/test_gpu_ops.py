@@ -236,6 +236,37 @@ def test_linear_f16_shapes_off_the_8_element_grid(ops, M, K, N, layout):
     assert_close_f16(host(y), want, f"linear {M}x{K}x{N} {layout}")
 
 
+def test_bounded_wait_gives_up_and_the_context_stays_usable(ops):
+    """The give-up path of the device-side waits, driven by a condition made on the host: the producer of the single-CTA GEMM
+    kernel is told to skip the last K-block of every tile and the waits of that launch poll at most 20000 times. The
+    MMA-issuing thread's wait runs out, the kernel records the site and returns (no trap, no fault); the library reports
+    B200_ERR_DEVICE_TIMEOUT once, and the next ordinary call on the same context is correct."""
+    import ctypes
+    from anygpu_b200 import capi
+    lib = capi.load()
+    r = np.random.default_rng(3)
+    M, K, N = 200, 512, 192
+    x = f16v(r.standard_normal((M, K), np.float32))
+    w = f16v(r.standard_normal((K, N), np.float32) * 0.05)
+    xd, wd = dev(x, torch.float16), dev(w, torch.float16)
+    yd = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.b200_last_device_error(stream, None) == 0
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    rc = lib.b200_debug_linear_starved_producer(p(xd), K, p(wd), capi.W_KN, p(yd), N, M, K, N, 20000, stream)
+    assert rc == 0, rc  # the launch itself succeeds
+    detail = ctypes.c_uint32(0)
+    assert lib.b200_last_device_error(stream, ctypes.byref(detail)) == -4  # B200_ERR_DEVICE_TIMEOUT
+    site = detail.value >> 16
+    assert site in (2, 4), hex(detail.value)  # the MMA thread's wait for a full stage (or an epilogue warp that noticed first)
+    assert lib.b200_last_device_error(stream, None) == 0  # reading the error word clears it
+    torch.cuda.synchronize()
+    y = ops.tensor_linear(xd, wd)  # the same kernel, ordinary call
+    want = (x.astype(np.float64) @ w.astype(np.float64)).astype(np.float32)
+    assert_close_f16(host(y), want, "linear after a timed-out launch")
+    assert lib.b200_last_device_error(stream, None) == 0
+
+
 def test_linear_f16_strided_rows(ops):
     r = np.random.default_rng(9)
     wide = f16v(r.standard_normal((96, 1064), np.float32))
