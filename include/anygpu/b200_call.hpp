@@ -24,14 +24,23 @@ inline void b200_check(const int status, const char* what)
 	exit(1);
 }
 
-// Returns a device buffer of at least `bytes` bytes that stays valid until the next larger request on this thread.
+// Returns a buffer of at least `bytes` bytes on the CURRENT device that stays valid until the next larger request of this
+// thread on that device (one buffer per thread and device: after cudaSetDevice the other device's buffer is not handed out).
 inline void* b200_workspace(const size_t bytes)
 {
-	thread_local std::shared_ptr<MemoryBuffer<CUDA>> ws;
-	if (!ws || static_cast<size_t>(ws->capacity) < bytes)
+	constexpr int kMaxDevices = 64;
+	thread_local std::shared_ptr<MemoryBuffer<CUDA>> ws[kMaxDevices];
+	int dev = 0;
+	CUDA_CHECK(cudaGetDevice(&dev));
+	if (dev < 0 || dev >= kMaxDevices)
+	{
+		log_error("b200_workspace: device index out of range");
+		exit(1);
+	}
+	if (!ws[dev] || static_cast<size_t>(ws[dev]->capacity) < bytes)
 	{
 		CUDA_CHECK(cudaDeviceSynchronize());  // kernels may still be using the old buffer
-		ws = std::make_shared<MemoryBuffer<CUDA>>(static_cast<int64>(bytes < 256 ? 256 : bytes));
+		ws[dev] = std::make_shared<MemoryBuffer<CUDA>>(static_cast<int64>(bytes < 256 ? 256 : bytes));
 	}
-	return ws->buffer;
+	return ws[dev]->buffer;
 }

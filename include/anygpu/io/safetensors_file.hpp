@@ -138,12 +138,35 @@ inline std::vector<TensorInfo> sft_read_tensorinfos(const std::string& path, uns
 		log_error("Unable to open file: " + path);
 		exit(1);
 	}
+	f.seekg(0, std::ios::end);
+	const unsigned long long file_size = static_cast<unsigned long long>(f.tellg());
+	f.seekg(0, std::ios::beg);
 	unsigned long long header_size = 0;
 	f.read(reinterpret_cast<char*>(&header_size), sizeof(header_size));
+	// a truncated or corrupt file must not turn into an unbounded allocation or silently empty tensors
+	if (!f || file_size < 8 || header_size > file_size - 8)
+	{
+		log_error("Not a safetensors file (header length exceeds the file): " + path);
+		exit(1);
+	}
 	std::string header(static_cast<size_t>(header_size), '\0');
 	f.read(header.data(), static_cast<std::streamsize>(header_size));
+	if (!f)
+	{
+		log_error("Unable to read the safetensors header: " + path);
+		exit(1);
+	}
 	std::vector<TensorInfo> infos;
 	_sft_read_tensorinfo_from_json(header, infos);
+	const unsigned long long data_bytes = file_size - 8ull - header_size;
+	for (const auto& info : infos)
+	{
+		if (info.offset_end < info.offset_start || info.offset_end > data_bytes)
+		{
+			log_error("safetensors data_offsets of '" + info.name + "' lie outside the file: " + path);
+			exit(1);
+		}
+	}
 	if (data_begin) *data_begin = 8ull + header_size;
 	return infos;
 }
@@ -165,12 +188,14 @@ inline Tensor<float32, CPU> sft_read_tensor_f32(const std::string& path, const s
 		{
 			ACASSERT(bytes == n * 4, "data_offsets do not match the shape");
 			f.read(reinterpret_cast<char*>(t.buffer()), static_cast<std::streamsize>(bytes));
+			ACASSERT(static_cast<bool>(f), "short read of tensor data");
 		}
 		else if (info.dtype == "F16" || info.dtype == "BF16")
 		{
 			ACASSERT(bytes == n * 2, "data_offsets do not match the shape");
 			std::vector<uint16_t> raw(n);
 			f.read(reinterpret_cast<char*>(raw.data()), static_cast<std::streamsize>(bytes));
+			ACASSERT(static_cast<bool>(f), "short read of tensor data");
 			for (size_t i = 0; i < n; ++i)
 			{
 				if (info.dtype == "BF16") t.buffer()[i] = sft_detail::bf16_to_f32(raw[i]);

@@ -1,8 +1,8 @@
 // Tensor<dtype, device> and MemoryBuffer<device> with the field and method names of anyGPU's
 // srcs/core/tensor.hpp:19-128 (MemoryBuffer) and :147-247 (Tensor): id, dim, offset (bytes), alignment, shape, stride
 // (elements), name; buffer(), raw_buffer(), numel(), size(), capacity(), copy_to_host(), copy_to_cuda().
-// Differences a caller can observe: device buffers are NOT zero-filled on allocation (every operator of this
-// library writes its whole output), and host buffers come from std::aligned_alloc.
+// Like anyGPU's, device buffers are zero-filled on allocation (srcs/core/tensor.hpp:80-84); host buffers come from
+// std::aligned_alloc and are zero-filled too.
 #pragma once
 
 #include <memory>
@@ -29,6 +29,7 @@ struct MemoryBuffer
 		else
 		{
 			CUDA_CHECK(cudaMalloc(&buffer, static_cast<size_t>(capacity)));
+			CUDA_CHECK(cudaMemset(buffer, 0, static_cast<size_t>(capacity)));  // as anyGPU does: code written against it may rely on zeros
 		}
 	}
 	MemoryBuffer(const MemoryBuffer&) = delete;
@@ -141,6 +142,33 @@ inline Tensor<dtype, device> tensor_slice_view(const Tensor<dtype, device>& x, c
 	y.shape[x.dim - 1] = hi - lo;
 	y.offset = x.offset + lo * static_cast<int64>(sizeof(dtype));
 	y.name = "";
+	return y;
+}
+
+// tensor_slice(x, axis, lo, hi) of anyGPU (srcs/ops/shape_ops.hpp:190-254): a NEW contiguous tensor holding x[..., lo:hi, ...]
+// along `axis`. anyGPU issues one cudaMemcpy per outer row from a host loop; here the tensor is seen as [outer, shape[axis], inner]
+// and one 2-D copy moves `outer` rows of (hi - lo) * inner elements. x must be contiguous (default strides), as in anyGPU.
+template <typename dtype, Device device>
+inline Tensor<dtype, device> tensor_slice(const Tensor<dtype, device>& x, const int64 axis, const int64 lo, const int64 hi)
+{
+	ACASSERT(axis >= 0 && axis < x.dim, "tensor_slice: axis out of range");
+	ACASSERT(0 <= lo && lo <= hi && hi <= x.shape[axis], "tensor_slice: bounds out of range");
+	Tensor<dtype, device> y(x.dim, [&] { Shape s = x.shape; s[axis] = hi - lo; return s; }());
+	int64 outer = 1, inner = 1;
+	for (int64 i = 0; i < axis; ++i) outer *= x.shape[i];
+	for (int64 i = axis + 1; i < x.dim; ++i) inner *= x.shape[i];
+	const size_t width = static_cast<size_t>((hi - lo) * inner) * sizeof(dtype);
+	const size_t src_pitch = static_cast<size_t>(x.shape[axis] * inner) * sizeof(dtype);
+	if (width == 0 || outer == 0) return y;
+	const char* src = reinterpret_cast<const char*>(x.buffer()) + static_cast<size_t>(lo * inner) * sizeof(dtype);
+	if constexpr (device == CPU)
+	{
+		for (int64 r = 0; r < outer; ++r) std::memcpy(reinterpret_cast<char*>(y.buffer()) + r * width, src + r * src_pitch, width);
+	}
+	else
+	{
+		CUDA_CHECK(cudaMemcpy2DAsync(y.buffer(), width, src, src_pitch, width, static_cast<size_t>(outer), cudaMemcpyDeviceToDevice, 0));
+	}
 	return y;
 }
 

@@ -18,12 +18,22 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 _i64 = ctypes.c_int64
 
 
+def reference_checkout():
+    """Where the anyGPU checkout lies: the environment variable ANYGPU_REF, else a directory named `reference` beside this
+    repository. None when neither holds the sources."""
+    root = os.path.dirname(_HERE)
+    for cand in (os.environ.get("ANYGPU_REF"), os.path.join(os.path.dirname(root), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "srcs", "core", "core.cpp")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build(with_ref=True):
     """Compile liboracle.so (always) and, only where the anyGPU checkout exists, _ref/libanygpu_ref.so (its CPU operators) and
     _ref/ref_cuda_bench (a timing program around its CUDA kernels)."""
     subprocess.check_call(["make", "-s", "-C", _HERE, "all"])
-    ref = os.environ.get("ANYGPU_REF", "/root/reference")  # where the anyGPU checkout lies (the Makefile's REF)
-    if with_ref and os.path.exists(os.path.join(ref, "srcs", "core", "core.cpp")):
+    ref = reference_checkout()
+    if with_ref and ref is not None:
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref", f"REF={ref}"])
         subprocess.check_call(["make", "-s", "-C", _HERE, "ref_cuda", f"REF={ref}"])
 

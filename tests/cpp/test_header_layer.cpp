@@ -322,6 +322,41 @@ static void test_mixer_f32_and_dat_files(const std::string& tmp_dir)
 	report("tensor_zamba_mamba_decoder f32 decode", close_enough(dout_t, et, 0.f, 1e-3f));
 }
 
+// tensor_slice under anyGPU's name (srcs/ops/shape_ops.hpp:190-254): a contiguous copy of x[..., lo:hi, ...] along any axis, on both
+// devices; and the zero fill of a fresh device tensor that anyGPU's MemoryBuffer guarantees (srcs/core/tensor.hpp:80-84).
+static void test_tensor_slice_and_zero_fill()
+{
+	const int64 b = 3, l = 5, d = 14;
+	auto h = crt_random_normal_tensor<float32, CPU>({ b, l, d }, 7);
+	auto dv = h.copy_to_cuda();
+	bool ok = true;
+	const int64 cases[3][3] = { { 2, 4, 11 }, { 1, 1, 4 }, { 0, 2, 3 } };
+	for (const auto& c : cases)
+	{
+		const int64 axis = c[0], lo = c[1], hi = c[2];
+		auto g = tensor_slice(dv, axis, lo, hi).copy_to_host();
+		auto e = tensor_slice(h, axis, lo, hi);
+		Shape want = h.shape;
+		want[axis] = hi - lo;
+		ok = ok && g.dim == 3 && g.shape == want && e.shape == want;
+		for (int64 i = 0; i < want[0] && ok; ++i)
+			for (int64 j = 0; j < want[1]; ++j)
+				for (int64 k = 0; k < want[2]; ++k)
+				{
+					const int64 si = i + (axis == 0 ? lo : 0), sj = j + (axis == 1 ? lo : 0), sk = k + (axis == 2 ? lo : 0);
+					const float ref = h.buffer()[(si * l + sj) * d + sk];
+					const int64 o = (i * want[1] + j) * want[2] + k;
+					ok = ok && g.buffer()[o] == ref && e.buffer()[o] == ref;
+				}
+	}
+	report("tensor_slice (axes 0, 1, 2; CPU and CUDA)", ok);
+	Tensor<float32, CUDA> fresh({ 7, 33 });
+	auto fh = fresh.copy_to_host();
+	bool zero = true;
+	for (int64 i = 0; i < fh.numel(); ++i) zero = zero && fh.buffer()[i] == 0.f;
+	report("fresh device tensor is zero-filled", zero);
+}
+
 int main(int argc, char** argv)
 {
 	const std::string tmp_dir = argc > 1 ? argv[1] : "/tmp";
@@ -337,6 +372,7 @@ int main(int argc, char** argv)
 	test_rms_norm();
 	test_chunk_scan_f16();
 	test_mixer_f32_and_dat_files(tmp_dir);
+	test_tensor_slice_and_zero_fill();
 	CUDA_CHECK(cudaDeviceSynchronize());
 	uint32_t detail = 0;
 	report("no device-side timeout", b200_last_device_error(nullptr, &detail) == B200_OK);

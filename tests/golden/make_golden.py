@@ -22,8 +22,12 @@ import sys
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-REF = os.environ.get("ANYGPU_REF", "/root/reference")
 sys.path.insert(0, ROOT)
+from oracle import oracle as _orc_for_ref  # noqa: E402
+
+REF = _orc_for_ref.reference_checkout()
+if REF is None:
+    raise SystemExit("the anyGPU checkout is needed to regenerate the golden vectors: set ANYGPU_REF to its path")
 sys.path.insert(0, os.path.join(REF, "scripts", "dnn_inspector"))
 sys.path.insert(0, os.path.join(REF, "scripts", "zamba2"))
 

@@ -55,3 +55,28 @@ def test_safetensors_reader_reads_f32_f16_bf16(tmp_path):
         wdt, wshape, ws, ws2 = want[name]
         assert dt == wdt and tuple(int(v) for v in shape) == tuple(wshape)
         assert abs(s - ws) <= 1e-6 * max(1.0, abs(ws)) and abs(s2 - ws2) <= 1e-6 * max(1.0, ws2), (name, s, ws, s2, ws2)
+
+
+def test_safetensors_reader_refuses_truncated_and_corrupt_files(tmp_path):
+    """A header length larger than the file, a header cut short and data_offsets that point past the end of the file must end
+    with an error message and exit status 1, not with an unbounded allocation or silently empty tensors."""
+    import build as cpp_build
+    exe = cpp_build.SFT_OUT if os.path.exists(cpp_build.SFT_OUT) else cpp_build.build_sft_dump()
+    a = np.arange(8, dtype=np.float32)
+    hj = json.dumps({"t": {"dtype": "F32", "shape": [8], "data_offsets": [0, 32]}}).encode()
+    good = struct.pack("<Q", len(hj)) + hj + a.tobytes()
+    bad_offsets = json.dumps({"t": {"dtype": "F32", "shape": [8], "data_offsets": [0, 64]}}).encode()
+    cases = {
+        "huge_header": struct.pack("<Q", 1 << 60) + hj + a.tobytes(),
+        "cut_in_header": good[:8 + len(hj) // 2],
+        "offsets_past_end": struct.pack("<Q", len(bad_offsets)) + bad_offsets + a.tobytes(),
+        "empty": b"",
+    }
+    path = tmp_path / "ok.safetensors"
+    path.write_bytes(good)
+    assert subprocess.run([exe, str(path)], capture_output=True, text=True, timeout=60).returncode == 0
+    for name, blob in cases.items():
+        path = tmp_path / (name + ".safetensors")
+        path.write_bytes(blob)
+        out = subprocess.run([exe, str(path)], capture_output=True, text=True, timeout=60)
+        assert out.returncode == 1, (name, out.returncode, out.stdout[-200:], out.stderr[-200:])
