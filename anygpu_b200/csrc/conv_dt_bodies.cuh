@@ -137,26 +137,25 @@ __device__ __forceinline__ void conv1d_tok_body(const T* __restrict__ x, int64_t
 // Block (block_x = batch * nchunks + chunk, block_y = group of kCsHeads heads); sdt: [Q][kCsHeads + 1] floats of shared memory.
 constexpr int kCsHeads = 8;
 
+// Core of the dt stage for ONE chunk of Q positions and kCsHeads heads starting at h0: `dt_chunk` points at the raw dt of the chunk's
+// first token (head 0), `valid` of its positions lie inside the sequence. Results of head h go to out0 + h * head_stride + l.
+// Shared by the batched layout below and by the packed (variable-length) layout, so that both round identically.
 template <typename T>
-__device__ __forceinline__ void ssd_dt_cumsum_body(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
-	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
-	float* __restrict__ dt_out, float* __restrict__ dacs_out, float* __restrict__ colf_out, float* sdt, unsigned block_x, unsigned block_y)
+__device__ __forceinline__ void ssd_dt_cumsum_core(const T* __restrict__ dt_chunk, int64_t dts, const float* __restrict__ A, int a_is_log,
+	const float* __restrict__ dt_bias, int dt_softplus, int valid, int H, int Q, int h0, int64_t out0, int64_t head_stride,
+	float* __restrict__ dt_out, float* __restrict__ dacs_out, float* __restrict__ colf_out, float* sdt)
 {
-	const int64_t b = block_x / nchunks;
-	const int c = static_cast<int>(block_x % nchunks);
-	const int h0 = block_y * kCsHeads;
 	for (int idx = threadIdx.x; idx < Q * kCsHeads; idx += blockDim.x)
 	{
 		const int l = idx / kCsHeads, hh = idx % kCsHeads;
 		const int h = h0 + hh;
-		const int64_t t = static_cast<int64_t>(c) * Q + l;
 		float v = 0.f;
 		if (h < H)
 		{
 			// positions past the end of the sequence: the reference pads dt with zeros before bias and softplus (they then decay
 			// the final state); B200_DT_SOFTPLUS_EXACT gives them dt = 0, which leaves the state alone
-			if (t < seqlen) v = ldf(dt + (b * seqlen + t) * dts + h);
-			if (t < seqlen || dt_softplus != B200_DT_SOFTPLUS_EXACT)
+			if (l < valid) v = ldf(dt_chunk + static_cast<int64_t>(l) * dts + h);
+			if (l < valid || dt_softplus != B200_DT_SOFTPLUS_EXACT)
 			{
 				if (dt_bias) v += dt_bias[h];
 				if (dt_softplus) v = softplus_f32(v);
@@ -179,8 +178,10 @@ __device__ __forceinline__ void ssd_dt_cumsum_body(const T* __restrict__ dt, int
 		{
 			const int l = lane * ep + i;
 			float v = 0.f;
-			if (i < ep && l < Q) v = sdt[l * (kCsHeads + 1) + hh] * a;
-			run += v;
+			// product and sum are rounded separately whatever the compiler knows about Q at the call site (a fused multiply-add
+			// in one instantiation only would make the batched and the packed layout round differently)
+			if (i < ep && l < Q) v = __fmul_rn(sdt[l * (kCsHeads + 1) + hh], a);
+			run = __fadd_rn(run, v);
 			loc[i] = run;
 		}
 		// exclusive prefix of lane totals
@@ -195,7 +196,7 @@ __device__ __forceinline__ void ssd_dt_cumsum_body(const T* __restrict__ dt, int
 		// dAcs at the end of this lane's 64-position block (Q % 64 == 0: ep divides 64, a block is 64/ep consecutive lanes)
 		const bool blocks64 = (Q % 64) == 0 && (64 % ep) == 0;
 		const float blk_end = blocks64 ? __shfl_sync(0xffffffffu, excl + run, lane | (64 / ep - 1)) : 0.f;
-		const int64_t base = ((b * H + h) * nchunks + c) * static_cast<int64_t>(Q);
+		const int64_t base = out0 + static_cast<int64_t>(h) * head_stride;
 #pragma unroll
 		for (int i = 0; i < 8; ++i)
 		{
@@ -205,10 +206,24 @@ __device__ __forceinline__ void ssd_dt_cumsum_body(const T* __restrict__ dt, int
 				const float dv = sdt[l * (kCsHeads + 1) + hh];
 				dacs_out[base + l] = excl + loc[i];
 				dt_out[base + l] = dv;
-				if (blocks64) colf_out[base + l] = __expf(blk_end - (excl + loc[i])) * dv;
+				if (blocks64 && colf_out) colf_out[base + l] = __expf(blk_end - (excl + loc[i])) * dv;
 			}
 		}
 	}
+}
+
+template <typename T>
+__device__ __forceinline__ void ssd_dt_cumsum_body(const T* __restrict__ dt, int64_t dts, const float* __restrict__ A,
+	int a_is_log, const float* __restrict__ dt_bias, int dt_softplus, int64_t seqlen, int H, int Q, int nchunks,
+	float* __restrict__ dt_out, float* __restrict__ dacs_out, float* __restrict__ colf_out, float* sdt, unsigned block_x, unsigned block_y)
+{
+	const int64_t b = block_x / nchunks;
+	const int c = static_cast<int>(block_x % nchunks);
+	const int64_t left = seqlen - static_cast<int64_t>(c) * Q;
+	const int valid = static_cast<int>(left < 0 ? 0 : (left > Q ? Q : left));
+	ssd_dt_cumsum_core<T>(dt + (b * seqlen + static_cast<int64_t>(c) * Q) * dts, dts, A, a_is_log, dt_bias, dt_softplus, valid, H, Q,
+		static_cast<int>(block_y) * kCsHeads, (b * H * nchunks + c) * static_cast<int64_t>(Q), static_cast<int64_t>(nchunks) * Q, dt_out, dacs_out,
+		colf_out, sdt);
 }
 
 }  // namespace b200

@@ -49,6 +49,15 @@ int ssd_combined_stages(int dtype, const void* x, int64_t x_stride, const void* 
 	int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk, int dt_softplus,
 	void* workspace, size_t workspace_bytes, void* stream, int stages);
 
+// packed variable-length batches in a fixed number of launches (varlen.cu)
+bool mixer_varlen_fused_applies(int dtype, const void* xbc_in, int64_t xs, const void* xbc, int64_t conv_dim, const void* conv_w,
+	const void* conv_b, int width, int64_t total_tokens, int64_t nseq, int64_t H, int64_t P, int64_t G, int64_t N, const void* y, int64_t ys,
+	const float* init, const float* fin);
+int mixer_conv_ssd_varlen_f16(const void* xbc_in, int64_t xs, const void* conv_w, const void* conv_b, int width, void* xbc, int64_t conv_dim,
+	void* conv_state_out, const void* dt, int64_t dts, const float* A_log, const float* dt_bias, const float* D, const float* init, void* y,
+	int64_t ys, float* fin, const int64_t* cu_host, int64_t nseq, int64_t H, int64_t P, int64_t G, int64_t N, void* scratch,
+	size_t scratch_bytes, cudaStream_t st);
+
 int ssd_segment_logdecay_of(float* out, int64_t batch, int64_t seqlen, int64_t H, int64_t P, int64_t G, int64_t N, int64_t chunk,
 	void* workspace, cudaStream_t st);
 int ssd_segment_prefix(const float* seg_states, const float* seg_logdecay, int nseg, int64_t batch, int64_t H, int64_t P, int64_t N,
@@ -655,7 +664,28 @@ extern "C" int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_con
 			m.d_in_proj, stream);
 		if (rc) return rc;
 	}
-	for (int64_t s = 0; s < nseq; ++s)
+	// f16 with the shapes of the one-kernel scan: conv1d + dt stage of all sequences in one launch, the scan in another. Taken
+	// unless the index arrays and the per-block dt rows do not fit the scan's scratch area (very many empty sequences).
+	bool packed_done = false;
+	if (T > 0 && mixer_varlen_fused_applies(dtype, ws.zxbcdt + d_inner * e, m.ldz, ws.xbc, m.conv_dim, w->conv1d_weight, w->conv1d_bias,
+			static_cast<int>(cfg->d_conv), T, nseq, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, ws.y, d_inner, initial_states,
+			ssm_state_out))
+	{
+		const int rc = mixer_conv_ssd_varlen_f16(ws.zxbcdt + d_inner * e, m.ldz, w->conv1d_weight, w->conv1d_bias, static_cast<int>(cfg->d_conv),
+			ws.xbc, m.conv_dim, conv_state_out, ws.zxbcdt + (d_inner + m.conv_dim) * e, m.ldz, w->A_log, w->dt_bias, w->D, initial_states, ws.y,
+			d_inner, ssm_state_out, cu_seqlens, nseq, cfg->nheads, cfg->headdim, cfg->ngroups, cfg->d_state, ws.ssd, ws.ssd_bytes, st);
+		if (rc == B200_OK)
+		{
+			packed_done = true;
+			// an empty sequence: its final state is its initial state (the scan kernel copies it), its conv_state is zero
+			for (int64_t s = 0; s < nseq && conv_state_out && cs_bytes; ++s)
+				if (cu_seqlens[s + 1] == cu_seqlens[s])
+					B200_CUDA_TRY(cudaMemsetAsync(static_cast<char*>(conv_state_out) + s * cs_bytes, 0, cs_bytes, st));
+		}
+		else if (rc != B200_ERR_WORKSPACE)
+			return rc;
+	}
+	for (int64_t s = 0; s < nseq && !packed_done; ++s)
 	{
 		const int64_t t0 = cu_seqlens[s], len = cu_seqlens[s + 1] - t0;
 		const float* init = initial_states ? initial_states + s * state_elems : nullptr;

@@ -80,6 +80,13 @@ bool ssd_fused_preferred(const SsdDims& d);
 int ssd_fused_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D,
 	const float* init, __half* y, int64_t ys, float* fin, const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);
 
+// The one-kernel scan over a packed batch of sequences (see ssd_fused.cu).
+bool ssd_fused_varlen_supported(int64_t total_tokens, int64_t nseq, int H, int P, int G, int N, const void* x, int64_t xs, const void* Bm,
+	int64_t bs, const void* Cm, int64_t cs, const void* y, int64_t ys, const float* init, const float* fin);
+int ssd_fused_varlen_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D,
+	const float* init, __half* y, int64_t ys, float* fin, int64_t total_tokens, int64_t nseq, int H, int G, const float* dt_rows,
+	const float* dacs_rows, const int* cu, const int* coff, int nblk, cudaStream_t st);
+
 template <typename T>
 int ssd_chunk_scan_simt(const T* x, int64_t xs, const T* Bm, int64_t bs, const T* Cm, int64_t cs, const float* D, T* y, int64_t ys,
 	const SsdDims& d, const SsdWorkspace& w, cudaStream_t st);

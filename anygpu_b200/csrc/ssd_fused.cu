@@ -58,11 +58,18 @@ __device__ __forceinline__ void named_barrier_sync(int id, int nthreads)
 	asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// VARLEN: the batch is a packed run of sequences (rows cu[s] .. cu[s+1]-1 of one [tokens, features] tensor); CTA = (sequence, head).
+// The dt stage then writes its rows per 128-token block of every sequence (block coff[s] + j of head h at ((h * nblk) + coff[s] + j) * 128,
+// cumulative sums restarting at every block, dt = 0 past the end of a sequence). Rows that a tile holds past the end of its
+// sequence belong to the next one; they carry dt = 0 in this sequence's scalars, which zeroes their columns of S and their
+// rows of the state update, and their rows of y are not stored.
+template <bool VARLEN>
 __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const __grid_constant__ CUtensorMap tmX,
 	const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmY,
 	const float* __restrict__ D, const float* __restrict__ dt, const float* __restrict__ dacs,
 	const float* init, float* fin /* may alias init: every thread reads its slice first */, int64_t seqlen, int H, int G, int Q, int nchunks,
-	uint32_t* err_word)
+	uint32_t* err_word, const int* __restrict__ cu /* VARLEN: token offsets [nseq + 1] */, const int* __restrict__ coff /* VARLEN: block offsets */,
+	int nblk /* VARLEN: 128-token blocks of all sequences */, __half* __restrict__ yv /* VARLEN: y, for the ragged last block */, int64_t ys)
 {
 	using namespace sfused;
 	extern __shared__ uint8_t smem_raw[];
@@ -82,12 +89,16 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 	const int half = (warp >> 2) & 1;  // which 64-wide K-block of S / which 32 columns of an accumulator this warp owns
 	const int r = q * 32 + lane;   // row (l, or p for the state) inside the block
 	const int h = static_cast<int>(blockIdx.x % H);
-	const int64_t b = blockIdx.x / H;
+	const int64_t bs_ = blockIdx.x / H;               // batch entry, or sequence of a packed batch
+	const int64_t b = VARLEN ? 0 : bs_;               // third TMA coordinate
+	const int tok0 = VARLEN ? cu[bs_] : 0;            // first row of the sequence inside the packed tensor
+	const int len = VARLEN ? cu[bs_ + 1] - tok0 : 0;  // VARLEN: tokens of this sequence
 	const int g = h / (H / G);
-	const int nsub = nchunks * (Q / QI);
-	const int64_t bh = b * H + h;
-	const float* dacs_bh = dacs + bh * nchunks * static_cast<int64_t>(Q);
-	const float* dt_bh = dt + bh * nchunks * static_cast<int64_t>(Q);
+	const int nsub = VARLEN ? (len + QI - 1) / QI : nchunks * (Q / QI);
+	const int64_t bh = bs_ * H + h;
+	const int64_t srow0 = VARLEN ? (static_cast<int64_t>(h) * nblk + coff[bs_]) * QI : bh * nchunks * static_cast<int64_t>(Q);
+	const float* dacs_bh = dacs + srow0;
+	const float* dt_bh = dt + srow0;
 	volatile int* abortp = &abort_flag;
 	const uint32_t in = smem_u32(&bar_in), cbb = smem_u32(&bar_cb), yb = smem_u32(&bar_y), stb = smem_u32(&bar_st),
 		sb = smem_u32(&bar_s), epib = smem_u32(&bar_epi);
@@ -132,7 +143,7 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 			// that brings the tiles of block j+1 into L2 meanwhile: a block's loads start only when the MMAs of the block before
 			// have released the buffers, so their latency is on the critical path of every block
 			auto issue_loads = [&](int j) {
-				const int t0 = j * QI;
+				const int t0 = tok0 + j * QI;
 				mbar_arrive_expect_tx(in, 3 * TILE);
 				tma_load_3d(base + OFF_C, &tmC, in, g * 64, t0, static_cast<int>(b));
 				tma_load_3d(base + OFF_B, &tmB, in, g * 64, t0, static_cast<int>(b));
@@ -145,7 +156,18 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 				}
 			};
 			auto store_y = [&](int j) {
-				const int t0 = j * QI;
+				const int t0 = tok0 + j * QI;
+				if (VARLEN)
+				{
+					// a whole block goes out as two boxes; the ragged last block was written row by row by the compute warps
+					if ((j + 1) * QI <= len)
+					{
+						tma_store_3d(&tmY, base + OFF_Y, h * 64, t0, 0);
+						tma_store_3d(&tmY, base + OFF_Y + 8192, h * 64, t0 + 64, 0);
+					}
+					bulk_commit_group();
+					return;
+				}
 				// rows past the end of the sequence are clipped by the store; a box that starts past it is not issued at all
 				if (t0 < seqlen) tma_store_3d(&tmY, base + OFF_Y, h * 64, t0, static_cast<int>(b));
 				if (t0 + 64 < seqlen) tma_store_3d(&tmY, base + OFF_Y + 8192, h * 64, t0 + 64, static_cast<int>(b));
@@ -158,7 +180,7 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 			const uint64_t c_desc = make_smem_desc_sw128(base + OFF_C, 16, 1024);
 			const uint64_t bk_desc = make_smem_desc_sw128(base + OFF_B, 16, 1024);
 			const uint64_t p_desc = make_smem_desc_sw128(base + OFF_P, 16, 1024);
-			issue_loads(0);
+			if (nsub > 0) issue_loads(0);
 			for (int j = 0; j < nsub && fail == 0; ++j)
 			{
 				const uint32_t par = static_cast<uint32_t>(j) & 1u;
@@ -211,7 +233,7 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 					issue_loads(j + 1);
 				}
 			}
-			if (fail == 0)
+			if (fail == 0 && nsub > 0)
 			{
 				if (mbar_wait(epib, static_cast<uint32_t>(nsub - 1) & 1u, abortp)) store_y(nsub - 1);
 				else fail = kErrProducerWait;
@@ -236,7 +258,8 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 				nx_dA = __ldg(dacs_bh + o + r);
 				nx_dt = __ldg(dt_bh + o + r);
 				nx_last = __ldg(dacs_bh + o + QI - 1);
-				nx_base = (o % Q) != 0 ? __ldg(dacs_bh + o - 1) : 0.f;  // the cumulative sums restart at every public chunk
+				// the cumulative sums restart at every public chunk (at every block of a packed batch)
+				nx_base = !VARLEN && (o % Q) != 0 ? __ldg(dacs_bh + o - 1) : 0.f;
 			}
 		};
 		fetch_scalars(0);
@@ -394,6 +417,11 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 				tc_fence_after();
 				const float rd = sc_rowdec[sbuf][r];
 				uint8_t* yrow = gen + OFF_Y + r * 128;
+				// packed batch, last block of a sequence that does not fill it: the rows of this sequence go from registers to global
+				// memory (64 contiguous bytes per thread), the rest of the tile belongs to the next sequence and is not written
+				const bool ragged = VARLEN && (j + 1) * QI > len;
+				__half* grow = VARLEN ? yv + (static_cast<int64_t>(tok0) + j * QI + r) * ys + h * 64 + half * 32 : nullptr;
+				const bool grow_ok = VARLEN && j * QI + r < len;
 #pragma unroll
 				for (int hh = 0; hh < 2; ++hh)  // 16 columns at a time: fewer live registers
 				{
@@ -407,7 +435,8 @@ __global__ void __launch_bounds__(sfused::THREADS, 2) ssd_fused_tc_kernel(const 
 						float o[8];
 #pragma unroll
 						for (int e = 0; e < 8; ++e) o[e] = fmaf(rd, __uint_as_float(zr[v * 8 + e]), __uint_as_float(yr[v * 8 + e]));
-						*reinterpret_cast<Half8*>(yrow + (((half * 4 + hh * 2 + v) ^ (r & 7)) << 4)) = pack8(o);
+						if (!ragged) *reinterpret_cast<Half8*>(yrow + (((half * 4 + hh * 2 + v) ^ (r & 7)) << 4)) = pack8(o);
+						else if (grow_ok) *reinterpret_cast<Half8*>(grow + hh * 16 + v * 8) = pack8(o);
 					}
 				}
 			}
@@ -506,10 +535,46 @@ int ssd_fused_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, cons
 	rc = tmap_3d_f16(&tmY, y, static_cast<uint64_t>(d.H) * 64, L, Bt, static_cast<uint64_t>(ys), L * ys, 64, 64);
 	if (rc) return rc;
 	static bool smem_ok[64] = {};
-	B200_CUDA_TRY(allow_dynamic_smem(ssd_fused_tc_kernel, sfused::TOTAL, smem_ok));
+	B200_CUDA_TRY(allow_dynamic_smem(ssd_fused_tc_kernel<false>, sfused::TOTAL, smem_ok));
 	const unsigned grid = static_cast<unsigned>(d.batch * d.H);
-	ssd_fused_tc_kernel<<<grid, sfused::THREADS, sfused::TOTAL, st>>>(tmX, tmB, tmC, tmY, D, w.dt, w.dacs, init, fin, d.seqlen, d.H, d.G,
-		d.Q, d.nchunks, device_error_word());
+	ssd_fused_tc_kernel<false><<<grid, sfused::THREADS, sfused::TOTAL, st>>>(tmX, tmB, tmC, tmY, D, w.dt, w.dacs, init, fin, d.seqlen, d.H,
+		d.G, d.Q, d.nchunks, device_error_word(), nullptr, nullptr, 0, nullptr, 0);
+	B200_LAUNCH_CHECK();
+	return B200_OK;
+}
+
+// Packed batch: x / B / C / y are [total_tokens, features] tensors (row strides xs, bs, cs, ys), sequence s in rows cu[s] .. cu[s+1]-1;
+// dt_rows / dacs_rows hold the dt stage's results per 128-token block of every sequence ([H][nblk][128], block coff[s] + j of
+// sequence s); cu and coff are DEVICE arrays of nseq + 1 ints. init / fin: [nseq, H, P, N] fp32 or null.
+bool ssd_fused_varlen_supported(int64_t total_tokens, int64_t nseq, int H, int P, int G, int N, const void* x, int64_t xs, const void* Bm,
+	int64_t bs, const void* Cm, int64_t cs, const void* y, int64_t ys, const float* init, const float* fin)
+{
+	if (P != 64 || N != 64 || H % G != 0) return false;
+	if (xs % 8 || bs % 8 || cs % 8 || ys % 8) return false;
+	if (!aligned16(x) || !aligned16(Bm) || !aligned16(Cm) || !aligned16(y)) return false;
+	if ((init && !aligned16(init)) || (fin && !aligned16(fin))) return false;
+	return total_tokens > 0 && total_tokens <= 0x7fffffffLL && nseq > 0 && nseq * H <= 0x7fffffffLL;
+}
+
+int ssd_fused_varlen_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, const __half* Cm, int64_t cs, const float* D,
+	const float* init, __half* y, int64_t ys, float* fin, int64_t total_tokens, int64_t nseq, int H, int G, const float* dt_rows,
+	const float* dacs_rows, const int* cu, const int* coff, int nblk, cudaStream_t st)
+{
+	CUtensorMap tmX, tmB, tmC, tmY;
+	const uint64_t L = static_cast<uint64_t>(total_tokens);
+	int rc = tmap_3d_f16(&tmX, x, static_cast<uint64_t>(H) * 64, L, 1, static_cast<uint64_t>(xs), L * xs, 64, sfused::QI);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmB, Bm, static_cast<uint64_t>(G) * 64, L, 1, static_cast<uint64_t>(bs), L * bs, 64, sfused::QI);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmC, Cm, static_cast<uint64_t>(G) * 64, L, 1, static_cast<uint64_t>(cs), L * cs, 64, sfused::QI);
+	if (rc) return rc;
+	rc = tmap_3d_f16(&tmY, y, static_cast<uint64_t>(H) * 64, L, 1, static_cast<uint64_t>(ys), L * ys, 64, 64);
+	if (rc) return rc;
+	static bool smem_ok[64] = {};
+	B200_CUDA_TRY(allow_dynamic_smem(ssd_fused_tc_kernel<true>, sfused::TOTAL, smem_ok));
+	const unsigned grid = static_cast<unsigned>(nseq * H);
+	ssd_fused_tc_kernel<true><<<grid, sfused::THREADS, sfused::TOTAL, st>>>(tmX, tmB, tmC, tmY, D, dt_rows, dacs_rows, init, fin, total_tokens, H,
+		G, sfused::QI, 0, device_error_word(), cu, coff, nblk, y, ys);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }

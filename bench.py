@@ -283,7 +283,7 @@ def decode_record(torch, ops, local_rank, peaks, steps=128, reps=5):
     outs = torch.empty_like(us)
     cd3, dip3 = synth.dims(c3)
     bytes_alg = (c3["d_model"] * dip3 + c3["d_inner"] * c3["d_model"]) * 2 + 2 * ss.size * 4 + 2 * cs.size * 2
-    u1, o1 = torch.empty_like(us[0]), torch.empty_like(us[0])
+    u1, o1 = us[0].clone(), torch.empty_like(us[0])  # the one-step graph replays this input every time
     g1 = mixer.capture_decode(u1, cache, o1)
     gsteps = 16 if steps % 16 == 0 else 1
     g16 = mixer.capture_decode_steps(us[:gsteps], cache, outs[:gsteps])
@@ -306,6 +306,10 @@ def decode_record(torch, ops, local_rank, peaks, steps=128, reps=5):
         us_per_step = min(fn() for _ in range(reps)) * 1e3 / steps
         res[name] = {"us_per_step": us_per_step, "gbs": bytes_alg / (us_per_step * 1e-6) / 1e9,
                      "frac_of_hbm": bytes_alg / (us_per_step * 1e-6) / 1e9 / peaks["hbm_gbs"]}
+        err = lib.b200_last_device_error(None, None)
+        if err != 0 or not bool(torch.isfinite(outs).all()) or not bool(torch.isfinite(cache.ssm_state).all()):
+            raise SystemExit(f"decode record, mode {name}: device error {err}, outputs finite {bool(torch.isfinite(outs).all())}, "
+                             f"state finite {bool(torch.isfinite(cache.ssm_state).all())}")
     lib.b200_launch_count(1)
     mixer.decode(us[0], cache, out=outs[0])
     launches_per_step = int(lib.b200_launch_count(1))
@@ -958,6 +962,25 @@ def run_kernel(args):
                                                         t[:, :, H * P + G * N:].unflatten(2, (G, N)), Q, D=D, dt_bias=dtb)
         nchunks = -(-l // Q)
         flops_alg = float(b * nchunks * (H * (2 * Q * Q * P + 4 * Q * N * P) + G * 2 * Q * Q * N))
+    elif k == "varlen":
+        # 256 sequences of about 32 tokens in one packed call against the same sequences prefilled one by one (cfg2 layer sizes)
+        r = np.random.default_rng(0)
+        lens = [int(v) for v in r.integers(20, 45, 256)]
+        total = sum(lens)
+        cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+        vcfg = dict(cfg, batch=1, seqlen=64, chunk=128)
+        wts = ops.ZambaMamba2weights.from_numpy(synth.make_weights(vcfg, 0), h)
+        mixer = ops.Mamba2Mixer(vcfg, wts)
+        ud = rn(total, vcfg["d_model"])
+        od = torch.empty_like(ud)
+        seqs = [ud[cu[s]:cu[s + 1]].unsqueeze(0).contiguous() for s in range(len(lens))]
+        if args.varlen_loop:
+            def fn(i):
+                for sq in seqs:
+                    mixer.prefill(sq)
+        else:
+            fn = lambda i: mixer.prefill_varlen(ud, cu, out=od)
+        extra = {"sequences": len(lens), "total_tokens": total, "mode": "one prefill per sequence" if args.varlen_loop else "one packed call"}
     elif k == "ssm_update":
         c3 = workload("cfg3")
         B_, H_, P_, N_, G_ = c3["batch"], c3["nheads"], c3["headdim"], c3["d_state"], c3["ngroups"]
@@ -1005,6 +1028,7 @@ def run_kernel(args):
     med, mn = ms[len(ms) // 2], ms[0]
     capi.check("b200_last_device_error", capi.load().b200_last_device_error(None, None))
     out = {"kernel": k, "small": bool(args.small), "graph": bool(args.graph), "graph_steps": (per_call if k == "conv1d_decode" else args.graph_steps) if args.graph else 0, "steps": args.steps, "median_us": med * 1e3, "min_us": mn * 1e3}
+    out.update(locals().get("extra", {}))
     if bytes_alg:
         out.update(algorithmic_bytes=bytes_alg, gbs_median=bytes_alg / (med * 1e-3) / 1e9, hbm_peak_gbs=peaks["hbm_gbs"],
                    frac_of_hbm_peak=bytes_alg / (med * 1e-3) / 1e9 / peaks["hbm_gbs"], peak_source=peaks["source"])
@@ -1032,6 +1056,7 @@ def main():
     ap.add_argument("--tp-chunk", type=int, default=2, help="sequences per compute / all-reduce pipeline step of the head-sharded runs")
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
+    ap.add_argument("--varlen-loop", action="store_true", help="with --kernel varlen: the per-sequence loop instead of the packed call")
     ap.add_argument("--chunk", type=int, default=0, help="with --kernel ssd: chunk length of the scan (default: the configuration's 256)")
     ap.add_argument("--layout", default="KN", choices=["KN", "NK"], help="with --kernel decode: projection weight layout")
     ap.add_argument("--graph-steps", type=int, default=1, help="with --kernel decode --graph: consecutive steps recorded into one graph")

@@ -263,7 +263,12 @@ int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_config* cfg,
  * out [total_tokens, d_model] belong to sequence s. cu_seqlens is a HOST array of nseq+1 non-decreasing offsets that starts at 0
  * (the `cu_seqlens` convention that scripts/zamba2/mamba_chunk_scan_comb.py:164-166 leaves unsupported). initial_states
  * [nseq,H,P,N] fp32 or NULL; conv_state_out [nseq, conv_dim, d_conv-1] (dtype) and ssm_state_out [nseq,H,P,N] fp32 or NULL. Every
- * sequence gets exactly what b200_mamba2_mixer_prefill gives for it alone; an empty sequence hands on its initial state. */
+ * sequence gets what b200_mamba2_mixer_prefill gives for it alone (bit for bit with chunk = 128, where both restart the cumulative
+ * sums of dt*A at the same tokens; otherwise up to the rounding of those sums); an empty sequence hands on its initial state.
+ * f16 batches with headdim = d_state = 64 take a fixed number of launches whatever the number of sequences (both projections and
+ * the gated norm over all tokens; the conv1d and the dt stage of all sequences in one launch; the scan in one launch over
+ * (sequence, head) pairs): many short sequences cost what one long one of the same token count costs. Other shapes and fp32 run
+ * the conv1d and the scan sequence by sequence. */
 size_t b200_mamba2_mixer_prefill_varlen_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t total_tokens);
 int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u, void* out, const int64_t* cu_seqlens, int64_t nseq,

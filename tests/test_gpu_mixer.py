@@ -323,6 +323,46 @@ def test_packed_variable_length_batch_equals_separate_prefills(ops, lens, dtype)
         assert rel_l2(host(got[cu[s]:cu[s + 1]])[None], want["out"]) < (2e-3 if dtype == "f16" else 1e-4)
 
 
+def test_packed_batch_of_many_short_sequences(ops):
+    """256 sequences of 20 to 44 tokens (and a few empty ones) in one packed call: every sequence equals a prefill of it alone
+    bit for bit, states included, and one of them is checked against the oracle. The packed call is a fixed handful of launches."""
+    from anygpu_b200 import capi
+    cfg = dict(SMALL, batch=1, seqlen=64, chunk=128)
+    r = np.random.default_rng(5)
+    lens = [int(v) for v in r.integers(20, 45, 256)]
+    for i in (7, 100, 255):
+        lens[i] = 0
+    total = sum(lens)
+    w = f16w(synth.make_weights(cfg, 14))
+    u = synth.to_f16_values(synth.make_input(cfg, 14, batch=1, seqlen=total)[0])
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16))
+    ud = torch.from_numpy(np.ascontiguousarray(u)).cuda().half()
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+    H, P, N = cfg["nheads"], cfg["headdim"], cfg["d_state"]
+    init = (torch.randn(len(lens), H, P, N, device="cuda", generator=torch.Generator("cuda").manual_seed(4)) * 0.1).contiguous()
+    cache = ops.ZambaMambaCache.zeros(cfg, len(lens), torch.float16)
+    cache.conv_state.fill_(7.0)
+    lib = capi.load()
+    mixer.prefill_varlen(ud, cu, initial_states=init, cache=cache)  # workspace and kernel attributes set up
+    lib.b200_launch_count(1)
+    got = mixer.prefill_varlen(ud, cu, initial_states=init, cache=cache)
+    launches = lib.b200_launch_count(1)
+    assert launches <= 6, launches  # in_proj, conv1d + dt, scan, gated norm, out_proj
+    for s in (0, 1, 7, 99, 100, 101, 254, 255):
+        n = lens[s]
+        if n == 0:
+            assert torch.equal(cache.ssm_state[s], init[s]) and torch.count_nonzero(cache.conv_state[s]) == 0
+            continue
+        one = ops.ZambaMambaCache.zeros(cfg, 1, torch.float16)
+        alone = mixer.prefill(ud[cu[s]:cu[s + 1]].unsqueeze(0).contiguous(), one, initial_states=init[s:s + 1].contiguous())
+        assert torch.equal(got[cu[s]:cu[s + 1]], alone[0]), s
+        assert torch.equal(cache.ssm_state[s], one.ssm_state[0]) and torch.equal(cache.conv_state[s], one.conv_state[0]), s
+    s = 33
+    want = orc.mixer_prefill(u[None, cu[s]:cu[s + 1]], w, dict(cfg, chunk=lens[s]), f16io=True, initial_states=host(init[s:s + 1]))
+    assert_close_f16(host(got[cu[s]:cu[s + 1]])[None], want["out"], "one of 256 packed sequences vs oracle")
+    assert_close_f16(host(cache.ssm_state[s:s + 1]), want["final_state"], "its final state")
+
+
 @pytest.mark.parametrize("bounds", [[0, 128, 256, 384, 512], [0, 100, 101, 300, 512], [0, 512]])
 @pytest.mark.parametrize("dtype", ["f16", "f32"])
 def test_sequence_parallel_segments_emulated_on_one_gpu(ops, bounds, dtype):
