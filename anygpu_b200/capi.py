@@ -63,6 +63,8 @@ SIGNATURES = {
     "b200_mamba2_mixer_prefill_host_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
     "b200_mamba2_mixer_prefill_host": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _i64,
                                               _i64, _vp, _sz, _vp]),
+    "b200_mamba2_mixer_prefill_host_ex": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _i64,
+                                              _i64, _vp, _sz, _vp, _int]),
     "b200_mamba2_mixer_prefill_tp_workspace_bytes": (_sz, [ctypes.POINTER(Mamba2Config), _int, _i64, _i64]),
     "b200_mamba2_mixer_prefill_tp_partial": (_int, [_int, ctypes.POINTER(Mamba2Config), ctypes.POINTER(Mamba2Weights), _vp, _vp, _vp,
                                                     _i64, _i64, _vp, _vp, _vp, _sz, _vp]),

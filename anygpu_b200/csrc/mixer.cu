@@ -87,6 +87,9 @@ constexpr int kTimingSlots = 256;  // mixer calls recorded between two collects
 struct StageTiming
 {
 	bool enabled = false;
+	int last_stage = kStages;  // marks 0 .. last_stage are recorded: kStages = every stage, 1 = the first stage (in_proj) only
+	int every = 1;             // every n-th call is recorded
+	int seen = 0;              // calls since enable
 	int calls = 0;
 	cudaEvent_t ev[kTimingSlots][kStages + 1] = {};
 	bool created = false;
@@ -95,7 +98,8 @@ static StageTiming g_timing;
 
 static void stage_mark(int stage, cudaStream_t st)
 {
-	if (g_timing.enabled && g_timing.calls < kTimingSlots) cudaEventRecord(g_timing.ev[g_timing.calls][stage], st);
+	if (g_timing.enabled && stage <= g_timing.last_stage && g_timing.seen % g_timing.every == 0 && g_timing.calls < kTimingSlots)
+		cudaEventRecord(g_timing.ev[g_timing.calls][stage], st);
 }
 
 struct PrefillWs
@@ -239,7 +243,11 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 		residual, ldr, st);
 	if (rc) return rc;
 	stage_mark(5, st);
-	if (g_timing.enabled && g_timing.calls < kTimingSlots) ++g_timing.calls;
+	if (g_timing.enabled)
+	{
+		if (g_timing.seen % g_timing.every == 0 && g_timing.calls < kTimingSlots) ++g_timing.calls;
+		++g_timing.seen;
+	}
 	return B200_OK;
 }
 
@@ -261,6 +269,9 @@ extern "C" int b200_stage_timing_enable(int enable)
 		g_timing.created = true;
 	}
 	g_timing.enabled = enable != 0;
+	g_timing.last_stage = enable == 2 ? 1 : kStages;
+	g_timing.every = enable == 2 ? 4 : 1;
+	g_timing.seen = 0;
 	g_timing.calls = 0;
 	return B200_OK;
 }
@@ -272,8 +283,8 @@ extern "C" int b200_stage_timing_collect(float* stage_ms, int* calls)
 	*calls = g_timing.calls;
 	for (int i = 0; i < g_timing.calls; ++i)
 	{
-		B200_CUDA_TRY(cudaEventSynchronize(g_timing.ev[i][kStages]));
-		for (int j = 0; j < kStages; ++j)
+		B200_CUDA_TRY(cudaEventSynchronize(g_timing.ev[i][g_timing.last_stage]));
+		for (int j = 0; j < g_timing.last_stage; ++j)
 		{
 			float ms = 0.f;
 			B200_CUDA_TRY(cudaEventElapsedTime(&ms, g_timing.ev[i][j], g_timing.ev[i][j + 1]));
@@ -293,15 +304,21 @@ extern "C" size_t b200_mamba2_mixer_prefill_host_workspace_bytes(const b200_mamb
 	return 2 * io + carve_prefill(nullptr, cfg, m, batch, seqlen).bytes;
 }
 
-// Copy engines of the host-buffer entry point: one stream for host->device, one for device->host, created once per
-// device, plus per-sequence events. The three activities of consecutive sequences overlap:
+// Engines of the host-buffer entry point: one stream for host->device, one for the mixer, one for device->host, created
+// once per device, plus per-sequence events. The three activities of consecutive sequences overlap:
 //   copy-in(i+1)  ||  mixer(i)  ||  copy-out(i-1)
+// The caller's stream only hands over to them at the start of a call and waits for the last copy-out at its end.
 namespace b200 {
 struct HostPipe
 {
-	cudaStream_t s_in = nullptr, s_out = nullptr;
+	cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
 	cudaEvent_t ev_start = nullptr, ev_end = nullptr;
-	std::vector<cudaEvent_t> ev_in, ev_done;
+	std::vector<cudaEvent_t> ev_in, ev_done, ev_out;  // per sequence: copied in, mixer done, copied out
+	// the call before this one on the device: where its staging tensors were, how it was cut into sequences, and its stream
+	const void* last_ws = nullptr;
+	int64_t last_batch = 0;
+	size_t last_seq_bytes = 0;
+	cudaStream_t last_stream = nullptr;
 };
 static int host_pipe(HostPipe** out, int64_t nchunks)
 {
@@ -313,28 +330,32 @@ static int host_pipe(HostPipe** out, int64_t nchunks)
 	if (!p.s_in)
 	{
 		B200_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_in, cudaStreamNonBlocking));
+		B200_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_comp, cudaStreamNonBlocking));
 		B200_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_out, cudaStreamNonBlocking));
 		B200_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_start, cudaEventDisableTiming));
 		B200_CUDA_TRY(cudaEventCreateWithFlags(&p.ev_end, cudaEventDisableTiming));
 	}
 	while (static_cast<int64_t>(p.ev_in.size()) < nchunks)
 	{
-		cudaEvent_t a, b;
+		cudaEvent_t a, b, c;
 		B200_CUDA_TRY(cudaEventCreateWithFlags(&a, cudaEventDisableTiming));
 		B200_CUDA_TRY(cudaEventCreateWithFlags(&b, cudaEventDisableTiming));
+		B200_CUDA_TRY(cudaEventCreateWithFlags(&c, cudaEventDisableTiming));
 		p.ev_in.push_back(a);
 		p.ev_done.push_back(b);
+		p.ev_out.push_back(c);
 	}
 	*out = &p;
 	return B200_OK;
 }
 }  // namespace b200
 
-extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+extern "C" int b200_mamba2_mixer_prefill_host_ex(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
-	void* workspace, size_t workspace_bytes, void* stream)
+	void* workspace, size_t workspace_bytes, void* stream, int flags)
 {
 	if (!cfg || !w || !u_host || !out_host) return B200_ERR_NULL;
+	if (flags & ~B200_HOST_OVERLAP) return B200_ERR_UNSUPPORTED;
 	MixerDims m;
 	if (!dims_ok(cfg, dtype, &m) || batch < 0 || seqlen < 0) return B200_ERR_BAD_SHAPE;
 	if (batch == 0 || seqlen == 0) return B200_OK;
@@ -359,29 +380,57 @@ extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_confi
 	const size_t seq_bytes = static_cast<size_t>(seqlen) * cfg->d_model * m.esz;
 	const char* uh = static_cast<const char*>(u_host);
 	char* oh = static_cast<char*>(out_host);
-	// the copy streams start after whatever the caller already queued on `stream`
-	B200_CUDA_TRY(cudaEventRecord(hp->ev_start, st));
-	B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_in, hp->ev_start, 0));
-	B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_start, 0));
-	for (int64_t i = 0; i < batch; ++i)
+	// What does the call wait for? By default for whatever the caller already queued on `stream` (which may be what fills u_host
+	// or the weights), and that includes the copy-out of the call before this one. With B200_HOST_OVERLAP the caller vouches that
+	// the call needs nothing queued on `stream` since the call before it; a call that repeats that one (same workspace, stream and
+	// shape) then only keeps off each staging slice while the earlier call still uses it: its copy-in of sequence i waits for the
+	// earlier mixer of sequence i, its mixer of sequence i for the earlier copy-out of sequence i. Back-to-back calls so keep both
+	// copy directions busy. Any other history, and a stream that is being captured into a graph, takes the default.
+	cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+	B200_CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
+	const bool repeat = (flags & B200_HOST_OVERLAP) && capturing == cudaStreamCaptureStatusNone && hp->last_ws == workspace &&
+		hp->last_batch == batch && hp->last_seq_bytes == seq_bytes && hp->last_stream == st;
+	if (!repeat)
 	{
-		B200_CUDA_TRY(cudaMemcpyAsync(u_dev + i * seq_bytes, uh + i * seq_bytes, seq_bytes, cudaMemcpyHostToDevice, hp->s_in));
-		B200_CUDA_TRY(cudaEventRecord(hp->ev_in[i], hp->s_in));
+		B200_CUDA_TRY(cudaEventRecord(hp->ev_start, st));
+		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_in, hp->ev_start, 0));
+		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_comp, hp->ev_start, 0));
+		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_start, 0));
 	}
 	for (int64_t i = 0; i < batch; ++i)
 	{
-		B200_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev_in[i], 0));
+		if (repeat) B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_in, hp->ev_done[i], 0));  // recorded by the call before: its mixer of slice i
+		B200_CUDA_TRY(cudaMemcpyAsync(u_dev + i * seq_bytes, uh + i * seq_bytes, seq_bytes, cudaMemcpyHostToDevice, hp->s_in));
+		B200_CUDA_TRY(cudaEventRecord(hp->ev_in[i], hp->s_in));
+	}
+	hp->last_ws = nullptr;  // an early return below leaves no history to build on
+	for (int64_t i = 0; i < batch; ++i)
+	{
+		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_comp, hp->ev_in[i], 0));
+		if (repeat) B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_comp, hp->ev_out[i], 0));  // the call before: its copy-out of slice i
 		rc = b200_mamba2_mixer_prefill(dtype, cfg, w, u_dev + i * seq_bytes, out_dev + i * seq_bytes, 1, seqlen, nullptr, nullptr, nullptr,
-			p + 2 * io, inner, stream);
+			p + 2 * io, inner, hp->s_comp);
 		if (rc) return rc;
-		B200_CUDA_TRY(cudaEventRecord(hp->ev_done[i], st));
+		B200_CUDA_TRY(cudaEventRecord(hp->ev_done[i], hp->s_comp));
 		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_done[i], 0));
 		B200_CUDA_TRY(cudaMemcpyAsync(oh + i * seq_bytes, out_dev + i * seq_bytes, seq_bytes, cudaMemcpyDeviceToHost, hp->s_out));
+		B200_CUDA_TRY(cudaEventRecord(hp->ev_out[i], hp->s_out));
 	}
 	// work queued on `stream` after this call (and a synchronisation of `stream`) sees the finished output
 	B200_CUDA_TRY(cudaEventRecord(hp->ev_end, hp->s_out));
 	B200_CUDA_TRY(cudaStreamWaitEvent(st, hp->ev_end, 0));
+	hp->last_ws = workspace;
+	hp->last_batch = batch;
+	hp->last_seq_bytes = seq_bytes;
+	hp->last_stream = st;
 	return B200_OK;
+}
+
+extern "C" int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
+	void* workspace, size_t workspace_bytes, void* stream)
+{
+	return b200_mamba2_mixer_prefill_host_ex(dtype, cfg, w, u_host, out_host, batch, seqlen, workspace, workspace_bytes, stream, 0);
 }
 
 // ---- head-sharded tensor parallelism ---------------------------------------------------------------------------------

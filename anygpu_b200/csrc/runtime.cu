@@ -59,7 +59,7 @@ extern "C" const char* b200_status_string(int status)
 
 extern "C" int b200_last_cuda_error(void) { return g_last_cuda_error; }
 
-extern "C" int b200_abi_version(void) { return 2; }
+extern "C" int b200_abi_version(void) { return 3; }
 
 extern "C" long long b200_launch_count(int reset)
 {

@@ -265,14 +265,17 @@ class Mamba2Mixer:
                   _p(ws), ws.numel(), _stream())
         return out
 
-    def prefill_host(self, u_host, out_host):
-        """Same with HOST (pinned) tensors: H2D copy, mixer, D2H copy, all inside the one C-ABI call."""
+    def prefill_host(self, u_host, out_host, overlap=False):
+        """Same with HOST (pinned) tensors: H2D copy, mixer, D2H copy, all inside the one C-ABI call. overlap=True vouches
+        that the call needs nothing queued on the stream since the previous call (u_host filled by the CPU, weights untouched),
+        which lets a call run under the copy-out of the call before it (B200_HOST_OVERLAP)."""
         b, l, _ = u_host.shape
         assert not u_host.is_cuda and not out_host.is_cuda and u_host.is_contiguous() and out_host.is_contiguous()
         lib = capi.load()
         ws = self._ensure_ws(lib.b200_mamba2_mixer_prefill_host_workspace_bytes(ctypes.byref(self.c_cfg), _DT[self.dtype], b, l))
-        capi.call("b200_mamba2_mixer_prefill_host", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w),
-                  ctypes.c_void_p(u_host.data_ptr()), ctypes.c_void_p(out_host.data_ptr()), b, l, _p(ws), ws.numel(), _stream())
+        capi.call("b200_mamba2_mixer_prefill_host_ex", _DT[self.dtype], ctypes.byref(self.c_cfg), ctypes.byref(self.c_w),
+                  ctypes.c_void_p(u_host.data_ptr()), ctypes.c_void_p(out_host.data_ptr()), b, l, _p(ws), ws.numel(), _stream(),
+                  1 if overlap else 0)
         return out_host
 
     def decode(self, u_t, cache, out=None):

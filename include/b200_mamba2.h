@@ -216,13 +216,27 @@ int b200_mamba2_mixer_prefill(int dtype, const b200_mamba2_config* cfg, const b2
 /* Same call for callers holding HOST tensors (anyGPU's Tensor<dtype,CPU>::copy_to_cuda / copy_to_host pattern,
  * srcs/core/tensor.hpp:318-370): copies u_host in, runs the mixer, copies out_host back. The call is asynchronous and
  * ordered on `stream` (work queued on `stream` afterwards, or a synchronisation of it, sees out_host complete); inside,
- * the sequences of the batch are pipelined over two library-owned copy streams so that the copy-in of sequence i+1, the
- * mixer of sequence i and the copy-out of sequence i-1 overlap. Pinned host memory is needed for that overlap.
+ * the sequences of the batch are pipelined over three library-owned streams (copy-in, mixer, copy-out) so that the copy-in
+ * of sequence i+1, the mixer of sequence i and the copy-out of sequence i-1 overlap. Pinned host memory is needed for that overlap.
  * The workspace must be b200_mamba2_mixer_prefill_host_workspace_bytes large (it also holds the staging tensors). */
 size_t b200_mamba2_mixer_prefill_host_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t batch, int64_t seqlen);
 int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
 	void* workspace, size_t workspace_bytes, void* stream);
+/* The same with flags. B200_HOST_OVERLAP: the caller vouches that this call needs nothing that was queued on `stream`
+ * since the previous call of this function: u_host was filled by the CPU (not by work still queued on `stream`) and the
+ * weights have not been touched. When the call then repeats the one before it (same workspace, stream, batch and sequence
+ * length) it does not wait for that call to finish: its copy-in of sequence i only waits until the earlier call's mixer
+ * has read staging slice i, its mixer of sequence i until the earlier copy-out of slice i is done. The copy-in of call k+1
+ * so runs under the compute and the copy-out of call k, and a loop of calls is bound by the slower of one PCIe direction
+ * and the compute instead of their sum per call. Ordering of out_host is unchanged (complete for work queued on `stream`
+ * afterwards, and for a synchronisation of it). The mixer kernels of this entry point run on a library-owned stream. A
+ * workspace is used from one stream at a time. During stream capture the flag is ignored. Other flag bits:
+ * B200_ERR_UNSUPPORTED. */
+enum { B200_HOST_OVERLAP = 1 };
+int b200_mamba2_mixer_prefill_host_ex(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
+	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
+	void* workspace, size_t workspace_bytes, void* stream, int flags);
 
 /* ---- head-sharded tensor parallelism (prefill) -----------------------------------------------------------------
  * No counterpart in anyGPU (single device only, srcs/core/core.cpp:115-122). Rank r of TP owns nheads/TP heads: cfg_local
@@ -313,7 +327,11 @@ int b200_mamba2_decoder_decode(int dtype, const b200_mamba2_config* cfg, const b
  * When enabled, the prefill mixer records CUDA events on the caller's stream between its five stages
  * (in_proj, conv1d, ssd, gated_rmsnorm, out_proj) for up to 256 calls. b200_stage_timing_collect waits for the recorded
  * calls, writes the SUM of each stage's milliseconds over those calls to stage_ms[5] and their number to *calls, and
- * starts a new window. Not thread safe; meant for a benchmark harness. */
+ * starts a new window. enable = 2 records only the two events around in_proj, and only in every fourth call (the other
+ * entries of stage_ms stay 0, *calls counts the recorded calls): an event between two kernels costs about 2.5 us of the
+ * step, so a harness that times whole steps and wants the dominant kernel's duration from the same steps uses 2 there and
+ * 1 in a pass of its own. Not thread safe; meant for a benchmark
+ * harness. */
 int b200_stage_timing_enable(int enable);
 int b200_stage_timing_collect(float* stage_ms, int* calls);
 

@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     lib = capi.load()
     for name in declared_functions():
         assert hasattr(lib, name), name
-    assert lib.b200_abi_version() == 2
+    assert lib.b200_abi_version() == 3
     assert lib.b200_status_string(0) == b"ok"
     assert lib.b200_status_string(-4) == b"device-side wait timed out"
 

@@ -106,6 +106,32 @@ def test_mixer_prefill_host_call_equals_device_call(ops):
     assert torch.equal(dev_out, out_pin)
 
 
+def test_back_to_back_host_calls_with_ready_inputs_overlap_and_stay_correct(ops):
+    """B200_HOST_OVERLAP: consecutive calls on one workspace and stream run their copy-in under the call before them.
+    Six calls with different inputs and outputs queued without a synchronisation in between, then one call of another shape
+    (which must fall back to the ordered form), every output equal to the device call's bit for bit. The last call feeds on the
+    output of the one before it WITHOUT the flag, so it has to wait for that copy-out."""
+    cfg = SMALL
+    w = f16w(synth.make_weights(cfg, 2))
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(w, torch.float16))
+    us = [torch.from_numpy(synth.make_input(cfg, 40 + i)).half() for i in range(6)]
+    want = [mixer.prefill(u.cuda()).cpu() for u in us]
+    pins = [u.pin_memory() for u in us]
+    outs = [torch.zeros_like(u).pin_memory() for u in us]
+    for u, o in zip(pins, outs):
+        mixer.prefill_host(u, o, overlap=True)
+    short = torch.from_numpy(synth.make_input(cfg, 50, batch=1, seqlen=100)).half()
+    short_pin, short_out = short.pin_memory(), torch.zeros_like(short).pin_memory()
+    mixer.prefill_host(short_pin, short_out, overlap=True)
+    chained = torch.zeros_like(short).pin_memory()
+    mixer.prefill_host(short_out, chained)  # input produced by the call before: ordered on the stream
+    torch.cuda.synchronize()
+    for i in range(6):
+        assert torch.equal(outs[i], want[i]), i
+    assert torch.equal(short_out, mixer.prefill(short.cuda()).cpu())
+    assert torch.equal(chained, mixer.prefill(short_out.cuda()).cpu())
+
+
 @pytest.mark.parametrize("dtype", ["f16", "f16_nk", "f32"])
 def test_mixer_decode_steps(ops, dtype):
     cfg = dict(SMALL, batch=5)
