@@ -313,12 +313,13 @@ struct HostPipe
 {
 	cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
 	cudaEvent_t ev_start = nullptr, ev_end = nullptr;
-	std::vector<cudaEvent_t> ev_in, ev_done, ev_out;  // per sequence: copied in, mixer done, copied out
+	std::vector<cudaEvent_t> ev_in, ev_done, ev_out;  // per slice of sequences: copied in, mixer done, copied out
 	// the call before this one on the device: where its staging tensors were, how it was cut into sequences, and its stream
 	const void* last_ws = nullptr;
 	int64_t last_batch = 0;
 	size_t last_seq_bytes = 0;
 	cudaStream_t last_stream = nullptr;
+	int last_flags = 0;
 };
 static int host_pipe(HostPipe** out, int64_t nchunks)
 {
@@ -370,26 +371,38 @@ extern "C" int b200_mamba2_mixer_prefill_host_ex(int dtype, const b200_mamba2_co
 	char* out_dev = p + io;
 	cudaStream_t st = static_cast<cudaStream_t>(stream);
 
-	// one sequence per pipeline step (sequences are independent through every stage of the mixer). The copy streams and events
-	// are shared by all calls on a device: calls from several host threads enqueue one after the other.
+	// A pipeline step is a slice of whole sequences (they are independent through every stage of the mixer): one sequence by
+	// default, which starts the compute soonest; with B200_HOST_OVERLAP enough sequences for ~4096 tokens (but at least two slices
+	// per call), because there the loop's rate counts and a lone short sequence leaves the GPU underfilled (the scan walks a
+	// sequence block by block whatever the batch). The copy streams and events are shared by all calls on a device: calls from
+	// several host threads enqueue one after the other.
+	int64_t per_slice = 1;
+	if (flags & B200_HOST_OVERLAP)
+	{
+		per_slice = cdiv(4096, seqlen);
+		if (per_slice > batch / 2) per_slice = batch / 2;
+		if (per_slice < 1) per_slice = 1;
+	}
+	const int64_t nslices = cdiv(batch, per_slice);
 	static std::mutex pipe_mutex;
 	std::lock_guard<std::mutex> pipe_lock(pipe_mutex);
 	HostPipe* hp = nullptr;
-	int rc = host_pipe(&hp, batch);
+	int rc = host_pipe(&hp, nslices);
 	if (rc) return rc;
 	const size_t seq_bytes = static_cast<size_t>(seqlen) * cfg->d_model * m.esz;
+	const size_t slice_bytes = static_cast<size_t>(per_slice) * seq_bytes;
 	const char* uh = static_cast<const char*>(u_host);
 	char* oh = static_cast<char*>(out_host);
 	// What does the call wait for? By default for whatever the caller already queued on `stream` (which may be what fills u_host
 	// or the weights), and that includes the copy-out of the call before this one. With B200_HOST_OVERLAP the caller vouches that
-	// the call needs nothing queued on `stream` since the call before it; a call that repeats that one (same workspace, stream and
-	// shape) then only keeps off each staging slice while the earlier call still uses it: its copy-in of sequence i waits for the
-	// earlier mixer of sequence i, its mixer of sequence i for the earlier copy-out of sequence i. Back-to-back calls so keep both
+	// the call needs nothing queued on `stream` since the call before it; a call that repeats that one (same workspace, stream,
+	// shape and flags) then only keeps off each staging slice while the earlier call still uses it: its copy-in of slice i waits
+	// for the earlier mixer of slice i, its mixer of slice i for the earlier copy-out of slice i. Back-to-back calls so keep both
 	// copy directions busy. Any other history, and a stream that is being captured into a graph, takes the default.
 	cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
 	B200_CUDA_TRY(cudaStreamIsCapturing(st, &capturing));
 	const bool repeat = (flags & B200_HOST_OVERLAP) && capturing == cudaStreamCaptureStatusNone && hp->last_ws == workspace &&
-		hp->last_batch == batch && hp->last_seq_bytes == seq_bytes && hp->last_stream == st;
+		hp->last_batch == batch && hp->last_seq_bytes == seq_bytes && hp->last_stream == st && hp->last_flags == flags;
 	if (!repeat)
 	{
 		B200_CUDA_TRY(cudaEventRecord(hp->ev_start, st));
@@ -397,23 +410,24 @@ extern "C" int b200_mamba2_mixer_prefill_host_ex(int dtype, const b200_mamba2_co
 		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_comp, hp->ev_start, 0));
 		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_start, 0));
 	}
-	for (int64_t i = 0; i < batch; ++i)
+	auto bytes_of = [&](int64_t i) { return static_cast<size_t>((i + 1) * per_slice <= batch ? per_slice : batch - i * per_slice) * seq_bytes; };
+	for (int64_t i = 0; i < nslices; ++i)
 	{
 		if (repeat) B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_in, hp->ev_done[i], 0));  // recorded by the call before: its mixer of slice i
-		B200_CUDA_TRY(cudaMemcpyAsync(u_dev + i * seq_bytes, uh + i * seq_bytes, seq_bytes, cudaMemcpyHostToDevice, hp->s_in));
+		B200_CUDA_TRY(cudaMemcpyAsync(u_dev + i * slice_bytes, uh + i * slice_bytes, bytes_of(i), cudaMemcpyHostToDevice, hp->s_in));
 		B200_CUDA_TRY(cudaEventRecord(hp->ev_in[i], hp->s_in));
 	}
 	hp->last_ws = nullptr;  // an early return below leaves no history to build on
-	for (int64_t i = 0; i < batch; ++i)
+	for (int64_t i = 0; i < nslices; ++i)
 	{
 		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_comp, hp->ev_in[i], 0));
 		if (repeat) B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_comp, hp->ev_out[i], 0));  // the call before: its copy-out of slice i
-		rc = b200_mamba2_mixer_prefill(dtype, cfg, w, u_dev + i * seq_bytes, out_dev + i * seq_bytes, 1, seqlen, nullptr, nullptr, nullptr,
-			p + 2 * io, inner, hp->s_comp);
+		rc = b200_mamba2_mixer_prefill(dtype, cfg, w, u_dev + i * slice_bytes, out_dev + i * slice_bytes,
+			static_cast<int64_t>(bytes_of(i) / seq_bytes), seqlen, nullptr, nullptr, nullptr, p + 2 * io, inner, hp->s_comp);
 		if (rc) return rc;
 		B200_CUDA_TRY(cudaEventRecord(hp->ev_done[i], hp->s_comp));
 		B200_CUDA_TRY(cudaStreamWaitEvent(hp->s_out, hp->ev_done[i], 0));
-		B200_CUDA_TRY(cudaMemcpyAsync(oh + i * seq_bytes, out_dev + i * seq_bytes, seq_bytes, cudaMemcpyDeviceToHost, hp->s_out));
+		B200_CUDA_TRY(cudaMemcpyAsync(oh + i * slice_bytes, out_dev + i * slice_bytes, bytes_of(i), cudaMemcpyDeviceToHost, hp->s_out));
 		B200_CUDA_TRY(cudaEventRecord(hp->ev_out[i], hp->s_out));
 	}
 	// work queued on `stream` after this call (and a synchronisation of `stream`) sees the finished output
@@ -423,6 +437,7 @@ extern "C" int b200_mamba2_mixer_prefill_host_ex(int dtype, const b200_mamba2_co
 	hp->last_batch = batch;
 	hp->last_seq_bytes = seq_bytes;
 	hp->last_stream = st;
+	hp->last_flags = flags;
 	return B200_OK;
 }
 

@@ -602,8 +602,10 @@ def run_gpu(args):
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
+    t_enq0 = time.perf_counter()
     for i in range(args.steps):
         mixer.prefill_host(u_pin[i % 2], out_pin, overlap=True)
+    e2e_enqueue_ms = (time.perf_counter() - t_enq0) * 1e3 / args.steps
     e1.record()
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1))
@@ -745,6 +747,7 @@ def run_gpu(args):
             "data": "synthetic", "config": _config_dict(args.workload, cfg, world), "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
                     "ms_per_step": e2e_ms / args.steps, "ms_one_call_alone": e2e_single_ms,
+                    "host_enqueue_ms_per_step": e2e_enqueue_ms,
                     "call": "b200_mamba2_mixer_prefill_host_ex with B200_HOST_OVERLAP (the inputs sit complete in pinned host memory before "
                             "each call, the weights do not change), the steps queued back to back: the copy-in of step k+1 runs under the compute and copy-out of step k; "
                             "every step copies its own input in and its own output out"},

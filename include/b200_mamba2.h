@@ -226,8 +226,10 @@ int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, con
 /* The same with flags. B200_HOST_OVERLAP: the caller vouches that this call needs nothing that was queued on `stream`
  * since the previous call of this function: u_host was filled by the CPU (not by work still queued on `stream`) and the
  * weights have not been touched. When the call then repeats the one before it (same workspace, stream, batch and sequence
- * length) it does not wait for that call to finish: its copy-in of sequence i only waits until the earlier call's mixer
- * has read staging slice i, its mixer of sequence i until the earlier copy-out of slice i is done. The copy-in of call k+1
+ * length) it does not wait for that call to finish: its copy-in of slice i only waits until the earlier call's mixer
+ * has read staging slice i, its mixer of slice i until the earlier copy-out of slice i is done (a slice is one sequence by
+ * default; with the flag it is as many whole sequences as make ~4096 tokens, at least two slices per call, since a loop is
+ * after throughput and a lone short sequence underfills the GPU). The copy-in of call k+1
  * so runs under the compute and the copy-out of call k, and a loop of calls is bound by the slower of one PCIe direction
  * and the compute instead of their sum per call. Ordering of out_host is unchanged (complete for work queued on `stream`
  * afterwards, and for a synchronisation of it). The mixer kernels of this entry point run on a library-owned stream. A
