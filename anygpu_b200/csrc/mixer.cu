@@ -99,7 +99,15 @@ static StageTiming g_timing;
 static void stage_mark(int stage, cudaStream_t st)
 {
 	if (g_timing.enabled && stage <= g_timing.last_stage && g_timing.seen % g_timing.every == 0 && g_timing.calls < kTimingSlots)
-		cudaEventRecord(g_timing.ev[g_timing.calls][stage], st);
+	{
+		// in a stream that is being captured an ordinary record would only become an edge of the graph; the external form makes a
+		// node that records the event on every replay, so a harness can time the stages of a replayed graph
+		cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+		if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusActive)
+			cudaEventRecordWithFlags(g_timing.ev[g_timing.calls][stage], st, cudaEventRecordExternal);
+		else
+			cudaEventRecord(g_timing.ev[g_timing.calls][stage], st);
+	}
 }
 
 struct PrefillWs

@@ -556,21 +556,36 @@ def run_gpu(args):
             sampler = ClockSampler(local_rank)  # nvidia-smi at its 100 ms period: few samples fall into a short region
         sampler.start()
         time.sleep(0.25)
-    # inside the timed region only the dominant kernel (in_proj, the first of the step) is bracketed by events, in every fourth
-    # step: an event between two kernels costs ~2.5 us, six of them 3% of the step; the table of all five stages comes from a
-    # pass of its own below
+    # The K timed steps are one CUDA graph: the same calls of the public prefill entry point, captured once and replayed, so that
+    # the GPU runs the 5 x K kernels back to back (launched one by one from the host they leave ~2 us between kernels, 10 us per
+    # step). Inside the timed region only the dominant kernel (in_proj, the first of the step) is bracketed by events, in every
+    # fourth step: an event between two kernels costs ~2.5 us, six of them 3% of the step; the table of all five stages comes
+    # from a pass of its own below. `--no-graph` times the same steps launched from the host.
     lib.b200_stage_timing_enable(2)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
+    graph = None
     lib.b200_launch_count(1)
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(args.steps):
+                mixer.prefill(us[i % nbuf], out=out)
+        gpu_launches = int(lib.b200_launch_count(1))  # kernel nodes of the graph: counted by the library at its launch sites during capture
+        graph.replay()  # one untimed replay: the first launch of a graph also uploads it
+        torch.cuda.synchronize()
+    barrier()
     t_wall0 = time.time()
     ev0.record()
-    for i in range(args.steps):
-        mixer.prefill(us[i % nbuf], out=out)
+    if graph is not None:
+        graph.replay()
+    else:
+        for i in range(args.steps):
+            mixer.prefill(us[i % nbuf], out=out)
     ev1.record()
     barrier()
     t_wall1 = time.time()
-    gpu_launches = int(lib.b200_launch_count(1))  # kernels this library launched between the two events
+    if graph is None:
+        gpu_launches = int(lib.b200_launch_count(1))  # kernels this library launched between the two events
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
     stage_ms = (ctypes.c_float * 5)()
     calls = ctypes.c_int(0)
@@ -751,7 +766,11 @@ def run_gpu(args):
                     "call": "b200_mamba2_mixer_prefill_host_ex with B200_HOST_OVERLAP (the inputs sit complete in pinned host memory before "
                             "each call, the weights do not change), the steps queued back to back: the copy-in of step k+1 runs under the compute and copy-out of step k; "
                             "every step copies its own input in and its own output out"},
-            "gpu_launches": gpu_launches, "gpu_launches_note": "counted by the library at its launch sites between the two events of the timed region (rank 0)",
+            "gpu_launches": gpu_launches,
+            "gpu_launches_note": ("kernel nodes of the CUDA graph that is the timed region, counted by the library at its launch sites while the graph was captured (rank 0)"
+                                  if not args.no_graph else "counted by the library at its launch sites between the two events of the timed region (rank 0)"),
+            "timed_region": ("one CUDA graph of the K steps (captured calls of b200_mamba2_mixer_prefill), replayed once" if not args.no_graph
+                             else "K calls of b200_mamba2_mixer_prefill launched from the host"),
             "roofline": roofline, "whole_step": whole, "sustained": sustained, "decode": decode, "conv_cfg1": conv1,
             "copy_only": copy_only, "cfg4_dp": cfg4_dp, "cfg4_tp": cfg4_tp, "cpu_baseline": cpu}
     print(json.dumps(line))
@@ -1078,6 +1097,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="only the prefill line: no sustained / decode / conv / copy-only / cfg4 records")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps from the host instead of replaying them as one CUDA graph")
     ap.add_argument("--no-cfg4", action="store_true", help="skip the two Zamba2-7B-shaped records (batch-sharded, head-sharded)")
     ap.add_argument("--mode", default="dp", choices=["dp", "tp", "sp"],
                     help="dp: batch-sharded (default); tp: head-sharded cfg4 layer; sp: one long sequence split over the ranks")

@@ -332,8 +332,9 @@ int b200_mamba2_decoder_decode(int dtype, const b200_mamba2_config* cfg, const b
  * starts a new window. enable = 2 records only the two events around in_proj, and only in every fourth call (the other
  * entries of stage_ms stay 0, *calls counts the recorded calls): an event between two kernels costs about 2.5 us of the
  * step, so a harness that times whole steps and wants the dominant kernel's duration from the same steps uses 2 there and
- * 1 in a pass of its own. Not thread safe; meant for a benchmark
- * harness. */
+ * 1 in a pass of its own. Calls captured into a CUDA graph while timing is enabled record their events on every replay
+ * (collect after the replay, not after the capture; a window then holds the calls of one capture). Not thread safe;
+ * meant for a benchmark harness. */
 int b200_stage_timing_enable(int enable);
 int b200_stage_timing_collect(float* stage_ms, int* calls);
 
