@@ -258,11 +258,12 @@ static int ssm_update(float* state, const void* x, int64_t xs, const void* dt, i
 		if (blocks > 0x7fffffffLL) return B200_ERR_UNSUPPORTED;
 		ssm_update_scalar_kernel<T><<<static_cast<unsigned>(blocks), 256, 0, st>>>(state, xp, xs, dtp, dts, A, a_is_log, bp, bs,
 			cp, cs, D, dt_bias, yp, ys, nrows, static_cast<int>(H), p, static_cast<int>(G), static_cast<int>(N), dt_softplus);
+		count_launch();  // launch_chained has counted the vector kernel
 	}
 #undef B200_SSM_LAUNCH
 #undef B200_SSM_RPT
 	B200_CUDA_TRY(launch_rc);
-	B200_LAUNCH_CHECK();
+	B200_CUDA_TRY(cudaGetLastError());
 	return B200_OK;
 }
 
