@@ -58,6 +58,10 @@ def test_null_and_shape_validation_needs_no_gpu():
     assert lib.b200_mamba_chunk_scan_combined(*args, 1, 32, 8, 8, 1, 16, 32, 1, one, 16, None) == -3  # workspace too small
     assert lib.b200_selective_state_update(capi.F16, None, one, 64, one, 8, one, 0, one, 16, one, 16, None, None, one, 64,
                                            1, 8, 8, 1, 16, 1, None) == -7
+    # host-buffer entry point: flag bits it does not know are refused before anything else is looked at
+    cfg, w = capi.Mamba2Config(), capi.Mamba2Weights()
+    assert lib.b200_mamba2_mixer_prefill_host_ex(capi.F16, ctypes.byref(cfg), ctypes.byref(w), one, one, 1, 8, one, 1 << 20, None, 2) == -6
+    assert lib.b200_mamba2_mixer_prefill_host_ex(capi.F16, ctypes.byref(cfg), ctypes.byref(w), None, one, 1, 8, one, 1 << 20, None, 1) == -7
 
 
 def test_workspace_queries():

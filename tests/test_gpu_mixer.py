@@ -106,6 +106,44 @@ def test_mixer_prefill_host_call_equals_device_call(ops):
     assert torch.equal(dev_out, out_pin)
 
 
+def test_stage_timing_windows_plain_and_inside_a_captured_graph(ops):
+    """b200_stage_timing_*: every stage of every call (mode 1), in_proj of every fourth call only (mode 2), and calls that were
+    captured into a CUDA graph, whose events are recorded when the graph is replayed."""
+    import ctypes
+    from anygpu_b200 import capi
+    lib = capi.load()
+    cfg = SMALL
+    mixer = ops.Mamba2Mixer(cfg, ops.ZambaMamba2weights.from_numpy(f16w(synth.make_weights(cfg, 2)), torch.float16))
+    u = torch.from_numpy(synth.to_f16_values(synth.make_input(cfg, 2))).cuda().half()
+    out = torch.empty_like(u)
+    want = mixer.prefill(u).clone()
+    ms, calls = (ctypes.c_float * 5)(), ctypes.c_int(0)
+    try:
+        assert lib.b200_stage_timing_enable(1) == 0
+        for _ in range(3):
+            mixer.prefill(u, out=out)
+        assert lib.b200_stage_timing_collect(ms, ctypes.byref(calls)) == 0
+        assert calls.value == 3 and all(0.0 < v < 50.0 for v in ms), (calls.value, list(ms))
+        assert lib.b200_stage_timing_enable(2) == 0
+        for _ in range(8):
+            mixer.prefill(u, out=out)
+        assert lib.b200_stage_timing_collect(ms, ctypes.byref(calls)) == 0
+        assert calls.value == 2 and ms[0] > 0.0 and all(v == 0.0 for v in list(ms)[1:]), (calls.value, list(ms))
+        assert lib.b200_stage_timing_enable(1) == 0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            mixer.prefill(u, out=out)
+            mixer.prefill(u, out=out)
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert lib.b200_stage_timing_collect(ms, ctypes.byref(calls)) == 0
+        assert calls.value == 2 and all(0.0 < v < 50.0 for v in ms), (calls.value, list(ms))
+        assert torch.equal(out, want)
+    finally:
+        lib.b200_stage_timing_enable(0)
+
+
 def test_back_to_back_host_calls_with_ready_inputs_overlap_and_stay_correct(ops):
     """B200_HOST_OVERLAP: consecutive calls on one workspace and stream run their copy-in under the call before them.
     Six calls with different inputs and outputs queued without a synchronisation in between, then one call of another shape
