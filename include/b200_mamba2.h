@@ -284,7 +284,9 @@ int b200_mamba2_mixer_prefill_continue(int dtype, const b200_mamba2_config* cfg,
  * f16 batches with headdim = d_state = 64 take a fixed number of launches whatever the number of sequences (both projections and
  * the gated norm over all tokens; the conv1d and the dt stage of all sequences in one launch; the scan in one launch over
  * (sequence, head) pairs): many short sequences cost what one long one of the same token count costs. Other shapes and fp32 run
- * the conv1d and the scan sequence by sequence. */
+ * the conv1d and the scan sequence by sequence. The fixed-launch form copies its index arrays from pageable host memory to the
+ * device inside the call (stream-ordered; the host arrays may be freed when the call returns), so the call cannot be captured
+ * into a CUDA graph; cu_seqlens is read on the host during the call only. */
 size_t b200_mamba2_mixer_prefill_varlen_workspace_bytes(const b200_mamba2_config* cfg, int dtype, int64_t total_tokens);
 int b200_mamba2_mixer_prefill_varlen(int dtype, const b200_mamba2_config* cfg, const b200_mamba2_weights* w,
 	const void* u, void* out, const int64_t* cu_seqlens, int64_t nseq,
