@@ -420,6 +420,15 @@ def cfg4_dp_record(torch, dist, ops, bdist, rank, world, steps, total_sequences=
             "steps": steps, "finite": ok}
 
 
+def tp_chunk_schedule(batch, world, chunk):
+    """Sequences per compute / all-reduce pipeline step of a head-sharded run. chunk > 0: that many in every step. chunk == 0: `world`
+    sequences per step, at least 2: the message an all-reduce needs to run at NVLink speed grows with the ranks. Measured at 8 ranks,
+    1 / 2 / 4 / 8 / 16 sequences per step: 7.64 / 6.36 / 5.44 / 5.23 / 5.68 ms; a schedule that tapers at the end (8, 8, 8, 4, 2, 2,
+    to shorten the last all-reduce, which nothing overlaps) measured 5.37 against 5.29 ms at 8 ranks and 14.4 against 14.1 ms at 2."""
+    c = max(1, min(chunk if chunk > 0 else max(2, world), batch))
+    return [min(c, batch - c0) for c0 in range(0, batch, c)]
+
+
 def cfg4_tp_record(torch, dist, ops, bdist, rank, world, steps, chunk, total_sequences=32):
     """Zamba2-7B-shaped layer, head-sharded over the ranks (TP = number of ranks): every rank holds all 32 sequences and
     nheads/TP heads, and the out_proj addends are summed by NCCL all-reduces (f16) together with the per-token sums of squares.
@@ -439,8 +448,9 @@ def cfg4_tp_record(torch, dist, ops, bdist, rank, world, steps, chunk, total_seq
     u = torch.randn(b, l, cfg["d_model"], device="cuda", generator=g).half()
     out = torch.empty_like(u)
     ss = torch.empty(b * l, device="cuda")
-    chunk = max(1, min(chunk if chunk > 0 else max(2, world), b))  # 0: one all-reduce message per `world` sequences (the size NVLS needs grows with the ranks)
-    slices = [(slice(c0, min(c0 + chunk, b)), slice(c0 * l, min(c0 + chunk, b) * l)) for c0 in range(0, b, chunk)]
+    sched = tp_chunk_schedule(b, world, chunk)
+    starts = [sum(sched[:i]) for i in range(len(sched))]
+    slices = [(slice(c0, c0 + n), slice(c0 * l, (c0 + n) * l)) for c0, n in zip(starts, sched)]
 
     def reduce_async(sl, rows):
         if world == 1:
@@ -500,7 +510,7 @@ def cfg4_tp_record(torch, dist, ops, bdist, rank, world, steps, chunk, total_seq
         del whole
     nbytes = b * l * cfg["d_model"] * 2
     rec = {"workload": f"cfg4: Zamba2-7B-shaped mixer prefill, {b} sequences x {l} tokens on every rank, {H} heads sharded {world}-way, "
-                       f"chunks of {chunk} sequence(s)", "scaling": "strong", "tp": world, "steps": steps,
+                       f"pipeline steps of {'/'.join(str(v) for v in sched)} sequences", "scaling": "strong", "tp": world, "steps": steps,
            "ms_per_step_pipelined": t_pipe, "tokens_per_s": b * l / (t_pipe * 1e-3), "ms_compute_only": t_comp,
            "ms_all_reduce_only": t_red, "exposed_ms": t_pipe - t_comp, "all_reduce_bytes_per_step_f16": nbytes,
            "all_reduce_algbw_gbs": (nbytes / (t_red * 1e-3) / 1e9) if t_red > 0 else None, "parity": parity}
@@ -882,12 +892,14 @@ def run_tp(args):
     u = torch.randn(b, l, cfg["d_model"], device="cuda", generator=g).half()
     out = torch.empty_like(u)
     ss = torch.empty(b * l, device="cuda")
-    chunk = min(args.tp_chunk if args.tp_chunk > 0 else max(2, world), b)
+    sched = tp_chunk_schedule(b, world, args.tp_chunk)
+    starts = [sum(sched[:i]) for i in range(len(sched))]
+    chunk = "/".join(str(v) for v in sched)
 
     def step():
         pending = None
-        for c0 in range(0, b, chunk):
-            sl = slice(c0, min(c0 + chunk, b))
+        for c0, n in zip(starts, sched):
+            sl = slice(c0, c0 + n)
             rows = slice(sl.start * l, sl.stop * l)
             mixer.partial(u[sl], partial_out=out[sl], sumsq=ss[rows])
             works = []
@@ -1106,8 +1118,7 @@ def main():
     ap.add_argument("--sp-batch", type=int, default=1)
     ap.add_argument("--tp-batch", type=int, default=32)
     ap.add_argument("--tp-chunk", type=int, default=0,
-                    help="sequences per compute / all-reduce pipeline step of the head-sharded runs (0: as many as ranks, at least 2; "
-                         "measured at 8 ranks: 1 / 2 / 4 / 8 / 16 sequences -> 7.64 / 6.36 / 5.44 / 5.23 / 5.68 ms per step)")
+                    help="sequences per compute / all-reduce pipeline step of the head-sharded runs (0: see tp_chunk_schedule)")
     ap.add_argument("--kernel", default=None, help="time one operator alone (see run_kernel)")
     ap.add_argument("--small", action="store_true", help="with --kernel: profiler-sized case")
     ap.add_argument("--varlen-loop", action="store_true", help="with --kernel varlen: the per-sequence loop instead of the packed call")
