@@ -724,10 +724,15 @@ def run_gpu(args):
                 "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak if achieved else None,
                 "peak_kind": ("burst" if burst else "sustained") + f" cuBLAS bf16, {peaks['source']}; timed region {region_s * 1e3:.1f} ms, "
                              f"median SM clock {clocks.get('sm_mhz') if clocks else None} MHz, power cap {'active' if capped else 'not active'}",
-                # DRAM bytes per launch: the ncu capture of the M=2048 case read the operands from DRAM exactly once and wrote the
-                # output once; scaled by the rows of this launch that is X + W read and Y written = the algorithmic bytes
-                "traffic": float(tokens * cfg["d_model"] * 2 + cfg["d_model"] * d_in_proj * 2 + tokens * d_in_proj * 2),
-                "traffic_note": "scaled from the ncu capture of the M=2048 case (profiles/gemm_f16_tcgen05_in_proj_small.md): operands read once from DRAM, output written once",
+                # DRAM bytes per launch: measured by ncu on this very launch (M = 8192: 79.9 MB read + 107.4 MB written before the kernel
+                # ends; the rest of the output still sits in L2); other shapes: operands read once and output written once, as the capture
+                # of the M = 2048 case showed
+                "traffic": (187.4e6 if (tokens, cfg["d_model"], d_in_proj) == (8192, 2048, 8384)
+                            else float(tokens * cfg["d_model"] * 2 + cfg["d_model"] * d_in_proj * 2 + tokens * d_in_proj * 2)),
+                "traffic_note": ("dram__bytes_read.sum + dram__bytes_write.sum of the full-size launch, one ncu pass (profiles/gemm_f16_tcgen05_in_proj_small.md, "
+                                 "last section); algorithmic bytes X + W + Y = 205.3 MB"
+                                 if (tokens, cfg["d_model"], d_in_proj) == (8192, 2048, 8384)
+                                 else "scaled from the ncu capture of the M=2048 case (profiles/gemm_f16_tcgen05_in_proj_small.md): operands read once from DRAM, output written once"),
                 "peak_burst": peaks["tflops_burst"], "peak_sustained": peaks["tflops_sustained"],
                 "frac_of_burst_peak": achieved / peaks["tflops_burst"] if achieved else None,
                 "frac_of_sustained_peak": achieved / peaks["tflops_sustained"] if achieved else None,
