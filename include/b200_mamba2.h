@@ -224,8 +224,8 @@ int b200_mamba2_mixer_prefill_host(int dtype, const b200_mamba2_config* cfg, con
 	const void* u_host, void* out_host, int64_t batch, int64_t seqlen,
 	void* workspace, size_t workspace_bytes, void* stream);
 /* The same with flags. B200_HOST_OVERLAP: the caller vouches that this call needs nothing that was queued on `stream`
- * since the previous call of this function: u_host was filled by the CPU (not by work still queued on `stream`) and the
- * weights have not been touched. When the call then repeats the one before it (same workspace, stream, batch and sequence
+ * since the previous call of this function: u_host was filled by the CPU (not by work still queued on `stream`), the
+ * weights have not been touched and nothing else has used the workspace in between. When the call then repeats the one before it (same workspace, stream, batch and sequence
  * length) it does not wait for that call to finish: its copy-in of slice i only waits until the earlier call's mixer
  * has read staging slice i, its mixer of slice i until the earlier copy-out of slice i is done (a slice is one sequence by
  * default; with the flag it is as many whole sequences as make ~4096 tokens, at least two slices per call, since a loop is
