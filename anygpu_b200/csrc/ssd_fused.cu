@@ -549,6 +549,7 @@ int ssd_fused_tc(const __half* x, int64_t xs, const __half* Bm, int64_t bs, cons
 bool ssd_fused_varlen_supported(int64_t total_tokens, int64_t nseq, int H, int P, int G, int N, const void* x, int64_t xs, const void* Bm,
 	int64_t bs, const void* Cm, int64_t cs, const void* y, int64_t ys, const float* init, const float* fin)
 {
+	if (fused_override() == 0) return false;  // B200_SSD_FUSED=0 keeps every caller off the one-kernel scan, this one included
 	if (P != 64 || N != 64 || H % G != 0) return false;
 	if (xs % 8 || bs % 8 || cs % 8 || ys % 8) return false;
 	if (!aligned16(x) || !aligned16(Bm) || !aligned16(Cm) || !aligned16(y)) return false;

@@ -387,10 +387,12 @@ def test_packed_variable_length_batch_equals_separate_prefills(ops, lens, dtype)
         assert rel_l2(host(got[cu[s]:cu[s + 1]])[None], want["out"]) < (2e-3 if dtype == "f16" else 1e-4)
 
 
-def test_packed_batch_of_many_short_sequences(ops):
+def test_packed_batch_of_many_short_sequences(ops, monkeypatch):
     """256 sequences of 20 to 44 tokens (and a few empty ones) in one packed call: every sequence equals a prefill of it alone
-    bit for bit, states included, and one of them is checked against the oracle. The packed call is a fixed handful of launches."""
+    bit for bit, states included, and one of them is checked against the oracle. The packed call is a fixed handful of launches
+    (with the scan left to choose its kernel: B200_SSD_FUSED=0 sends this batch through the per-sequence loop)."""
     from anygpu_b200 import capi
+    monkeypatch.delenv("B200_SSD_FUSED", raising=False)
     cfg = dict(SMALL, batch=1, seqlen=64, chunk=128)
     r = np.random.default_rng(5)
     lens = [int(v) for v in r.integers(20, 45, 256)]
