@@ -280,7 +280,8 @@ template <int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) gemm_f16_tcgen05_pair_kernel(
 	const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M,
 	int N, int K, int m_tiles /* of 256 rows */, int n_tiles, uint32_t* err_word, const __half* __restrict__ residual, int64_t ldr,
-	int n_first /* order in which the tiles are dealt: 0 = down the rows of X first, 1 = across the columns of W first */)
+	int n_first /* order in which the tiles are dealt: 0 = down the rows of X first, 1 = across the columns of W first, 2 = the same
+	               from the last row block of X to the first */)
 {
 	using namespace gemm2;
 	using namespace tc;
@@ -333,7 +334,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) g
 			uint32_t phase = 0;
 			for (int tile = pair; tile < num_tiles; tile += npairs)
 			{
-				const int tm = n_first ? tile / n_tiles : tile % m_tiles, tn = n_first ? tile % n_tiles : tile / m_tiles;
+				const int tm = n_first ? (n_first > 1 ? m_tiles - 1 - tile / n_tiles : tile / n_tiles) : tile % m_tiles, tn = n_first ? tile % n_tiles : tile / m_tiles;
 				const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
 				const int n0 = tn * BN + static_cast<int>(rank) * (BN / 2);
 				for (int kb = 0; kb < k_blocks; ++kb)
@@ -420,7 +421,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) g
 		uint32_t nchunk = 0;
 		for (int tile = pair; tile < num_tiles; tile += npairs)
 		{
-			const int tm = n_first ? tile / n_tiles : tile % m_tiles, tn = n_first ? tile % n_tiles : tile / m_tiles;
+			const int tm = n_first ? (n_first > 1 ? m_tiles - 1 - tile / n_tiles : tile / n_tiles) : tile % m_tiles, tn = n_first ? tile % n_tiles : tile / m_tiles;
 			const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
 			const int n0 = tn * BN;
 			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp))
@@ -507,9 +508,11 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 	// Whatever is touched by every wave has to stay in L2 between waves, and what a CTA finds there is about half of the 126 MB
 	// (each die keeps its own copy of lines both use). X of out_proj (67 MB at 8192 tokens, W 17 MB) does not: ncu counted 206 MB
 	// read from DRAM per launch against 84 MB of operands; in_proj (X 34 MB, W 34 MB) read 83 MB against 68 MB. Measured in the
-	// mixer step: out_proj 107.1 -> 106.4 us, step 0.4450 -> 0.4426 ms (its X is partly in L2 from the kernel before it).
+	// mixer step: out_proj 107.1 -> 106.4 us, step 0.4450 -> 0.4426 ms (its X is partly in L2 from the kernel before it). Such an X
+	// is walked from its last row block to its first: whatever produced it most likely wrote the rows in ascending order, so the
+	// last ones are the ones still in L2 (step 0.4366 -> 0.4351 ms).
 	const double x_bytes = 2.0 * M * K, w_bytes = 2.0 * N * K;
-	const int n_first = x_bytes > 48e6 && w_bytes < x_bytes ? 1 : 0;
+	const int n_first = x_bytes > 48e6 && w_bytes < x_bytes ? 2 : 0;  // 2: and from the last row block of X to the first
 	gemm_f16_tcgen05_pair_kernel<B_MN><<<static_cast<unsigned>(2 * pairs), THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles,
 		n_tiles, device_error_word(), residual, ldr, n_first);
 	B200_LAUNCH_CHECK();
