@@ -276,12 +276,30 @@ constexpr int THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 }  // namespace gemm2
 
+// Tile order of the pair kernel. panel = 0: down the rows of X first (tile t -> row block t % m_tiles, column block t / m_tiles).
+// panel = G > 0: the column blocks of W in panels of G; inside a panel across its columns first, then to the next row block, the
+// row blocks taken from the last to the first. A wave of 74 tiles then touches 74 / G row blocks of X and G column blocks of W.
+__device__ __forceinline__ void pair_tile_coords(int tile, int m_tiles, int n_tiles, int panel, int* tm, int* tn)
+{
+	if (panel == 0)
+	{
+		*tm = tile % m_tiles;
+		*tn = tile / m_tiles;
+		return;
+	}
+	const int per_panel = panel * m_tiles;
+	const int p = tile / per_panel;
+	const int r = tile - p * per_panel;
+	const int width = min(panel, n_tiles - p * panel);  // the last panel may be narrower
+	*tm = m_tiles - 1 - r / width;
+	*tn = p * panel + r % width;
+}
+
 template <int B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) gemm_f16_tcgen05_pair_kernel(
 	const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmY, int M,
 	int N, int K, int m_tiles /* of 256 rows */, int n_tiles, uint32_t* err_word, const __half* __restrict__ residual, int64_t ldr,
-	int n_first /* order in which the tiles are dealt: 0 = down the rows of X first, 1 = across the columns of W first, 2 = the same
-	               from the last row block of X to the first */)
+	int panel /* tile order, see pair_tile_coords */)
 {
 	using namespace gemm2;
 	using namespace tc;
@@ -334,7 +352,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) g
 			uint32_t phase = 0;
 			for (int tile = pair; tile < num_tiles; tile += npairs)
 			{
-				const int tm = n_first ? (n_first > 1 ? m_tiles - 1 - tile / n_tiles : tile / n_tiles) : tile % m_tiles, tn = n_first ? tile % n_tiles : tile / m_tiles;
+				int tm, tn;
+				pair_tile_coords(tile, m_tiles, n_tiles, panel, &tm, &tn);
 				const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
 				const int n0 = tn * BN + static_cast<int>(rank) * (BN / 2);
 				for (int kb = 0; kb < k_blocks; ++kb)
@@ -421,7 +440,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1) g
 		uint32_t nchunk = 0;
 		for (int tile = pair; tile < num_tiles; tile += npairs)
 		{
-			const int tm = n_first ? (n_first > 1 ? m_tiles - 1 - tile / n_tiles : tile / n_tiles) : tile % m_tiles, tn = n_first ? tile % n_tiles : tile / m_tiles;
+			int tm, tn;
+			pair_tile_coords(tile, m_tiles, n_tiles, panel, &tm, &tn);
 			const int m0 = tm * (2 * BM) + static_cast<int>(rank) * BM;
 			const int n0 = tn * BN;
 			if (!mbar_wait(smem_u32(&bar_tfull[acc]), acc_phase, abortp))
@@ -503,18 +523,25 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
 	const int m_tiles = static_cast<int>(cdiv(M, 2 * BM)), n_tiles = static_cast<int>(cdiv(N, BN));
 	const int64_t tiles = static_cast<int64_t>(m_tiles) * n_tiles;
 	const int64_t pairs = tiles < kNumSMs / 2 ? tiles : kNumSMs / 2;
-	// Tile order. The pairs of one wave work on consecutive tiles: dealt down the rows first, a wave touches every row block of X
-	// and 74 / m_tiles column blocks of W; dealt across the columns first, every column block of W and 74 / n_tiles row blocks of X.
-	// Whatever is touched by every wave has to stay in L2 between waves, and what a CTA finds there is about half of the 126 MB
-	// (each die keeps its own copy of lines both use). X of out_proj (67 MB at 8192 tokens, W 17 MB) does not: ncu counted 206 MB
-	// read from DRAM per launch against 84 MB of operands; in_proj (X 34 MB, W 34 MB) read 83 MB against 68 MB. Measured in the
-	// mixer step: out_proj 107.1 -> 106.4 us, step 0.4450 -> 0.4426 ms (its X is partly in L2 from the kernel before it). Such an X
-	// is walked from its last row block to its first: whatever produced it most likely wrote the rows in ascending order, so the
-	// last ones are the ones still in L2 (step 0.4366 -> 0.4351 ms).
-	const double x_bytes = 2.0 * M * K, w_bytes = 2.0 * N * K;
-	const int n_first = x_bytes > 48e6 && w_bytes < x_bytes ? 2 : 0;  // 2: and from the last row block of X to the first
+	// Tile order (pair_tile_coords). The pairs of one wave work on consecutive tiles; what every wave touches has to stay in L2
+	// between waves, and what a CTA finds there is about half of the 126 MB (each die keeps its own copy of lines both use). Dealt
+	// down the rows first, a wave touches every row block of X: fine while X fits (in_proj at 8192 tokens, X 34 MB: ncu counted
+	// 83 MB read from DRAM per launch against 68 MB of operands), not beyond (out_proj there, X 67 MB and W 17 MB: 206 MB against
+	// 84 MB). A larger X is walked in panels of column blocks whose slab of W (~30 MB) stays resident while the row blocks stream
+	// past it once per panel, from the last row block to the first (whatever produced X most likely wrote its rows in ascending
+	// order, so the last ones are the ones still in L2). Measured: 8192 tokens, out_proj 107.1 -> 105.5 us; 16384 tokens of the
+	// 7B-shaped layer (X 117 / 235 MB), panels of 16 / 8 against one panel of all columns: in_proj 1.416 -> 1.257 ms, out_proj
+	// 0.654 -> 0.618 ms, step 2.60 -> 2.37 ms; panels at 8192 tokens for in_proj as well: 0.4400 -> 0.4432 ms per step.
+	const double x_bytes = 2.0 * M * K;
+	int panel = 0;
+	if (x_bytes > 48e6)
+	{
+		panel = static_cast<int>(30e6 / (512.0 * K));
+		panel = panel < 4 ? 4 : panel;
+		panel = panel > n_tiles ? n_tiles : panel;
+	}
 	gemm_f16_tcgen05_pair_kernel<B_MN><<<static_cast<unsigned>(2 * pairs), THREADS, SMEM_BYTES, st>>>(tmA, tmB, tmY, M, N, K, m_tiles,
-		n_tiles, device_error_word(), residual, ldr, n_first);
+		n_tiles, device_error_word(), residual, ldr, panel);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }
