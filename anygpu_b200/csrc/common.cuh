@@ -181,6 +181,16 @@ struct Pack
 		else
 			asm volatile("ld.global.v2.u32 {%0, %1}, [%2];" : "=r"(bits.x), "=r"(bits.y) : "l"(p) : "memory");
 	}
+	// The same for data that is read once: the lines are marked first to leave L2, so that what the kernel writes (the next
+	// kernel's input) is what stays there.
+	__device__ __forceinline__ void load_pinned_once(const T* p)
+	{
+		static_assert(V * sizeof(T) == 16, "load_pinned_once moves 16 bytes");
+		uint64_t pol;
+		asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+		asm volatile("ld.global.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+			: "=r"(bits.x), "=r"(bits.y), "=r"(bits.z), "=r"(bits.w) : "l"(p), "l"(pol) : "memory");
+	}
 	__device__ __forceinline__ void store(T* p) const { *reinterpret_cast<B*>(p) = bits; }
 	// f16 pairs go through the packed half2 conversions (a scalar f16 -> f32 conversion issues on the slow XU pipe)
 	__device__ __forceinline__ void unpack(float* f) const

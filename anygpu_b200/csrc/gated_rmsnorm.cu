@@ -44,7 +44,8 @@ __device__ __forceinline__ float block_sum(float v, float* red)
 // VEC: 16-byte vectors (rows and group starts 16-byte aligned). CACHED: the group fits the register cache.
 template <typename T, bool CACHED, int kNormThreads>
 __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T* x, int64_t xs,
-	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* y /* may alias x */, int64_t ys, int gsize, int ngroups, float eps)
+	const T* __restrict__ z, int64_t zs, const T* __restrict__ w, T* y /* may alias x */, int64_t ys, int gsize, int ngroups, float eps,
+	int ONCE /* x and z are dead after this kernel: their lines are marked first to leave L2 */)
 {
 	constexpr int E = NV<T>::E;
 	__shared__ float red[kNormThreads / 32];
@@ -69,8 +70,8 @@ __global__ void __launch_bounds__(kNormThreads) gated_rmsnorm_vec_kernel(const T
 			const int i = threadIdx.x + it * kNormThreads;
 			if (i < nvec)
 			{
-				rx[it].load_pinned(xr + i * E);
-				rz[it].load_pinned(zr + i * E);
+				if (ONCE) { rx[it].load_pinned_once(xr + i * E); rz[it].load_pinned_once(zr + i * E); }
+				else { rx[it].load_pinned(xr + i * E); rz[it].load_pinned(zr + i * E); }
 			}
 		}
 #pragma unroll
@@ -380,7 +381,7 @@ static int rms_norm(const void* xv, int64_t xs, const void* wv, void* yv, int64_
 
 template <typename T>
 static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs, const void* wv, void* yv, int64_t ys,
-	int64_t rows, int64_t d, int64_t gsize, float eps, cudaStream_t st)
+	int64_t rows, int64_t d, int64_t gsize, float eps, cudaStream_t st, int once = 0)
 {
 	constexpr int E = NV<T>::E;
 	const T* x = static_cast<const T*>(xv);
@@ -398,11 +399,11 @@ static int gated_rmsnorm(const void* xv, int64_t xs, const void* zv, int64_t zs,
 	if (!vec)
 		gated_rmsnorm_scalar_kernel<T, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
 	else if (gsize / E <= kNormCache * 128)
-		gated_rmsnorm_vec_kernel<T, true, 128><<<g, 128, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+		gated_rmsnorm_vec_kernel<T, true, 128><<<g, 128, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps, once);
 	else if (gsize / E <= kNormCache * 256)
-		gated_rmsnorm_vec_kernel<T, true, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+		gated_rmsnorm_vec_kernel<T, true, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps, once);
 	else
-		gated_rmsnorm_vec_kernel<T, false, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps);
+		gated_rmsnorm_vec_kernel<T, false, 256><<<g, 256, 0, st>>>(x, xs, z, zs, w, y, ys, gs, ngroups, eps, once);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
 }
@@ -465,6 +466,18 @@ int row_scale_rsqrt(int dtype, void* out, int64_t ld, const float* sumsq, int64_
 			static_cast<int>(cols), inv_d, eps);
 	B200_LAUNCH_CHECK();
 	return B200_OK;
+}
+
+// The gated norm inside the prefill mixer: its inputs (the scan's y, read in place, and the z columns of the in_proj output) are
+// not read again, so they are loaded with an evict-first L2 policy and the output, which out_proj reads next, is what stays in L2
+// (8192 x 4096: 36.2 -> 34.9 us).
+int gated_rmsnorm_last_use(int dtype, const void* x, int64_t xs, const void* z, int64_t zs, const void* w, void* y, int64_t ys,
+	int64_t rows, int64_t d, int64_t group_size, float eps, cudaStream_t st)
+{
+	if (group_size == 0) group_size = d;
+	if (rows <= 0) return B200_OK;
+	if (dtype == B200_F16) return gated_rmsnorm<__half>(x, xs, z, zs, w, y, ys, rows, d, group_size, eps, st, 1);
+	return gated_rmsnorm<float>(x, xs, z, zs, w, y, ys, rows, d, group_size, eps, st, 1);
 }
 
 }  // namespace b200

@@ -65,6 +65,8 @@ int ssd_segment_prefix(const float* seg_states, const float* seg_logdecay, int n
 
 int linear_f16_residual(const void* x, int64_t ldx, const void* w, int w_layout, void* y, int64_t ldy, int64_t M, int64_t K, int64_t N,
 	const void* residual, int64_t ldr, cudaStream_t st);
+int gated_rmsnorm_last_use(int dtype, const void* x, int64_t xs, const void* z, int64_t zs, const void* w, void* y, int64_t ys,
+	int64_t rows, int64_t d, int64_t group_size, float eps, cudaStream_t st);
 
 // fused decode stages (gemm_decode.cu, ssm_update.cu)
 bool decode_linear_applies(int dtype, int64_t M, int64_t K, int64_t N);
@@ -243,8 +245,8 @@ static int mixer_prefill_impl(int dtype, const b200_mamba2_config* cfg, const b2
 		conv_state_out, ssm_state_out, st, true);
 	if (rc) return rc;
 	stage_mark(3, st);
-	rc = b200_gated_rmsnorm(dtype, ws.y, d_inner, ws.zxbcdt, m.ldz, w->norm_weight, ws.y, d_inner, T, d_inner,
-		cfg->norm_group_size, cfg->eps, stream);
+	rc = gated_rmsnorm_last_use(dtype, ws.y, d_inner, ws.zxbcdt, m.ldz, w->norm_weight, ws.y, d_inner, T, d_inner,
+		cfg->norm_group_size, cfg->eps, st);
 	if (rc) return rc;
 	stage_mark(4, st);
 	rc = out_proj_residual(dtype, ws.y, d_inner, w->out_proj_weight, w->out_proj_layout, out, cfg->d_model, T, d_inner, cfg->d_model,
